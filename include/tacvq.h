@@ -1,0 +1,169 @@
+/*
+ * tacvq.h - C ABI of libtacvq.so: hard residual GSRQ/CQ KV-cache quantization on B200 (sm_100a).
+ *
+ * The reference project (wrb1371/tac-vq-kv-cache) is pure Python and has no FFI of its own; its
+ * boundary is a set of Python callables.  Each entry point below names the reference callable whose
+ * forward arithmetic it replaces (paths are inside the reference project).  A Python binding that
+ * keeps the reference's signatures on top of these entry points ships in the package
+ * (tac_vq_kv_cache_b200/jointkv); any other host language can bind the same symbols.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its comment says "host".  The library never
+ *     allocates or frees device memory; scratch space is passed in by the caller.
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call returns
+ *     without synchronising.  NULL is the legacy default stream.
+ *   - Return value: 0 on success; < 0 an argument error found on the host before anything was
+ *     launched (see enum tacvq_status); > 0 a cudaError_t from a launch.  No call aborts or prints.
+ *   - Canonical layouts (row-major, innermost last):
+ *       states  [B, H, T, D]          fp16 or fp32; D = G*d contiguous, other strides given in elements
+ *       tables  [H, S, G, K, d]       fp16 "deployed" codewords (the fp16 round trip of the masters)
+ *       codes   [B, H, T_cap, S, G]   uint8; the reference's [B,H,T,S] (G=1) and [B,H,T,G] (S=1)
+ *                                     layouts are this one with a unit axis dropped
+ *     H = KV heads, G = channel groups, S = residual stages, K <= 256 codewords, d = D/G.
+ *   - Arithmetic contract for a code (closed_loop_vq.py:66-75, cq_tac.py:86-96): fp32 distance
+ *     (|x|^2 + |c_k|^2) - 2*(x.c_k) in that association; x.c_k one fused-multiply-add chain from
+ *     element 0; squared norms from separately rounded products (order documented in
+ *     csrc/common.cuh); lowest index wins a tie.
+ */
+#ifndef TACVQ_H
+#define TACVQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TACVQ_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define TACVQ_API __attribute__((visibility("default")))
+#else
+#define TACVQ_API
+#endif
+
+enum tacvq_dtype { TACVQ_F16 = 0, TACVQ_F32 = 1 };
+
+enum tacvq_status {
+    TACVQ_OK = 0,
+    TACVQ_ERR_NULL = -1,        /* a required pointer is NULL */
+    TACVQ_ERR_GEOMETRY = -2,    /* sizes inconsistent (D != G*d, Hq % Hkv, non-positive extent ...) */
+    TACVQ_ERR_DTYPE = -3,       /* dtype tag is not a tacvq_dtype */
+    TACVQ_ERR_RANGE = -4,       /* token offset/extent outside the code buffer */
+    TACVQ_ERR_WORKSPACE = -5,   /* scratch buffer missing, too small or misaligned */
+    TACVQ_ERR_UNSUPPORTED = -6, /* geometry valid but no kernel is built for it */
+    TACVQ_ERR_ALIGN = -7,       /* a pointer or stride breaks the stated alignment */
+    TACVQ_ERR_DEVICE = -8       /* current device is not compute capability 10.x */
+};
+
+typedef void *tacvq_stream_t;
+
+/* ABI version of the loaded library (TACVQ_ABI_VERSION at build time). */
+TACVQ_API int tacvq_version(void);
+
+/* Static, human-readable text for a status returned by any call below. */
+TACVQ_API const char *tacvq_status_string(int status);
+
+/*
+ * Squared norms of all codewords, out[words] fp32, words = H*S*G*K, in the library's documented
+ * order.  Replaces `table.square().sum(dim=-1)` (closed_loop_vq.py:66; cq_tac.py:86).
+ */
+TACVQ_API int tacvq_table_sqnorm(const uint16_t *tables_f16, float *out, int64_t words, int d, tacvq_stream_t stream);
+
+/*
+ * Encode: greedy residual nearest-codeword search, all S stages fused, groups independent.
+ * Replaces the forward of hard_residual_vq_exits (closed_loop_vq.py:235-410, G=1) and of
+ * hard_grouped_cq (cq_tac.py:33-114, S=1), including _nearest_indices (closed_loop_vq.py:52-76).
+ *
+ *   x, x_dtype         states [B,H,T,D]; strides sxb,sxh,sxt in elements, last axis contiguous;
+ *                      base and strides such that every row starts 16-byte aligned
+ *   tables_f16         [H,S,G,K,d]
+ *   table_sqnorm       NULL (computed inside) or [H,S,G,K] fp32 supplied by the caller
+ *   codes              [B,H,T_cap,S,G]; rows t0 .. t0+T-1 are written, the rest is untouched
+ *   recon, recon_dtype NULL, or [B,H,T,D] contiguous receiving sum_s word_s (fp32 sum in stage
+ *                      order, one final cast) - the reference's exit at depth S
+ *   d = D/G must be one of 1..8, 16, 32, 64, 128.
+ */
+TACVQ_API int tacvq_encode(const void *x, int x_dtype, int64_t sxb, int64_t sxh, int64_t sxt, const uint16_t *tables_f16,
+                 const float *table_sqnorm, uint8_t *codes, void *recon, int recon_dtype, int B, int H, int T, int D,
+                 int G, int S, int K, int64_t t0, int64_t T_cap, tacvq_stream_t stream);
+
+/*
+ * Encode with a whitened assignment geometry.  Replaces the `assignment_whiteners` branch of
+ * hard_residual_vq_exits (closed_loop_vq.py:312-320, 384-390: one [D,D] matrix per head, G must
+ * be 1 there) and the `selector_whiteners` branch of hard_grouped_cq (cq_tac.py:80-85: one [d,d]
+ * matrix per (head, group), S must be 1 there).  The search runs on W.x against W-transformed
+ * words and subtracts transformed words; codes index the plain tables, recon uses plain words.
+ *
+ *   whitener           [H,G,d,d] fp32, row-major (y_i = sum_j W[i][j] x_j)
+ *   search_tables      [H,S,G,K,d] fp32 scratch: receives the transformed words (caller-owned)
+ *   search_rows        [B,H,T,D] fp32 scratch: receives the transformed rows (caller-owned)
+ */
+TACVQ_API int tacvq_encode_whitened(const void *x, int x_dtype, int64_t sxb, int64_t sxh, int64_t sxt,
+                          const uint16_t *tables_f16, const float *whitener, float *search_tables,
+                          float *search_rows, uint8_t *codes, void *recon, int recon_dtype, int B, int H, int T, int D,
+                          int G, int S, int K, int64_t t0, int64_t T_cap, tacvq_stream_t stream);
+
+/*
+ * Decode: rebuild rows t0 .. t0+T-1 from stored codes using the first S_use stages.
+ * Replaces _gather_words + the fp32 stage sum (closed_loop_vq.py:127-139, 376-381, 398-403),
+ * _gather_group_words (cq_tac.py:21-30) and frozen_assignment_u16_reconstruction
+ * (experiments/train_pure_uniform16_closed_loop_vq.py:395-442).   out [B,H,T,D] contiguous.
+ */
+TACVQ_API int tacvq_decode(const uint8_t *codes, const uint16_t *tables_f16, void *out, int out_dtype, int B, int H, int T,
+                 int D, int G, int S, int S_use, int K, int64_t t0, int64_t T_cap, tacvq_stream_t stream);
+
+/*
+ * Gradient of the hard forward with respect to the codeword masters: grad_tables[h,s,g,code,:] +=
+ * grad_out[b,h,t,g*d:(g+1)*d] for every stage s < S_use (the straight-through edge through the
+ * fp16 round trip has unit gain: closed_loop_vq.py:298, 376-381; cq_tac.py:77, 98-99).
+ * grad_tables [H,S,G,K,d] fp32 is accumulated into (caller zeroes it); grad_out [B,H,T,D] fp32 contiguous.
+ */
+TACVQ_API int tacvq_codeword_grad(const uint8_t *codes, const float *grad_out, float *grad_tables, int B, int H, int T, int D,
+                        int G, int S, int S_use, int K, int64_t t0, int64_t T_cap, tacvq_stream_t stream);
+
+/*
+ * Bytes of scratch tacvq_attn_decode needs for this geometry (host computation, no CUDA call
+ * besides a device-attribute query).  0 on invalid geometry.
+ */
+TACVQ_API size_t tacvq_attn_workspace_bytes(int B, int Hq, int Hkv, int D, int G, int S);
+
+/*
+ * One decode step of attention computed directly on the stored codes: per-query look-up table of
+ * q . codeword, score = sum of table entries addressed by the K codes, softmax, V accumulated
+ * from the V codes, sequence split across thread blocks and merged by log-sum-exp.
+ * Replaces the decode branch of the reference's attention_forward
+ * (experiments_followup_mistral/evaluate_mistral_longbench.py:112-122) together with the dense
+ * decoded window LayerCache keeps for it (:53-70); rotary embedding is NOT applied here.
+ *
+ *   q_f16              [B,Hq,D] fp16, already multiplied by the softmax scale
+ *   kcodes, vcodes     [B,Hkv,T_cap,S,G] uint8 (16-byte aligned)
+ *   ktab_f16, vtab_f16 [Hkv,S,G,K,d] fp16
+ *   seq_start, seq_end NULL or int32 [B]: row b attends tokens [seq_start[b], seq_end[b]);
+ *                      NULL means 0 resp. T_cap.  An empty range yields out = 0, m = -inf, l = 0.
+ *   workspace          scratch of at least tacvq_attn_workspace_bytes(...) bytes, 256-byte aligned
+ *   out_f16            NULL or [B,Hq,D] fp16: acc / l
+ *   state_out          NULL or [B,Hq,2+D] fp32: (m, l, acc[D]) with m the maximum score (natural
+ *                      log units), l = sum exp(s-m), acc = sum exp(s-m) v  - the partial softmax
+ *                      state that ranks exchange when the sequence is split across GPUs
+ *   Hq % Hkv == 0, Hq/Hkv <= 8, K == 256, D % 32 == 0, D <= 256.
+ */
+TACVQ_API int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_t *vcodes, const uint16_t *ktab_f16,
+                      const uint16_t *vtab_f16, const int32_t *seq_start, const int32_t *seq_end, void *workspace,
+                      size_t workspace_bytes, uint16_t *out_f16, float *state_out, int B, int Hq, int Hkv, int D,
+                      int G, int S, int K, int64_t T_cap, tacvq_stream_t stream);
+
+/*
+ * Log-sum-exp merge of n_parts partial softmax states [n_parts,B,Hq,2+D] fp32 (for example the
+ * all-gathered per-GPU states of a sequence-split decode): M = max m_r, L = sum l_r e^(m_r-M),
+ * A = sum acc_r e^(m_r-M).  out_f16 (NULL or [B,Hq,D]) receives A/L; merged (NULL or [B,Hq,2+D])
+ * receives (M, L, A).  Softmax attention itself: src/jointkv/local_attention.py:673-679.
+ */
+TACVQ_API int tacvq_attn_combine(const float *states, int n_parts, uint16_t *out_f16, float *merged, int B, int Hq, int D,
+                       tacvq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TACVQ_H */

@@ -1,0 +1,105 @@
+"""Preallocated uint8 code store for one layer, with in-place append and attention over the codes.
+
+Replaces the reference's decode-time ``LayerCache``
+(experiments_followup_mistral/evaluate_mistral_longbench.py:29-78) and the decode
+branch of its ``attention_forward`` (:112-122):
+
+* the reference grows ``[1,H,T,S]`` code tensors with ``torch.cat`` on every token
+  (:49-50, an O(T) copy per step) and additionally keeps a dense fp16 window of the
+  last 4096 decoded tokens (:53-59) which its attention reads;
+* here the codes live in one ``[B,H,T_max,S,G]`` buffer per side that the encode
+  kernel writes at offset ``length``, and attention reads the codes themselves,
+  so there is no decoded window.
+
+``visible()`` keeps the reference's window rule ``start = max(0, length - window)``
+(:62-70) and ``payload_bytes()`` its byte count (:72-73): the bytes of the stored
+codes of both sides.  Rotary position embedding is not applied by the attention
+kernel (keys are stored as encoded).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+
+class VQCodeCache:
+    """K and V codes of one layer for a batch of sequences that advance in lockstep."""
+
+    def __init__(
+        self,
+        key_tables: torch.Tensor,
+        value_tables: torch.Tensor,
+        *,
+        batch: int,
+        max_tokens: int,
+        window: int | None = None,
+        device: torch.device | str | None = None,
+    ) -> None:
+        """``key_tables`` / ``value_tables``: ``[H,S,G,K,d]`` masters or deployed fp16 tables."""
+        if key_tables.ndim != 5 or key_tables.shape != value_tables.shape:
+            raise ValueError("tables must be [H,S,G,K,d] with equal K and V geometry")
+        if batch <= 0 or max_tokens <= 0 or (window is not None and window <= 0):
+            raise ValueError("batch, max_tokens and window must be positive")
+        self.device = torch.device(device if device is not None else key_tables.device)
+        self.key_tables = ops.deployed_tables(key_tables).to(self.device)
+        self.value_tables = ops.deployed_tables(value_tables).to(self.device)
+        heads, stages, groups, _words, sub = map(int, key_tables.shape)
+        self.batch, self.heads, self.stages, self.groups, self.dim = batch, heads, stages, groups, groups * sub
+        self.max_tokens = int(max_tokens)
+        self.window = window
+        shape = (batch, heads, self.max_tokens, stages, groups)
+        self.key = torch.zeros(shape, dtype=torch.uint8, device=self.device)
+        self.value = torch.zeros(shape, dtype=torch.uint8, device=self.device)
+        self.length = 0
+        self._start = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self._end = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self._workspace: torch.Tensor | None = None
+
+    def reset(self) -> None:
+        self.length = 0
+
+    def append(self, raw_key: torch.Tensor, raw_value: torch.Tensor, *, want_recon: bool = False):
+        """Encode ``[B,H,T,D]`` rows and store their codes at positions ``length .. length+T-1``.
+
+        Returns ``(key_recon, value_recon)`` (``None`` unless ``want_recon``), the
+        quantised rows an adapter attends with during prefill.
+        """
+        tokens = int(raw_key.shape[2])
+        if raw_key.shape != raw_value.shape or tuple(raw_key.shape[:2]) != (self.batch, self.heads) or raw_key.shape[3] != self.dim:
+            raise ValueError("rows must be [B,H,T,D] matching the cache geometry")
+        if self.length + tokens > self.max_tokens:
+            raise ValueError("code cache is full")
+        _, key_recon = ops.encode(raw_key, self.key_tables, codes=self.key, t0=self.length, want_recon=want_recon)
+        _, value_recon = ops.encode(raw_value, self.value_tables, codes=self.value, t0=self.length, want_recon=want_recon)
+        self.length += tokens
+        return key_recon, value_recon
+
+    def visible(self) -> tuple[int, int]:
+        """Token range a decode step sees: the last ``window`` stored positions."""
+        start = 0 if self.window is None else max(0, self.length - self.window)
+        return start, self.length
+
+    def payload_bytes(self) -> int:
+        """Bytes of the stored K and V codes (what the reference's ledger counts)."""
+        return 2 * self.batch * self.heads * self.length * self.stages * self.groups
+
+    def attend(self, query: torch.Tensor, *, want_state: bool = False):
+        """One decode step: ``query [B,Hq,D]`` fp16 (already scaled) -> fp16 ``[B,Hq,D]``.
+
+        With ``want_state`` also returns the partial softmax state ``[B,Hq,2+D]``.
+        """
+        start, end = self.visible()
+        self._start.fill_(start)
+        self._end.fill_(end)
+        if self._workspace is None:
+            need = ops.attn_workspace_bytes(self.batch, int(query.shape[1]), self.heads, self.dim, self.groups, self.stages)
+            if need == 0:
+                raise ValueError("attention geometry not supported")
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        out, state = ops.attn_decode(
+            query, self.key, self.value, self.key_tables, self.value_tables, self._start, self._end,
+            workspace=self._workspace, want_state=want_state,
+        )
+        return (out, state) if want_state else out

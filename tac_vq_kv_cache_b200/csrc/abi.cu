@@ -1,0 +1,191 @@
+// C ABI of libtacvq.so: argument validation on the host, then dispatch to the kernels.
+// Declarations and the per-function contract live in include/tacvq.h.
+
+#include "common.cuh"
+
+namespace tacvq {
+
+int encode_dispatch(const EncodeArgs &a);
+int decode_dispatch(const uint8_t *codes, const __half *tables, void *out, int out_dtype, int B, int H, int T, int D,
+                    int G, int S, int S_use, int K, int64_t t0, int64_t T_cap, cudaStream_t stream);
+int codeword_grad_dispatch(const uint8_t *codes, const float *grad_out, float *grad_tables, int B, int H, int T, int D,
+                           int G, int S, int S_use, int K, int64_t t0, int64_t T_cap, cudaStream_t stream);
+int table_sqnorm_dispatch(const __half *tables, float *out, int64_t words, int d, cudaStream_t stream);
+int whiten_dispatch(const void *x, int x_dtype, int64_t sxb, int64_t sxh, int64_t sxt, const __half *tables,
+                    const float *whitener, float *search_tables, float *search_rows, int B, int H, int T, int D, int G,
+                    int S, int K, cudaStream_t stream);
+int attn_generic_splits(int B, int Hkv, int64_t T_cap, int sms);
+int attn_generic_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
+                          const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, float *part, int B,
+                          int Hq, int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits, cudaStream_t stream);
+int attn_combine_dispatch(const float *states, int n_parts, __half *out, float *merged, int64_t rows, int D,
+                          cudaStream_t stream);
+bool attn_gsrq_supported(int Hq, int Hkv, int D, int G, int S, int K);
+size_t attn_gsrq_workspace_bytes(int B, int Hq, int Hkv, int D, int sms);
+int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
+                       const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, void *workspace,
+                       __half *out, float *state_out, int B, int Hq, int Hkv, int64_t T_cap, int sms,
+                       cudaStream_t stream);
+
+constexpr int kGenericMaxSplits = 64;
+
+static int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+static bool dtype_ok(int t) { return t == TACVQ_F16 || t == TACVQ_F32; }
+
+static bool sub_dim_ok(int d) { return (d >= 1 && d <= 8) || d == 16 || d == 32 || d == 64 || d == 128; }
+
+static int check_code_geometry(int B, int H, int T, int D, int G, int S, int K, int64_t t0, int64_t T_cap) {
+    if (B < 0 || T < 0 || H <= 0 || D <= 0 || G <= 0 || S <= 0 || K <= 0 || K > kMaxWords) return TACVQ_ERR_GEOMETRY;
+    if (D % G != 0) return TACVQ_ERR_GEOMETRY;
+    if (t0 < 0 || T_cap < 0 || t0 + T > T_cap) return TACVQ_ERR_RANGE;
+    return TACVQ_OK;
+}
+
+}  // namespace tacvq
+
+using namespace tacvq;
+
+extern "C" {
+
+int tacvq_version(void) { return TACVQ_ABI_VERSION; }
+
+const char *tacvq_status_string(int status) {
+    switch (status) {
+        case TACVQ_OK: return "ok";
+        case TACVQ_ERR_NULL: return "a required pointer is NULL";
+        case TACVQ_ERR_GEOMETRY: return "inconsistent geometry";
+        case TACVQ_ERR_DTYPE: return "unknown dtype tag";
+        case TACVQ_ERR_RANGE: return "token range outside the code buffer";
+        case TACVQ_ERR_WORKSPACE: return "workspace missing, too small or misaligned";
+        case TACVQ_ERR_UNSUPPORTED: return "no kernel built for this geometry";
+        case TACVQ_ERR_ALIGN: return "pointer or stride alignment";
+        case TACVQ_ERR_DEVICE: return "device is not compute capability 10.x";
+        default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
+    }
+}
+
+int tacvq_table_sqnorm(const uint16_t *tables_f16, float *out, int64_t words, int d, tacvq_stream_t stream) {
+    if (!tables_f16 || !out) return TACVQ_ERR_NULL;
+    if (words < 0 || d <= 0 || d > 128) return TACVQ_ERR_GEOMETRY;
+    return table_sqnorm_dispatch((const __half *)tables_f16, out, words, d, (cudaStream_t)stream);
+}
+
+int tacvq_encode(const void *x, int x_dtype, int64_t sxb, int64_t sxh, int64_t sxt, const uint16_t *tables_f16,
+                 const float *table_sqnorm, uint8_t *codes, void *recon, int recon_dtype, int B, int H, int T, int D,
+                 int G, int S, int K, int64_t t0, int64_t T_cap, tacvq_stream_t stream) {
+    if (!x || !tables_f16 || !codes) return TACVQ_ERR_NULL;
+    if (!dtype_ok(x_dtype) || (recon && !dtype_ok(recon_dtype))) return TACVQ_ERR_DTYPE;
+    const int g = check_code_geometry(B, H, T, D, G, S, K, t0, T_cap);
+    if (g != TACVQ_OK) return g;
+    if (!sub_dim_ok(D / G)) return TACVQ_ERR_UNSUPPORTED;
+    if (sxb < 0 || sxh < 0 || sxt < D) return TACVQ_ERR_GEOMETRY;
+    if ((int64_t)B * T == 0) return TACVQ_OK;
+    EncodeArgs a{x, x_dtype, sxb, sxh, sxt, tables_f16, false, table_sqnorm, codes, recon, recon_dtype,
+                 (const __half *)tables_f16, B, H, T, D, G, S, K, t0, T_cap, (cudaStream_t)stream};
+    return encode_dispatch(a);
+}
+
+int tacvq_encode_whitened(const void *x, int x_dtype, int64_t sxb, int64_t sxh, int64_t sxt,
+                          const uint16_t *tables_f16, const float *whitener, float *search_tables,
+                          float *search_rows, uint8_t *codes, void *recon, int recon_dtype, int B, int H, int T, int D,
+                          int G, int S, int K, int64_t t0, int64_t T_cap, tacvq_stream_t stream) {
+    if (!x || !tables_f16 || !codes || !whitener || !search_tables || !search_rows) return TACVQ_ERR_NULL;
+    if (!dtype_ok(x_dtype) || (recon && !dtype_ok(recon_dtype))) return TACVQ_ERR_DTYPE;
+    const int g = check_code_geometry(B, H, T, D, G, S, K, t0, T_cap);
+    if (g != TACVQ_OK) return g;
+    if (!sub_dim_ok(D / G)) return TACVQ_ERR_UNSUPPORTED;
+    if (sxb < 0 || sxh < 0 || sxt < D) return TACVQ_ERR_GEOMETRY;
+    if ((int64_t)B * T == 0) return TACVQ_OK;
+    int st = whiten_dispatch(x, x_dtype, sxb, sxh, sxt, (const __half *)tables_f16, whitener, search_tables,
+                             search_rows, B, H, T, D, G, S, K, (cudaStream_t)stream);
+    if (st != TACVQ_OK) return st;
+    EncodeArgs a{search_rows, TACVQ_F32, (int64_t)H * T * D, (int64_t)T * D, (int64_t)D, search_tables, true, nullptr,
+                 codes, recon, recon_dtype, (const __half *)tables_f16, B, H, T, D, G, S, K, t0, T_cap,
+                 (cudaStream_t)stream};
+    return encode_dispatch(a);
+}
+
+int tacvq_decode(const uint8_t *codes, const uint16_t *tables_f16, void *out, int out_dtype, int B, int H, int T,
+                 int D, int G, int S, int S_use, int K, int64_t t0, int64_t T_cap, tacvq_stream_t stream) {
+    if (!codes || !tables_f16 || !out) return TACVQ_ERR_NULL;
+    if (!dtype_ok(out_dtype)) return TACVQ_ERR_DTYPE;
+    const int g = check_code_geometry(B, H, T, D, G, S, K, t0, T_cap);
+    if (g != TACVQ_OK) return g;
+    if (S_use < 0 || S_use > S) return TACVQ_ERR_GEOMETRY;
+    return decode_dispatch(codes, (const __half *)tables_f16, out, out_dtype, B, H, T, D, G, S, S_use, K, t0, T_cap,
+                           (cudaStream_t)stream);
+}
+
+int tacvq_codeword_grad(const uint8_t *codes, const float *grad_out, float *grad_tables, int B, int H, int T, int D,
+                        int G, int S, int S_use, int K, int64_t t0, int64_t T_cap, tacvq_stream_t stream) {
+    if (!codes || !grad_out || !grad_tables) return TACVQ_ERR_NULL;
+    const int g = check_code_geometry(B, H, T, D, G, S, K, t0, T_cap);
+    if (g != TACVQ_OK) return g;
+    if (S_use < 0 || S_use > S) return TACVQ_ERR_GEOMETRY;
+    return codeword_grad_dispatch(codes, grad_out, grad_tables, B, H, T, D, G, S, S_use, K, t0, T_cap,
+                                  (cudaStream_t)stream);
+}
+
+static int check_attn_geometry(int B, int Hq, int Hkv, int D, int G, int S, int K) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || G <= 0 || S <= 0) return TACVQ_ERR_GEOMETRY;
+    if (Hq % Hkv != 0 || D % G != 0) return TACVQ_ERR_GEOMETRY;
+    const int rep = Hq / Hkv;
+    if (K != 256 || D % 32 != 0 || D > 256) return TACVQ_ERR_UNSUPPORTED;
+    if (rep != 1 && rep != 2 && rep != 4 && rep != 8) return TACVQ_ERR_UNSUPPORTED;
+    if ((D / G) % (D / 32) != 0) return TACVQ_ERR_UNSUPPORTED;  // a lane's channels stay inside one group
+    return TACVQ_OK;
+}
+
+size_t tacvq_attn_workspace_bytes(int B, int Hq, int Hkv, int D, int G, int S) {
+    if (check_attn_geometry(B, Hq, Hkv, D, G, S, 256) != TACVQ_OK) return 0;
+    size_t generic = (size_t)kGenericMaxSplits * B * Hq * (D + 2) * sizeof(float);
+    size_t fast = attn_gsrq_supported(Hq, Hkv, D, G, S, 256) ? attn_gsrq_workspace_bytes(B, Hq, Hkv, D, sm_count()) : 0;
+    size_t need = generic > fast ? generic : fast;
+    return (need + 255) & ~(size_t)255;
+}
+
+int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_t *vcodes, const uint16_t *ktab_f16,
+                      const uint16_t *vtab_f16, const int32_t *seq_start, const int32_t *seq_end, void *workspace,
+                      size_t workspace_bytes, uint16_t *out_f16, float *state_out, int B, int Hq, int Hkv, int D,
+                      int G, int S, int K, int64_t T_cap, tacvq_stream_t stream) {
+    if (!q_f16 || !kcodes || !vcodes || !ktab_f16 || !vtab_f16) return TACVQ_ERR_NULL;
+    if (!out_f16 && !state_out) return TACVQ_ERR_NULL;
+    const int g = check_attn_geometry(B, Hq, Hkv, D, G, S, K);
+    if (g != TACVQ_OK) return g;
+    if (T_cap < 0 || T_cap > 0x7fffffff) return TACVQ_ERR_RANGE;
+    if (!workspace || ((uintptr_t)workspace & 255) != 0 || workspace_bytes < tacvq_attn_workspace_bytes(B, Hq, Hkv, D, G, S))
+        return TACVQ_ERR_WORKSPACE;
+    if ((((uintptr_t)kcodes | (uintptr_t)vcodes) & 15) != 0) return TACVQ_ERR_ALIGN;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (attn_gsrq_supported(Hq, Hkv, D, G, S, K)) {
+        return attn_gsrq_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
+                                  (const __half *)vtab_f16, seq_start, seq_end, workspace, (__half *)out_f16, state_out,
+                                  B, Hq, Hkv, T_cap, sm_count(), s);
+    }
+    const int splits = attn_generic_splits(B, Hkv, T_cap, sm_count());
+    int st = attn_generic_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
+                                   (const __half *)vtab_f16, seq_start, seq_end, (float *)workspace, B, Hq, Hkv, D, G,
+                                   S, K, T_cap, splits, s);
+    if (st != TACVQ_OK) return st;
+    return attn_combine_dispatch((const float *)workspace, splits, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);
+}
+
+int tacvq_attn_combine(const float *states, int n_parts, uint16_t *out_f16, float *merged, int B, int Hq, int D,
+                       tacvq_stream_t stream) {
+    if (!states || (!out_f16 && !merged)) return TACVQ_ERR_NULL;
+    if (n_parts <= 0 || B <= 0 || Hq <= 0 || D <= 0) return TACVQ_ERR_GEOMETRY;
+    return attn_combine_dispatch(states, n_parts, (__half *)out_f16, merged, (int64_t)B * Hq, D, (cudaStream_t)stream);
+}
+
+}  // extern "C"

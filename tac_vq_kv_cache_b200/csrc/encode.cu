@@ -1,0 +1,369 @@
+// Encode kernels: greedy residual nearest-codeword search with all stages fused.
+//
+// Two kernels cover the geometry family (G groups, S stages, d = D/G, K <= 256 codewords):
+//   encode_small  d <= 16   one thread owns TPT rows of one (head, group); the stage tables of that
+//                           (head, group) live in shared memory as fp32 and are read as warp
+//                           broadcasts; residual, running minimum and reconstruction stay in registers.
+//   encode_large  d >= 32   a register-tiled fp32 GEMM per stage (4 rows x 16 codewords per thread),
+//                           residual tile and stage table in shared memory, the contraction index
+//                           outermost so every dot product is still one FMA chain from element 0.
+// Both are FFMA-bound by design: an exact fp32 distance is what decides a code.
+//
+// Reference statements: src/jointkv/closed_loop_vq.py:52-76 (search), :343-395 (stage recursion),
+// src/jointkv/cq_tac.py:86-105 (grouped one-stage form).
+
+#include "common.cuh"
+
+namespace tacvq {
+
+// ------------------------------------------------------------------------------------------------
+// d <= 16
+// ------------------------------------------------------------------------------------------------
+
+template <int DSUB, int TPT, typename XT, typename TT>
+__global__ void __launch_bounds__(128)
+encode_small_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const TT *__restrict__ tables,
+                    const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
+                    int recon_dtype, const __half *__restrict__ recon_tables, int B, int H, int T, int G, int S, int K,
+                    int64_t t0, int64_t T_cap) {
+    extern __shared__ __align__(16) float smem[];
+    float *tab = smem;                       // [S][K][DSUB]
+    float *nrm = smem + (size_t)S * K * DSUB;  // [S][K]
+
+    const int hg = blockIdx.y;
+    const int h = hg / G, g = hg % G;
+    const int tid = threadIdx.x;
+
+    for (int idx = tid; idx < S * K * DSUB; idx += blockDim.x) {
+        const int i = idx % DSUB;
+        const int k = (idx / DSUB) % K;
+        const int s = idx / (DSUB * K);
+        tab[idx] = to_float<TT>(tables[((((int64_t)h * S + s) * G + g) * K + k) * DSUB + i]);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < S * K; idx += blockDim.x) {
+        if (sqnorm_in != nullptr) {
+            const int k = idx % K, s = idx / K;
+            nrm[idx] = sqnorm_in[(((int64_t)h * S + s) * G + g) * K + k];
+        } else {
+            const float *row = tab + (size_t)idx * DSUB;
+            nrm[idx] = sqnorm_ordered<DSUB>([&](int i) { return row[i]; });
+        }
+    }
+    __syncthreads();
+
+    const int64_t rows = (int64_t)B * T;
+    const int64_t tile = (int64_t)blockIdx.x * (128 * TPT);
+
+    float res[TPT][DSUB];
+    float dec[TPT][DSUB];
+    int64_t row_of[TPT];
+#pragma unroll
+    for (int j = 0; j < TPT; ++j) {
+        const int64_t row = tile + j * 128 + tid;
+        row_of[j] = row;
+        if (row < rows) {
+            const int64_t b = row / T, t = row % T;
+            const XT *src = x + b * sxb + (int64_t)h * sxh + t * sxt + (int64_t)g * DSUB;
+#pragma unroll
+            for (int i = 0; i < DSUB; ++i) res[j][i] = to_float<XT>(src[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < DSUB; ++i) res[j][i] = 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < DSUB; ++i) dec[j][i] = 0.0f;
+    }
+
+    for (int s = 0; s < S; ++s) {
+        const float *stab = tab + (size_t)s * K * DSUB;
+        const float *snrm = nrm + (size_t)s * K;
+        float xx[TPT], best[TPT];
+        int arg[TPT];
+#pragma unroll
+        for (int j = 0; j < TPT; ++j) {
+            xx[j] = sqnorm_ordered<DSUB>([&](int i) { return res[j][i]; });
+            best[j] = __int_as_float(0x7f800000);
+            arg[j] = 0;
+        }
+#pragma unroll 2
+        for (int k = 0; k < K; ++k) {
+            float c[DSUB];
+#pragma unroll
+            for (int i = 0; i < DSUB; ++i) c[i] = stab[k * DSUB + i];
+            const float cc = snrm[k];
+#pragma unroll
+            for (int j = 0; j < TPT; ++j) {
+                float dot = 0.0f;
+#pragma unroll
+                for (int i = 0; i < DSUB; ++i) dot = __fmaf_rn(res[j][i], c[i], dot);
+                const float dist = distance_expr(xx[j], cc, dot);
+                if (dist < best[j]) {
+                    best[j] = dist;
+                    arg[j] = k;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < TPT; ++j) {
+            const float *sel = stab + arg[j] * DSUB;
+#pragma unroll
+            for (int i = 0; i < DSUB; ++i) res[j][i] = __fsub_rn(res[j][i], sel[i]);
+            if (recon != nullptr) {
+                if (recon_tables == nullptr) {
+#pragma unroll
+                    for (int i = 0; i < DSUB; ++i) dec[j][i] = __fadd_rn(dec[j][i], sel[i]);
+                } else {
+                    const __half *plain = recon_tables + ((((int64_t)h * S + s) * G + g) * K + arg[j]) * DSUB;
+#pragma unroll
+                    for (int i = 0; i < DSUB; ++i) dec[j][i] = __fadd_rn(dec[j][i], __half2float(plain[i]));
+                }
+            }
+            if (row_of[j] < rows) {
+                const int64_t b = row_of[j] / T, t = row_of[j] % T;
+                codes[((((int64_t)b * H + h) * T_cap + t0 + t) * S + s) * G + g] = (uint8_t)arg[j];
+            }
+        }
+    }
+
+    if (recon != nullptr) {
+#pragma unroll
+        for (int j = 0; j < TPT; ++j) {
+            if (row_of[j] >= rows) continue;
+            const int64_t b = row_of[j] / T, t = row_of[j] % T;
+            const int64_t o = (((int64_t)b * H + h) * T + t) * ((int64_t)G * DSUB) + (int64_t)g * DSUB;
+            if (recon_dtype == TACVQ_F16) {
+#pragma unroll
+                for (int i = 0; i < DSUB; ++i) store_as<__half>((__half *)recon + o + i, dec[j][i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < DSUB; ++i) store_as<float>((float *)recon + o + i, dec[j][i]);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// d >= 32
+// ------------------------------------------------------------------------------------------------
+
+constexpr int kLargeRows = 64;    // rows (tokens) per block
+constexpr int kLargeThreads = 256;
+
+template <int DSUB>
+struct LargeLayout {
+    static constexpr int kStride = DSUB + 4;  // floats; keeps 16-byte rows and spreads rows over banks
+    static constexpr size_t kResFloats = (size_t)kLargeRows * kStride;
+    static constexpr size_t kTabFloats = (size_t)kMaxWords * kStride;
+    static constexpr size_t bytes(int S) {
+        return (kResFloats + kTabFloats + kMaxWords + kLargeRows) * sizeof(float) + (size_t)kLargeRows * sizeof(int) +
+               (size_t)kLargeRows * S;
+    }
+};
+
+template <int DSUB, typename XT, typename TT>
+__global__ void __launch_bounds__(kLargeThreads)
+encode_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const TT *__restrict__ tables,
+                    const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
+                    int recon_dtype, const __half *__restrict__ recon_tables, int B, int H, int T, int G, int S, int K,
+                    int64_t t0, int64_t T_cap) {
+    using L = LargeLayout<DSUB>;
+    constexpr int STR = L::kStride;
+    extern __shared__ __align__(16) float smem[];
+    float *res = smem;                      // [64][STR]
+    float *tab = res + L::kResFloats;       // [256][STR]
+    float *nrm = tab + L::kTabFloats;       // [256]
+    float *xxs = nrm + kMaxWords;           // [64]
+    int *pick = (int *)(xxs + kLargeRows);  // [64]
+    uint8_t *hist = (uint8_t *)(pick + kLargeRows);  // [64][S] codes chosen so far
+
+    const int hg = blockIdx.y;
+    const int h = hg / G, g = hg % G;
+    const int tid = threadIdx.x;
+    const int tx = tid & 15;   // codeword lane: owns words tx, tx+16, ...
+    const int ty = tid >> 4;   // row lane: owns rows 4*ty .. 4*ty+3
+    const int64_t rows = (int64_t)B * T;
+    const int64_t tile = (int64_t)blockIdx.x * kLargeRows;
+
+    for (int idx = tid; idx < kLargeRows * DSUB; idx += kLargeThreads) {
+        const int r = idx / DSUB, i = idx % DSUB;
+        const int64_t row = tile + r;
+        float v = 0.0f;
+        if (row < rows) {
+            const int64_t b = row / T, t = row % T;
+            v = to_float<XT>(x[b * sxb + (int64_t)h * sxh + t * sxt + (int64_t)g * DSUB + i]);
+        }
+        res[r * STR + i] = v;
+    }
+
+    for (int s = 0; s < S; ++s) {
+        __syncthreads();  // residual tile settled; previous stage's table no longer read
+        const TT *src = tables + (((int64_t)h * S + s) * G + g) * (int64_t)K * DSUB;
+        for (int idx = tid; idx < kMaxWords * DSUB; idx += kLargeThreads) {
+            const int k = idx / DSUB, i = idx % DSUB;
+            tab[k * STR + i] = (k < K) ? to_float<TT>(src[(int64_t)k * DSUB + i]) : 0.0f;
+        }
+        __syncthreads();
+        if (tid < kMaxWords) {
+            const float *row = tab + tid * STR;
+            float v;
+            if (tid >= K) v = __int_as_float(0x7f800000);  // padding words can never win
+            else if (sqnorm_in != nullptr) v = sqnorm_in[(((int64_t)h * S + s) * G + g) * K + tid];
+            else v = sqnorm_ordered_rt(row, DSUB);
+            nrm[tid] = v;
+        }
+        if (tid < kLargeRows) xxs[tid] = sqnorm_ordered_rt(res + tid * STR, DSUB);
+        __syncthreads();
+
+        float acc[4][16];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int w = 0; w < 16; ++w) acc[a][w] = 0.0f;
+
+#pragma unroll 1
+        for (int i = 0; i < DSUB; i += 4) {
+            float4 xv[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) xv[a] = *reinterpret_cast<const float4 *>(res + (ty * 4 + a) * STR + i);
+#pragma unroll
+            for (int w = 0; w < 16; ++w) {
+                const float4 cv = *reinterpret_cast<const float4 *>(tab + (tx + 16 * w) * STR + i);
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    float v = acc[a][w];
+                    v = __fmaf_rn(xv[a].x, cv.x, v);
+                    v = __fmaf_rn(xv[a].y, cv.y, v);
+                    v = __fmaf_rn(xv[a].z, cv.z, v);
+                    v = __fmaf_rn(xv[a].w, cv.w, v);
+                    acc[a][w] = v;
+                }
+            }
+        }
+
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const float xx = xxs[ty * 4 + a];
+            float best = __int_as_float(0x7f800000);
+            int arg = tx;
+#pragma unroll
+            for (int w = 0; w < 16; ++w) {
+                const int k = tx + 16 * w;
+                const float dist = distance_expr(xx, nrm[k], acc[a][w]);
+                if (dist < best) {
+                    best = dist;
+                    arg = k;
+                }
+            }
+            // lowest (distance, index) among the 16 codeword lanes of this row (a half warp)
+#pragma unroll
+            for (int off = 8; off >= 1; off >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
+                if (ob < best || (ob == best && oa < arg)) {
+                    best = ob;
+                    arg = oa;
+                }
+            }
+            if (tx == 0) pick[ty * 4 + a] = arg < K ? arg : 0;
+        }
+        __syncthreads();
+
+        for (int idx = tid; idx < kLargeRows * DSUB; idx += kLargeThreads) {
+            const int r = idx / DSUB, i = idx % DSUB;
+            res[r * STR + i] = __fsub_rn(res[r * STR + i], tab[pick[r] * STR + i]);
+        }
+        if (tid < kLargeRows) {
+            const int64_t row = tile + tid;
+            hist[tid * S + s] = (uint8_t)pick[tid];
+            if (row < rows) {
+                const int64_t b = row / T, t = row % T;
+                codes[((((int64_t)b * H + h) * T_cap + t0 + t) * S + s) * G + g] = (uint8_t)pick[tid];
+            }
+        }
+    }
+
+    if (recon != nullptr) {
+        __syncthreads();
+        const __half *plain = recon_tables;
+        for (int idx = tid; idx < kLargeRows * DSUB; idx += kLargeThreads) {
+            const int r = idx / DSUB, i = idx % DSUB;
+            const int64_t row = tile + r;
+            if (row >= rows) continue;
+            float sum = 0.0f;
+            for (int s = 0; s < S; ++s) {
+                const int code = hist[r * S + s];
+                sum = __fadd_rn(sum, __half2float(plain[((((int64_t)h * S + s) * G + g) * K + code) * DSUB + i]));
+            }
+            const int64_t b = row / T, t = row % T;
+            const int64_t o = (((int64_t)b * H + h) * T + t) * ((int64_t)G * DSUB) + (int64_t)g * DSUB + i;
+            if (recon_dtype == TACVQ_F16) store_as<__half>((__half *)recon + o, sum);
+            else store_as<float>((float *)recon + o, sum);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host-side dispatch
+// ------------------------------------------------------------------------------------------------
+
+template <int DSUB, int TPT, typename XT, typename TT>
+static int launch_small(const EncodeArgs &a) {
+    const size_t smem = ((size_t)a.S * a.K * DSUB + (size_t)a.S * a.K) * sizeof(float);
+    auto kernel = encode_small_kernel<DSUB, TPT, XT, TT>;
+    if (smem > 48 * 1024) {
+        if (smem > 227 * 1024) return TACVQ_ERR_UNSUPPORTED;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int64_t rows = (int64_t)a.B * a.T;
+    dim3 grid((unsigned)((rows + 128 * TPT - 1) / (128 * TPT)), (unsigned)(a.H * a.G));
+    // The search tables are the plain tables unless a whitened search is running.
+    const __half *plain = a.tables_f32 ? a.recon_tables : nullptr;
+    kernel<<<grid, 128, smem, a.stream>>>((const XT *)a.x, a.sxb, a.sxh, a.sxt, (const TT *)a.tables, a.sqnorm, a.codes,
+                                          a.recon, a.recon_dtype, plain, a.B, a.H, a.T, a.G, a.S, a.K, a.t0, a.T_cap);
+    return launch_status();
+}
+
+template <int DSUB, typename XT, typename TT>
+static int launch_large(const EncodeArgs &a) {
+    const size_t smem = LargeLayout<DSUB>::bytes(a.S);
+    auto kernel = encode_large_kernel<DSUB, XT, TT>;
+    if (smem > 227 * 1024) return TACVQ_ERR_UNSUPPORTED;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const int64_t rows = (int64_t)a.B * a.T;
+    dim3 grid((unsigned)((rows + kLargeRows - 1) / kLargeRows), (unsigned)(a.H * a.G));
+    kernel<<<grid, kLargeThreads, smem, a.stream>>>((const XT *)a.x, a.sxb, a.sxh, a.sxt, (const TT *)a.tables, a.sqnorm,
+                                                    a.codes, a.recon, a.recon_dtype, a.recon_tables, a.B, a.H, a.T, a.G,
+                                                    a.S, a.K, a.t0, a.T_cap);
+    return launch_status();
+}
+
+template <typename XT, typename TT>
+static int dispatch_d(const EncodeArgs &a) {
+    switch (a.D / a.G) {
+        case 1: return launch_small<1, 4, XT, TT>(a);
+        case 2: return launch_small<2, 4, XT, TT>(a);
+        case 3: return launch_small<3, 4, XT, TT>(a);
+        case 4: return launch_small<4, 4, XT, TT>(a);
+        case 5: return launch_small<5, 4, XT, TT>(a);
+        case 6: return launch_small<6, 4, XT, TT>(a);
+        case 7: return launch_small<7, 4, XT, TT>(a);
+        case 8: return launch_small<8, 4, XT, TT>(a);
+        case 16: return launch_small<16, 2, XT, TT>(a);
+        case 32: return launch_large<32, XT, TT>(a);
+        case 64: return launch_large<64, XT, TT>(a);
+        case 128: return launch_large<128, XT, TT>(a);
+        default: return TACVQ_ERR_UNSUPPORTED;
+    }
+}
+
+int encode_dispatch(const EncodeArgs &a) {
+    if (a.x_dtype == TACVQ_F16) {
+        return a.tables_f32 ? dispatch_d<__half, float>(a) : dispatch_d<__half, __half>(a);
+    }
+    return a.tables_f32 ? dispatch_d<float, float>(a) : dispatch_d<float, __half>(a);
+}
+
+}  // namespace tacvq

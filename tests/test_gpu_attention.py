@@ -1,0 +1,135 @@
+"""GPU parity of decode-step attention over codes (through the C ABI).
+
+Oracle: rebuild K and V from the codes as the reference does (fp32 stage sum,
+one cast to fp16), repeat KV heads, softmax(q K^T) V over the visible range.
+Tolerance (fp16 output): relative L2 error <= 2e-3 and max abs error <= 2e-3 of
+the largest reference magnitude.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import c_oracle as C
+from tests.util import make_tables, max_rel, rel_l2
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def _ops():
+    from tac_vq_kv_cache_b200 import ops
+
+    return ops
+
+
+def _workload(seed, b, hq, hkv, t, groups, stages, sub, scales=None):
+    gen = torch.Generator().manual_seed(seed)
+    dim = groups * sub
+    kcodes = torch.randint(0, 256, (b, hkv, t, stages, groups), generator=gen, dtype=torch.uint8)
+    vcodes = torch.randint(0, 256, (b, hkv, t, stages, groups), generator=gen, dtype=torch.uint8)
+    ktab = make_tables(gen, hkv, stages, groups, sub, scales)
+    vtab = make_tables(gen, hkv, stages, groups, sub, scales)
+    q = (torch.randn(b, hq, dim, generator=gen) / dim**0.5).half()
+    return q, kcodes, vcodes, ktab, vtab
+
+
+def _check(out, want):
+    assert rel_l2(out, want) <= TOL, (rel_l2(out, want), max_rel(out, want))
+    assert max_rel(out, want) <= TOL, (rel_l2(out, want), max_rel(out, want))
+
+
+def _run(device, work, start=None, end=None, **kw):
+    ops = _ops()
+    dev = [x.to(device) for x in work]
+    st = None if start is None else torch.tensor(start, dtype=torch.int32, device=device)
+    en = None if end is None else torch.tensor(end, dtype=torch.int32, device=device)
+    return ops.attn_decode(*dev, st, en, **kw)
+
+
+@pytest.mark.parametrize("case", ["gsrq", "cq"])
+def test_attention_matches_reference_golden(golden, device, case):
+    g = golden("attention.npz")
+    work = tuple(g(f"{case}.{n}") for n in ("q", "kcodes", "vcodes", "ktab", "vtab"))
+    out, _ = _run(device, work, g(f"{case}.seq_start").tolist(), g(f"{case}.seq_end").tolist())
+    _check(out, g(f"{case}.out"))
+
+
+@pytest.mark.parametrize("tokens", [1, 2, 31, 32, 33, 255, 257, 1000, 4097])
+def test_gsrq2_geometry_ragged_lengths(device, tokens):
+    work = _workload(tokens, 2, 8, 2, tokens, 16, 2, 8)
+    out, state = _run(device, work, want_state=True)
+    want, want_state = C.attention(*work)
+    _check(out, want)
+    torch.testing.assert_close(state[..., 0].cpu(), want_state[..., 0], rtol=0, atol=2e-3)  # row maxima
+    _check(state[..., 2:].cpu() / state[..., 1:2].cpu(), want_state[..., 2:] / want_state[..., 1:2])
+
+
+def test_sliding_window_and_empty_rows(device):
+    # 6144 stored tokens, the last 4096 visible (the reference's window), one row empty, one row partial
+    work = _workload(5, 4, 8, 2, 6144, 16, 2, 8)
+    start, end = [2048, 0, 100, 6000], [6144, 0, 4196, 6144]
+    out, state = _run(device, work, start, end, want_state=True)
+    want, want_state = C.attention(*work, start, end)
+    _check(out, want)
+    assert bool((out[1] == 0).all()) and bool((state[1, :, 1] == 0).all()) and bool(torch.isinf(state[1, :, 0]).all())
+
+
+@pytest.mark.parametrize(
+    "b,hq,hkv,t,groups,stages,sub",
+    [
+        (2, 8, 2, 700, 1, 2, 128),   # two additive full-width codebooks
+        (1, 8, 8, 300, 1, 16, 128),  # the reference's own GSRQ layout, depth 16, no query-head sharing
+        (2, 4, 2, 500, 16, 1, 8),    # one-stage grouped CQ
+        (1, 4, 1, 400, 32, 1, 4),    # 32 groups of 4
+        (2, 16, 2, 333, 8, 2, 8),    # 8 query heads per KV head, head_dim 64
+    ],
+)
+def test_other_geometries(device, b, hq, hkv, t, groups, stages, sub):
+    work = _workload(9, b, hq, hkv, t, groups, stages, sub, [0.1] * stages if sub == 128 else None)
+    out, _ = _run(device, work)
+    want, _ = C.attention(*work)
+    _check(out, want)
+
+
+def test_partial_states_merge_to_the_whole(device):
+    """Sequence split as ranks would do it: per-range states, then the log-sum-exp merge."""
+    ops = _ops()
+    work = _workload(13, 2, 8, 2, 3000, 16, 2, 8)
+    whole, _ = _run(device, work)
+    states = []
+    for lo, hi in ((0, 1000), (1000, 1000), (1000, 2200), (2200, 3000)):  # one empty range
+        _, st = _run(device, work, [lo, lo], [hi, hi], want_out=False, want_state=True)
+        states.append(st)
+    merged_out, merged_state = ops.attn_combine(torch.stack(states), want_state=True)
+    want, want_state = C.attention(*work)
+    _check(merged_out, want)
+    _check(whole, want)
+    torch.testing.assert_close(merged_state[..., 0].cpu(), want_state[..., 0], rtol=0, atol=2e-3)
+    c_out, _ = C.merge(torch.stack(states).cpu())
+    _check(merged_out, c_out)
+
+
+def test_benchmark_size_32k_context(device):
+    """Full benchmark shape: batch 8, 32 query / 8 KV heads, 32768 tokens, 2x16 code bytes per token."""
+    work = _workload(8601, 8, 32, 8, 32768, 16, 2, 8)
+    out, _ = _run(device, work)
+    want, _ = C.attention(*work)
+    _check(out, want)
+    again, _ = _run(device, work)
+    assert torch.equal(out, again)  # deterministic
+
+
+def test_attention_argument_errors(device):
+    from tac_vq_kv_cache_b200 import _lib
+
+    ops = _ops()
+    work = [x.to(device) for x in _workload(1, 1, 4, 1, 64, 16, 2, 8)]
+    with pytest.raises(_lib.TacvqError) as err:
+        ops.attn_decode(*work, workspace=torch.empty(256, dtype=torch.uint8, device=device))
+    assert err.value.status == -5
+    with pytest.raises(ValueError):
+        ops.attn_decode(work[0].float(), *work[1:])
+    with pytest.raises(ValueError):
+        ops.attn_decode(work[0][:, :3].contiguous(), *work[1:])  # 3 query heads over 1 KV head is fine? no: rep=3 unsupported

@@ -1,0 +1,228 @@
+"""GPU parity of encode / decode (through the C ABI) against the golden vectors and the oracles.
+
+Bar: codes bit-exact; reconstruction bit-exact; any differing code must be a
+near tie (fp64 margin <= 4 fp32 ulp of the distance expression) and is counted.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import pytest
+import torch
+
+from oracle import c_oracle as C
+from oracle import jointkv_oracle as O
+from tests.util import make_states, make_tables
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from tac_vq_kv_cache_b200 import ops
+
+    return ops
+
+
+def _assert_codes(states, tables, got, want):
+    report = O.code_mismatch_report(states.cpu(), tables.float().cpu(), got.cpu(), want.cpu())
+    assert report["errors"] == 0, report
+    assert report["differing_codes"] <= max(2, report["total"] // 50000), report
+    return report
+
+
+@pytest.mark.parametrize("case", ["g16s1", "g16s2", "g1s2", "g32s1", "g1s4_t1"])
+def test_encode_matches_reference_golden(golden, device, case):
+    ops = _ops()
+    g = golden("encode.npz")
+    states, tables = g(f"{case}.states"), g(f"{case}.tables")
+    codes, recon = ops.encode(states.to(device), tables.to(device))
+    want_codes, want_recon = g(f"{case}.codes"), g(f"{case}.recon")
+    report = _assert_codes(states, tables, codes, want_codes)
+    if report["differing_codes"] == 0:
+        assert torch.equal(recon.cpu(), want_recon)
+    assert torch.equal(ops.decode(want_codes.to(device), tables.to(device), states.dtype).cpu(), want_recon)
+
+
+def test_stage_prefix_decode_matches_reference(golden, device):
+    ops = _ops()
+    g = golden("encode.npz")
+    got = ops.decode(g("g16s2.codes").to(device), g("g16s2.tables").to(device), torch.float16, depth=1)
+    assert torch.equal(got.cpu(), g("g16s2.recon_depth1"))
+
+
+@pytest.mark.parametrize("case,prefixes", [("seed7", (1, 2, 3)), ("seed9", (1, 2, 3)), ("seed10", (3,)), ("seed41", (1, 2, 3)), ("seed53", (1, 2, 3))])
+def test_reference_unit_test_cases_through_the_drop_in_api(golden, device, case, prefixes):
+    """Shapes/seeds of the reference's own tests (K in {4,8}, D=4, identity and random whiteners)."""
+    from tac_vq_kv_cache_b200.jointkv.closed_loop_vq import hard_residual_vq_exits
+
+    g = golden("reftests.npz")
+    w = g(f"{case}.whitener").to(device) if g.has(f"{case}.whitener") else None
+    exits, codes = hard_residual_vq_exits(
+        g(f"{case}.states").to(device), g(f"{case}.tables").to(device), prefixes=prefixes, assignment_whiteners=w,
+        token_chunk_size=g.int(f"{case}.chunk"), straight_through_states=False,
+    )
+    assert torch.equal(codes.cpu(), g(f"{case}.codes"))
+    for depth in prefixes:
+        assert torch.equal(exits[depth].cpu(), g(f"{case}.exit{depth}"))
+
+
+def test_modules_match_reference_golden(golden, device):
+    from tac_vq_kv_cache_b200.jointkv.cq_tac import ClosedLoopGroupedCQ
+    from tac_vq_kv_cache_b200.jointkv.uniform_depth_tac import ClosedLoopUniformResidualVQ
+
+    g = golden("modules.npz")
+    kt, vt = g("uni.key_tables"), g("uni.value_tables")
+    codec = ClosedLoopUniformResidualVQ(list(kt), list(vt), [None, None], depth=2, dynamic_bpa=0.5).to(device)
+    with torch.no_grad():
+        q = codec(1, g("uni.k").to(device), g("uni.v").to(device), mode="uniform")
+    for name in ("key", "value", "key_indices", "value_indices"):
+        assert torch.equal(getattr(q, name).cpu(), g(f"uni.{name}")), name
+    assert q.projected_depths is None
+    with pytest.raises(ValueError):
+        codec(0, g("uni.k").to(device), g("uni.v").to(device), mode="mixed")
+    kc, vc = g("cq.key_tables"), g("cq.value_tables")
+    eye = [torch.eye(8).repeat(2, 4, 1, 1) for _ in range(2)]
+    codec = ClosedLoopGroupedCQ(list(kc), list(vc), eye, dynamic_bpa=1.0).to(device)
+    with torch.no_grad():
+        q = codec(0, g("cq.k").to(device), g("cq.v").to(device), mode="uniform")
+    for name in ("key", "value", "key_indices", "value_indices"):
+        assert torch.equal(getattr(q, name).cpu(), g(f"cq.{name}")), name
+
+
+def test_gradients_match_reference_golden(golden, device):
+    from tac_vq_kv_cache_b200.jointkv.closed_loop_vq import hard_residual_vq_exits
+    from tac_vq_kv_cache_b200.jointkv.cq_tac import hard_grouped_cq
+
+    g = golden("grads.npz")
+    states = g("rvq.states").to(device).requires_grad_()
+    tables = g("rvq.tables").to(device).requires_grad_()
+    weight = g("rvq.weight").to(device)
+    exits, codes = hard_residual_vq_exits(states, tables, prefixes=(2, 3))
+    assert torch.equal(codes.cpu(), g("rvq.codes"))
+    assert torch.equal(exits[3].detach().cpu(), g("rvq.exit3"))
+    ((exits[3] * weight).sum() + (exits[2] * weight.flip(-1)).sum()).backward()
+    torch.testing.assert_close(states.grad.cpu(), g("rvq.grad_states"), rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(tables.grad.cpu(), g("rvq.grad_tables"), rtol=1e-5, atol=1e-5)
+
+    states = g("cq.states").to(device).requires_grad_()
+    books = g("cq.tables").to(device).requires_grad_()
+    recon, codes = hard_grouped_cq(states, books)
+    assert torch.equal(codes.cpu(), g("cq.codes"))
+    assert torch.equal(recon.detach().cpu(), g("cq.recon"))
+    (recon * g("cq.weight").to(device)).sum().backward()
+    torch.testing.assert_close(states.grad.cpu(), g("cq.grad_states"), rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(books.grad.cpu(), g("cq.grad_tables"), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize(
+    "name,shape,dtype,stages,groups,outliers",
+    [
+        ("gsrq1_cpu_config", (1, 8, 2048, 128), torch.float32, 1, 16, 0),
+        ("gsrq2_layer_reduced", (2, 8, 1024, 128), torch.float16, 2, 16, 4),
+        ("cq_additive_reduced", (2, 8, 512, 128), torch.float16, 2, 1, 0),
+        ("reference_gsrq_depth16", (1, 2, 192, 128), torch.float16, 16, 1, 0),
+        ("grouped_d4", (1, 4, 300, 128), torch.float32, 1, 32, 0),
+        ("d16", (1, 2, 130, 64), torch.float16, 2, 4, 0),
+        ("d32", (1, 2, 70, 64), torch.float32, 3, 2, 0),
+        ("d64", (1, 2, 65, 64), torch.float16, 2, 1, 0),
+    ],
+)
+def test_encode_is_bit_exact_with_the_c_oracle(device, name, shape, dtype, stages, groups, outliers):
+    ops = _ops()
+    gen = torch.Generator().manual_seed(8601)
+    states = make_states(gen, shape, dtype, outliers)
+    sub = shape[-1] // groups
+    scales = [0.1] * stages if sub == 128 else None
+    tables = make_tables(gen, shape[1], stages, groups, sub, scales)
+    want_codes, want_recon = C.encode(states, tables)
+    codes, recon = ops.encode(states.to(device), tables.to(device))
+    assert torch.equal(codes.cpu(), want_codes), int((codes.cpu() != want_codes).sum())
+    assert torch.equal(recon.cpu(), want_recon)
+    again, _ = ops.encode(states.to(device), tables.to(device), want_recon=False)
+    assert torch.equal(again, codes)  # run-to-run determinism
+    if name == "gsrq1_cpu_config":  # also against the torch restatement of the reference
+        ref_recon, ref_codes = O.grouped_cq_encode(states, tables[:, 0].float())
+        _assert_codes(states, tables, codes[:, :, :, 0], ref_codes)
+        assert torch.equal(recon.cpu(), ref_recon)
+
+
+@pytest.mark.parametrize("tokens", [0, 1, 31, 33, 127, 129, 513])
+def test_ragged_token_counts_and_in_place_append(device, tokens):
+    ops = _ops()
+    gen = torch.Generator().manual_seed(tokens + 1)
+    tables = make_tables(gen, 2, 2, 16, 8)
+    states = make_states(gen, (2, 2, tokens, 128))
+    cache = torch.full((2, 2, tokens + 7, 2, 16), 0xAB, dtype=torch.uint8, device=device)
+    ops.encode(states.to(device), tables.to(device), codes=cache, t0=5, want_recon=False)
+    want, _ = C.encode(states, tables, want_recon=False)
+    assert torch.equal(cache[:, :, 5 : 5 + tokens].cpu(), want)
+    assert bool((cache[:, :, :5] == 0xAB).all()) and bool((cache[:, :, 5 + tokens :] == 0xAB).all())
+    if tokens:
+        back = ops.decode(cache, tables.to(device), torch.float16, t0=5, tokens=tokens)
+        assert torch.equal(back.cpu(), C.decode(want, tables, torch.float16))
+
+
+def test_strided_states_and_small_codebooks(device):
+    ops = _ops()
+    gen = torch.Generator().manual_seed(3)
+    # [B,T,H,D] projection output viewed as [B,H,T,D] (what an attention adapter hands over)
+    raw = make_states(gen, (2, 50, 4, 128))
+    view = raw.transpose(1, 2)
+    tables = make_tables(gen, 4, 1, 16, 8)
+    want, want_recon = C.encode(view.contiguous(), tables)
+    strided = raw.to(device).transpose(1, 2)  # strides (T*H*D, D, H*D, 1): used in place, no copy
+    assert not strided.is_contiguous()
+    codes, recon = ops.encode(strided, tables.to(device))
+    assert torch.equal(codes.cpu(), want) and torch.equal(recon.cpu(), want_recon)
+    small = tables[:, :, :, :37].contiguous()  # K = 37 codewords
+    want, want_recon = C.encode(view.contiguous(), small)
+    codes, recon = ops.encode(view.contiguous().to(device), small.to(device))
+    assert torch.equal(codes.cpu(), want) and torch.equal(recon.cpu(), want_recon)
+    assert int(codes.max()) < 37
+
+
+def test_caller_supplied_table_norms_and_own_norm_kernel(device):
+    ops = _ops()
+    gen = torch.Generator().manual_seed(11)
+    for sub, groups in ((8, 16), (128, 1), (16, 8), (4, 32)):
+        tables = make_tables(gen, 2, 2, groups, sub)
+        norms = ops.table_sqnorm(tables.to(device))
+        assert torch.equal(norms.cpu(), C.table_sqnorm(tables))
+        assert torch.equal(norms.cpu(), tables.float().square().sum(-1)) or sub not in (4, 8)
+        states = make_states(gen, (1, 2, 40, groups * sub))
+        a, _ = ops.encode(states.to(device), tables.to(device), want_recon=False)
+        b, _ = ops.encode(states.to(device), tables.to(device), want_recon=False, table_sqnorm=norms)
+        assert torch.equal(a, b)
+
+
+def test_argument_errors_are_reported_before_any_launch(device):
+    from tac_vq_kv_cache_b200 import _lib
+    from tac_vq_kv_cache_b200.jointkv.closed_loop_vq import hard_residual_vq_exits
+    from tac_vq_kv_cache_b200.jointkv.cq_tac import hard_grouped_cq
+
+    lib = _lib.load()
+    x = torch.zeros(1, 1, 4, 128, dtype=torch.float16, device=device)
+    tab = torch.zeros(1, 1, 16, 256, 8, dtype=torch.float16, device=device)
+    codes = torch.zeros(1, 1, 4, 1, 16, dtype=torch.uint8, device=device)
+    null = ctypes.c_void_p(0)
+    args = lambda **kw: [kw.get("x", x.data_ptr()), kw.get("dt", 0), 512, 512, 128, tab.data_ptr(), null, kw.get("codes", codes.data_ptr()), null, 0,
+                         1, 1, kw.get("T", 4), kw.get("D", 128), kw.get("G", 16), 1, kw.get("K", 256), kw.get("t0", 0), 4, null]
+    assert lib.tacvq_encode(*args()) == 0
+    assert lib.tacvq_encode(*args(x=null)) == -1
+    assert lib.tacvq_encode(*args(dt=7)) == -3
+    assert lib.tacvq_encode(*args(G=3)) == -2
+    assert lib.tacvq_encode(*args(K=300)) == -2
+    assert lib.tacvq_encode(*args(t0=2)) == -4
+    assert lib.tacvq_encode(*args(D=144, G=16)) == -6  # d = 9 has no kernel
+    assert b"NULL" in lib.tacvq_status_string(-1)
+    torch.cuda.synchronize()
+    with pytest.raises(ValueError):
+        hard_grouped_cq(x, torch.zeros(1, 16, 256, 4, device=device))
+    with pytest.raises(ValueError):
+        hard_residual_vq_exits(x, torch.zeros(1, 2, 256, 128, device=device), prefixes=(3,))
+    with pytest.raises(NotImplementedError):
+        hard_residual_vq_exits(x, torch.zeros(1, 2, 256, 128, device=device), prefixes=(2,), soft_backward_topk=4,
+                               soft_backward_temperature=1.0, soft_backward_beta=0.5)
+    with pytest.raises(RuntimeError):
+        hard_grouped_cq(x.cpu(), torch.zeros(1, 16, 256, 8))
