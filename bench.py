@@ -185,7 +185,8 @@ def run_ours(args) -> dict:
     e2e = None
     encode = None
     cpu = None
-    if rank == 0 or world > 1:
+    extras = not args.kernel_only
+    if extras and (rank == 0 or world > 1):
         e2e_steps = max(10, min(args.steps, 100))
         cache = VQCodeCache(ktab, vtab, batch=BATCH, max_tokens=CONTEXT + e2e_steps + args.warmup + 8, device=device)
         cache.key[:, :, :CONTEXT].copy_(code_sets[0][0])
@@ -224,7 +225,7 @@ def run_ours(args) -> dict:
         }
         del cache
 
-    if rank == 0:
+    if extras and rank == 0:
         # ---- encode throughput: one 2-stage layer, K (with outlier channels) and V ------------
         egen = torch.Generator().manual_seed(8601)
         k_rows = torch.randn(4, KV_HEADS, 8192, DIM, generator=egen)
@@ -382,6 +383,7 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--kernel-only", action="store_true", help="time the decode-attention launches only (used for profiler captures)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
     result = run_reference(args) if args.impl == "reference" else run_ours(args)

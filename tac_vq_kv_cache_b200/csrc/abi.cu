@@ -84,13 +84,13 @@ int tacvq_table_sqnorm(const uint16_t *tables_f16, float *out, int64_t words, in
 int tacvq_encode(const void *x, int x_dtype, int64_t sxb, int64_t sxh, int64_t sxt, const uint16_t *tables_f16,
                  const float *table_sqnorm, uint8_t *codes, void *recon, int recon_dtype, int B, int H, int T, int D,
                  int G, int S, int K, int64_t t0, int64_t T_cap, tacvq_stream_t stream) {
-    if (!x || !tables_f16 || !codes) return TACVQ_ERR_NULL;
     if (!dtype_ok(x_dtype) || (recon && !dtype_ok(recon_dtype))) return TACVQ_ERR_DTYPE;
     const int g = check_code_geometry(B, H, T, D, G, S, K, t0, T_cap);
     if (g != TACVQ_OK) return g;
     if (!sub_dim_ok(D / G)) return TACVQ_ERR_UNSUPPORTED;
+    if ((int64_t)B * T == 0) return TACVQ_OK;  // nothing to encode: pointers of empty tensors may be NULL
+    if (!x || !tables_f16 || !codes) return TACVQ_ERR_NULL;
     if (sxb < 0 || sxh < 0 || sxt < D) return TACVQ_ERR_GEOMETRY;
-    if ((int64_t)B * T == 0) return TACVQ_OK;
     EncodeArgs a{x, x_dtype, sxb, sxh, sxt, tables_f16, false, table_sqnorm, codes, recon, recon_dtype,
                  (const __half *)tables_f16, B, H, T, D, G, S, K, t0, T_cap, (cudaStream_t)stream};
     return encode_dispatch(a);
@@ -100,13 +100,13 @@ int tacvq_encode_whitened(const void *x, int x_dtype, int64_t sxb, int64_t sxh, 
                           const uint16_t *tables_f16, const float *whitener, float *search_tables,
                           float *search_rows, uint8_t *codes, void *recon, int recon_dtype, int B, int H, int T, int D,
                           int G, int S, int K, int64_t t0, int64_t T_cap, tacvq_stream_t stream) {
-    if (!x || !tables_f16 || !codes || !whitener || !search_tables || !search_rows) return TACVQ_ERR_NULL;
     if (!dtype_ok(x_dtype) || (recon && !dtype_ok(recon_dtype))) return TACVQ_ERR_DTYPE;
     const int g = check_code_geometry(B, H, T, D, G, S, K, t0, T_cap);
     if (g != TACVQ_OK) return g;
     if (!sub_dim_ok(D / G)) return TACVQ_ERR_UNSUPPORTED;
-    if (sxb < 0 || sxh < 0 || sxt < D) return TACVQ_ERR_GEOMETRY;
     if ((int64_t)B * T == 0) return TACVQ_OK;
+    if (!x || !tables_f16 || !codes || !whitener || !search_tables || !search_rows) return TACVQ_ERR_NULL;
+    if (sxb < 0 || sxh < 0 || sxt < D) return TACVQ_ERR_GEOMETRY;
     int st = whiten_dispatch(x, x_dtype, sxb, sxh, sxt, (const __half *)tables_f16, whitener, search_tables,
                              search_rows, B, H, T, D, G, S, K, (cudaStream_t)stream);
     if (st != TACVQ_OK) return st;
@@ -118,11 +118,12 @@ int tacvq_encode_whitened(const void *x, int x_dtype, int64_t sxb, int64_t sxh, 
 
 int tacvq_decode(const uint8_t *codes, const uint16_t *tables_f16, void *out, int out_dtype, int B, int H, int T,
                  int D, int G, int S, int S_use, int K, int64_t t0, int64_t T_cap, tacvq_stream_t stream) {
-    if (!codes || !tables_f16 || !out) return TACVQ_ERR_NULL;
     if (!dtype_ok(out_dtype)) return TACVQ_ERR_DTYPE;
     const int g = check_code_geometry(B, H, T, D, G, S, K, t0, T_cap);
     if (g != TACVQ_OK) return g;
     if (S_use < 0 || S_use > S) return TACVQ_ERR_GEOMETRY;
+    if ((int64_t)B * T == 0) return TACVQ_OK;
+    if (!codes || !tables_f16 || !out) return TACVQ_ERR_NULL;
     return decode_dispatch(codes, (const __half *)tables_f16, out, out_dtype, B, H, T, D, G, S, S_use, K, t0, T_cap,
                            (cudaStream_t)stream);
 }
