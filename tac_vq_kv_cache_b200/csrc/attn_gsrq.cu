@@ -41,7 +41,10 @@ namespace tacvq {
 
 namespace gsrq {
 
-constexpr int kThreads = 512;
+#ifndef TACVQ_GSRQ_THREADS
+#define TACVQ_GSRQ_THREADS 512
+#endif
+constexpr int kThreads = TACVQ_GSRQ_THREADS;
 constexpr int kWarps = kThreads / 32;
 constexpr int kDim = 128, kGroups = 16, kStages = 2, kSub = 8, kRep = 4, kSlots = 32, kWords = 256;
 constexpr int kTile = 32;          // tokens per warp tile
@@ -55,7 +58,9 @@ constexpr int kEntryMax = 8191;      // 13-bit fields: 8 of them sum below 2^16
 // shared-memory carve-up (bytes)
 constexpr int kLutBytes = kWords * kSlots * 8;              // 65536
 constexpr int kVtabBytes = kWords * kSlots * 16;            // 131072
-constexpr int kStagePerWarp = 1024 + 256;                   // transposed V codes + fp16 probabilities
+constexpr int kVBlock = 144;                                // 32 words + 16 B pad: staggers the banks of odd/even tokens
+constexpr int kVStage = 8 * kVBlock;                        // 1152
+constexpr int kStagePerWarp = kVStage + 256;                // transposed V codes + fp16 probabilities
 constexpr int kStageBytes = kWarps * kStagePerWarp;         // 20480 (also min/max scratch of the table build)
 constexpr int kQBytes = kRep * kDim * 4;                    // 2048
 constexpr int kPrefixBytes = (kMaxBatch + 1) * 4 + 12;      // 2064
@@ -110,6 +115,13 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void mma1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0));
 }
 
 // Tiles of batch row b and the running totals, shared by the scan and the merge kernel.
@@ -194,8 +206,8 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
     const uint32_t lut_base = smem_u32(lut_s);
     unsigned char *my_stage = stage_s + warp * kStagePerWarp;
     const uint32_t vstage_u32 = smem_u32(my_stage);
-    const uint32_t pstage_u32 = vstage_u32 + 1024;
-    __half *pstage = reinterpret_cast<__half *>(my_stage + 1024);
+    const uint32_t pstage_u32 = vstage_u32 + kVStage;
+    __half *pstage = reinterpret_cast<__half *>(my_stage + kVStage);
 
     int loaded_head = -1;
 
@@ -247,14 +259,14 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
             for (int r = 0; r < kRep; ++r)
 #pragma unroll
                 for (int i = 0; i < kSub; ++i) qv[r][i] = q_s[r * kDim + g * kSub + i];
-            float val[16][kRep];
             float mn[kRep], mx[kRep];
 #pragma unroll
             for (int r = 0; r < kRep; ++r) { mn[r] = INFINITY; mx[r] = -INFINITY; }
-            const __half *tab = ktab + ((((size_t)h * kStages + s) * kGroups + g) * kWords + warp * 16) * kSub;
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(tab + c * kSub));
+            const __half *tab = ktab + ((((size_t)h * kStages + s) * kGroups + g) * kWords ) * kSub;
+            // the four partial scores of codeword c of this lane's slot (computed twice: once for the
+            // value range, once to quantise - cheaper than keeping 64 values in registers)
+            auto dots = [&](int c, float (&out)[kRep]) {
+                const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(tab + (size_t)c * kSub));
                 const __half2 *hp = reinterpret_cast<const __half2 *>(&raw);
                 float w[kSub];
 #pragma unroll
@@ -268,9 +280,17 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
                     float dot = 0.0f;
 #pragma unroll
                     for (int i = 0; i < kSub; ++i) dot = fmaf(qv[r][i], w[i], dot);
-                    val[c][r] = dot;
-                    mn[r] = fminf(mn[r], dot);
-                    mx[r] = fmaxf(mx[r], dot);
+                    out[r] = dot;
+                }
+            };
+#pragma unroll 4
+            for (int c = warp; c < kWords; c += kWarps) {  // codes dealt round-robin to the warps
+                float d4[kRep];
+                dots(c, d4);
+#pragma unroll
+                for (int r = 0; r < kRep; ++r) {
+                    mn[r] = fminf(mn[r], d4[r]);
+                    mx[r] = fmaxf(mx[r], d4[r]);
                 }
             }
             float *red = reinterpret_cast<float *>(stage_s);  // [warp][slot][8]
@@ -304,16 +324,18 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
                 step_l2[r] = step * kLog2e;
                 offs_l2[r] = offs * kLog2e;
             }
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
+#pragma unroll 4
+            for (int c = warp; c < kWords; c += kWarps) {
+                float d4[kRep];
+                dots(c, d4);
                 uint32_t e[kRep];
 #pragma unroll
                 for (int r = 0; r < kRep; ++r)
-                    e[r] = min((uint32_t)kEntryMax, __float2uint_rn((val[c][r] - mn[r]) * inv_step[r]));
+                    e[r] = min((uint32_t)kEntryMax, __float2uint_rn((d4[r] - mn[r]) * inv_step[r]));
                 uint2 packed;
                 packed.x = e[0] | (e[1] << 16);
                 packed.y = e[2] | (e[3] << 16);
-                *reinterpret_cast<uint2 *>(lut_s + (size_t)(warp * 16 + c) * 256 + slot * 8) = packed;
+                *reinterpret_cast<uint2 *>(lut_s + (size_t)c * 256 + slot * 8) = packed;
             }
         }
         cp_async_wait_all();
@@ -331,19 +353,23 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
 
         const size_t row_base = ((size_t)b * Hkv + h) * (size_t)T_cap;
 
-        for (int tile = tile_lo + warp; tile < tile_hi; tile += kWarps) {
-            const int tok = tile * kTile + lane;             // index inside the visible range
-            const bool live = tok < n_tokens;
-            const size_t tok_abs = row_base + (size_t)(tok_lo_row + (live ? tok : n_tokens - 1));
-            const uint4 *kp = reinterpret_cast<const uint4 *>(kcodes + tok_abs * 32);
-            const uint4 *vp = reinterpret_cast<const uint4 *>(vcodes + tok_abs * 32);
-            const uint4 k0 = ldg_stream(kp), k1 = ldg_stream(kp + 1);
-            const uint4 v0 = ldg_stream(vp), v1 = ldg_stream(vp + 1);
-            if (tile + 2 * kWarps < tile_hi) {  // warm L2 two rounds ahead
-                prefetch_l2(reinterpret_cast<const unsigned char *>(kp) + (size_t)2 * kWarps * kTile * 32);
-                prefetch_l2(reinterpret_cast<const unsigned char *>(vp) + (size_t)2 * kWarps * kTile * 32);
-            }
+        // codes of a tile: lane = token; rows past the end of the range re-read the last valid row
+        auto code_ptrs = [&](int tile, const uint4 *&kp, const uint4 *&vp) {
+            const int tok = tile * kTile + lane;
+            const size_t tok_abs = row_base + (size_t)(tok_lo_row + min(tok, n_tokens - 1));
+            kp = reinterpret_cast<const uint4 *>(kcodes + tok_abs * 32);
+            vp = reinterpret_cast<const uint4 *>(vcodes + tok_abs * 32);
+        };
+        uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0, v0 = k0, v1 = k0;
+        if (tile_lo + warp < tile_hi) {
+            const uint4 *kp, *vp;
+            code_ptrs(tile_lo + warp, kp, vp);
+            k0 = ldg_stream(kp); k1 = ldg_stream(kp + 1);
+            v0 = ldg_stream(vp); v1 = ldg_stream(vp + 1);
+        }
 
+        for (int tile = tile_lo + warp; tile < tile_hi; tile += kWarps) {
+            const bool live = tile * kTile + lane < n_tokens;
             // -- value codes: byte transpose so that word r holds this token's 4 codes of groups r, r+8
             {
                 const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
@@ -358,13 +384,23 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
                     tw[half * 4 + 3] = prmt(t1, t3, 0x7632u);
                 }
                 __syncwarp();  // previous tile's readers are done with the staging area
-                unsigned char *dst = my_stage + (((lane >> 3) * 2 + (lane & 1)) * 128) + (((lane >> 1) & 3) * 32);
+                unsigned char *dst = my_stage + (((lane >> 3) * 2 + (lane & 1)) * kVBlock) + (((lane >> 1) & 3) * 32);
                 *reinterpret_cast<uint4 *>(dst) = make_uint4(tw[0], tw[1], tw[2], tw[3]);
                 *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(tw[4], tw[5], tw[6], tw[7]);
             }
 
             // -- scores: 32 look-ups of 8 bytes, four 13-bit fields each, flushed every 8 look-ups
             uint32_t kw[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+            if (tile + kWarps < tile_hi) {  // next tile's codes travel while this tile is computed
+                const uint4 *kp, *vp;
+                code_ptrs(tile + kWarps, kp, vp);
+                k0 = ldg_stream(kp); k1 = ldg_stream(kp + 1);
+                v0 = ldg_stream(vp); v1 = ldg_stream(vp + 1);
+                if (tile + 3 * kWarps < tile_hi) {  // and warm L2 two more rounds ahead
+                    prefetch_l2(reinterpret_cast<const unsigned char *>(kp) + (size_t)2 * kWarps * kTile * 32);
+                    prefetch_l2(reinterpret_cast<const unsigned char *>(vp) + (size_t)2 * kWarps * kTile * 32);
+                }
+            }
             if (k_word_swap & 1) {
 #pragma unroll
                 for (int i = 0; i < 8; i += 2) { const uint32_t t = kw[i]; kw[i] = kw[i + 1]; kw[i + 1] = t; }
@@ -435,46 +471,32 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
             }
             __syncwarp();
 
-            // -- values: gather codewords, add the two stages, pair tokens, 8 MMAs per 16 tokens
+            // -- values: per 8-token step gather this lane's two tokens (4 codewords each), add the two
+            //    stages, pair the tokens into A fragments and issue 8 m16n8k8 products
 #pragma unroll
-            for (int kt = 0; kt < 2; ++kt) {
-                uint32_t cw[4];
+            for (int ks = 0; ks < 4; ++ks) {
+                uint32_t b0 = 0u;
+                if (b_valid) b0 = lds32(pstage_u32 + (uint32_t)(b_head * kTile * 2 + (ks * 4 + kq) * 4));
+                uint4 sa[2], sb[2];
 #pragma unroll
-                for (int j = 0; j < 4; ++j)  // tokens 2kq, 2kq+1, 2kq+8, 2kq+9 of this 16-token half
-                    cw[j] = lds32(vstage_u32 + (uint32_t)(((kt * 2 + (j >> 1)) * 2 + (j & 1)) * 128 + kq * 32 + r8 * 4));
-                uint32_t b0 = 0u, b1 = 0u;
-                if (b_valid) {
-                    b0 = lds32(pstage_u32 + (uint32_t)(b_head * kTile * 2 + (kt * 8 + kq) * 4));
-                    b1 = lds32(pstage_u32 + (uint32_t)(b_head * kTile * 2 + (kt * 8 + kq + 4) * 4));
-                }
-                uint32_t afrag[8][4];
+                for (int tk = 0; tk < 2; ++tk) {
+                    const uint32_t word = lds32(vstage_u32 + (uint32_t)((ks * 2 + tk) * kVBlock + kq * 32 + r8 * 4));
+                    uint4 gth[4];
 #pragma unroll
-                for (int pr = 0; pr < 2; ++pr) {
-                    uint4 sa[2], sb[2];
-#pragma unroll
-                    for (int tk = 0; tk < 2; ++tk) {
-                        const uint32_t word = cw[pr * 2 + tk];
-                        uint4 gth[4];
-#pragma unroll
-                        for (int st = 0; st < 4; ++st) {
-                            const uint32_t code256 = prmt(word, 0u, v_sel[st]);
-                            gth[st] = lds128(v_off[st] + code256 + code256);
-                        }
-                        sa[tk] = make_uint4(hadd2(gth[0].x, gth[1].x), hadd2(gth[0].y, gth[1].y), hadd2(gth[0].z, gth[1].z), hadd2(gth[0].w, gth[1].w));
-                        sb[tk] = make_uint4(hadd2(gth[2].x, gth[3].x), hadd2(gth[2].y, gth[3].y), hadd2(gth[2].z, gth[3].z), hadd2(gth[2].w, gth[3].w));
+                    for (int st = 0; st < 4; ++st) {
+                        const uint32_t code256 = prmt(word, 0u, v_sel[st]);
+                        gth[st] = lds128(v_off[st] + code256 + code256);
                     }
-                    const uint32_t a0[4] = {sa[0].x, sa[0].y, sa[0].z, sa[0].w}, a1[4] = {sa[1].x, sa[1].y, sa[1].z, sa[1].w};
-                    const uint32_t c0[4] = {sb[0].x, sb[0].y, sb[0].z, sb[0].w}, c1[4] = {sb[1].x, sb[1].y, sb[1].z, sb[1].w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        afrag[2 * i][pr * 2 + 0] = prmt(a0[i], a1[i], 0x5410u);
-                        afrag[2 * i + 1][pr * 2 + 0] = prmt(a0[i], a1[i], 0x7632u);
-                        afrag[2 * i][pr * 2 + 1] = prmt(c0[i], c1[i], 0x5410u);
-                        afrag[2 * i + 1][pr * 2 + 1] = prmt(c0[i], c1[i], 0x7632u);
-                    }
+                    sa[tk] = make_uint4(hadd2(gth[0].x, gth[1].x), hadd2(gth[0].y, gth[1].y), hadd2(gth[0].z, gth[1].z), hadd2(gth[0].w, gth[1].w));
+                    sb[tk] = make_uint4(hadd2(gth[2].x, gth[3].x), hadd2(gth[2].y, gth[3].y), hadd2(gth[2].z, gth[3].z), hadd2(gth[2].w, gth[3].w));
                 }
+                const uint32_t a0[4] = {sa[0].x, sa[0].y, sa[0].z, sa[0].w}, a1[4] = {sa[1].x, sa[1].y, sa[1].z, sa[1].w};
+                const uint32_t c0[4] = {sb[0].x, sb[0].y, sb[0].z, sb[0].w}, c1[4] = {sb[1].x, sb[1].y, sb[1].z, sb[1].w};
 #pragma unroll
-                for (int mm = 0; mm < 8; ++mm) mma16816(acc[mm], afrag[mm], b0, b1);
+                for (int i = 0; i < 4; ++i) {
+                    mma1688(acc[2 * i], prmt(a0[i], a1[i], 0x5410u), prmt(c0[i], c1[i], 0x5410u), b0);
+                    mma1688(acc[2 * i + 1], prmt(a0[i], a1[i], 0x7632u), prmt(c0[i], c1[i], 0x7632u), b0);
+                }
             }
         }
 
@@ -502,6 +524,7 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
         {
             // column n = 2kq (+1): head n&3, class n>>2 = x_class; rows 0-7 hold group r8+8*x_class, rows 8-15 the other
             const int h0 = (2 * kq) & 3, h1 = h0 + 1;
+            const float fin0 = (kq & 1) ? fin[2] : fin[0], fin1 = (kq & 1) ? fin[3] : fin[1];
             const int g_lo = r8 + 8 * x_class, g_hi = r8 + 8 * (1 - x_class);
             float *base = wacc + (size_t)warp * kRep * kDim;
 #pragma unroll
@@ -511,15 +534,15 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
                     for (int mm = 0; mm < 8; ++mm) {
                         float *p0 = base + h0 * kDim, *p1 = base + h1 * kDim;
                         if (pass == 0) {
-                            p0[g_lo * 8 + mm] = acc[mm][0] * fin[h0];
-                            p1[g_lo * 8 + mm] = acc[mm][1] * fin[h1];
-                            p0[g_hi * 8 + mm] = acc[mm][2] * fin[h0];
-                            p1[g_hi * 8 + mm] = acc[mm][3] * fin[h1];
+                            p0[g_lo * 8 + mm] = acc[mm][0] * fin0;
+                            p1[g_lo * 8 + mm] = acc[mm][1] * fin1;
+                            p0[g_hi * 8 + mm] = acc[mm][2] * fin0;
+                            p1[g_hi * 8 + mm] = acc[mm][3] * fin1;
                         } else {
-                            p0[g_lo * 8 + mm] += acc[mm][0] * fin[h0];
-                            p1[g_lo * 8 + mm] += acc[mm][1] * fin[h1];
-                            p0[g_hi * 8 + mm] += acc[mm][2] * fin[h0];
-                            p1[g_hi * 8 + mm] += acc[mm][3] * fin[h1];
+                            p0[g_lo * 8 + mm] += acc[mm][0] * fin0;
+                            p1[g_lo * 8 + mm] += acc[mm][1] * fin1;
+                            p0[g_hi * 8 + mm] += acc[mm][2] * fin0;
+                            p1[g_hi * 8 + mm] += acc[mm][3] * fin1;
                         }
                     }
                 }
@@ -528,7 +551,8 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
         }
         __syncthreads();
         {
-            const int r = tid >> 7, dim = tid & 127;  // 512 threads = 4 heads x 128 channels
+        for (int o = tid; o < kRep * kDim; o += kThreads) {
+            const int r = o >> 7, dim = o & 127;  // 4 heads x 128 channels
             float top = -INFINITY;
             for (int w = 0; w < kWarps; ++w) top = fmaxf(top, wm[w * kRep + r]);
             float lsum = 0.0f, asum = 0.0f;
@@ -545,6 +569,7 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
                 dst[1] = lsum;
             }
             dst[2 + dim] = asum;
+        }
         }
         cursor = item_end;
     }
