@@ -64,7 +64,7 @@ constexpr int kStagePerWarp = kVStage + 256;                // transposed V code
 constexpr int kStageBytes = kWarps * kStagePerWarp;         // 20480 (also min/max scratch of the table build)
 constexpr int kQBytes = kRep * kDim * 4;                    // 2048
 constexpr int kPrefixBytes = (kMaxBatch + 1) * 4 + 12;      // 2064
-constexpr int kSmemBytes = kLutBytes + kVtabBytes + kStageBytes + kQBytes + kPrefixBytes;
+constexpr int kSmemBytes = kLutBytes + kVtabBytes + kStageBytes + kPrefixBytes;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -138,23 +138,149 @@ __device__ __forceinline__ long long block_first_tile(long long total, int block
 }
 
 // ------------------------------------------------------------------------------------------------
+// prepare kernel: everything that depends only on (query, tables), laid out for shared memory
+// ------------------------------------------------------------------------------------------------
+//   blocks [0, B*Hkv)            score table of pair p = h*B + b: lut_g[p][code][slot] (8 bytes: four 13-bit
+//                                fields) and scale_g[p] = (step_r * log2 e, offset_r * log2 e), r = 0..3
+//   blocks [B*Hkv, B*Hkv + Hkv)  value codewords of head h in the bank-striped order the scan uses
+// Thread t of a score block always works on slot t % 32 (its codes are t/32, t/32 + 16, ...), so the
+// per-slot value range is a reduction over the warps and table writes are coalesced.
+
+constexpr int kPrepThreads = 512;
+constexpr int kPrepWarps = kPrepThreads / 32;
+constexpr int kPrepCodes = kWords / kPrepWarps;  // codes per thread
+constexpr int kPrepSlotStride = kWords * 16 + 16;   // padded so that lanes (= slots) read different banks
+constexpr int kPrepSmemBytes = kSlots * kPrepSlotStride + kRep * kDim * 4 + kPrepWarps * kSlots * 8 * 4;
+
+__global__ void __launch_bounds__(kPrepThreads)
+attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict__ ktab,
+                         const __half *__restrict__ vtab, uint2 *__restrict__ lut_g, uint4 *__restrict__ vperm_g,
+                         float *__restrict__ scale_g, int B, int Hkv) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pairs = B * Hkv;
+    if ((int)blockIdx.x >= pairs) {
+        const int h = blockIdx.x - pairs;
+        for (int j = tid; j < kWords * kSlots; j += kPrepThreads) {
+            const int code = j >> 5, pos = j & 31;
+            const int bq = pos & 7, u = pos >> 3;
+            const int s = bq >> 2, gh = (bq >> 1) & 1;
+            const int g = (bq & 1) | (u << 1) | (gh << 3);
+            const __half *src = vtab + ((((size_t)h * kStages + s) * kGroups + g) * kWords + code) * kSub;
+            vperm_g[(size_t)h * (kWords * kSlots) + j] = __ldg(reinterpret_cast<const uint4 *>(src));
+        }
+        return;
+    }
+    extern __shared__ __align__(128) unsigned char psm[];
+    unsigned char *ktab_s = psm;                                            // [slot][256 words x 16 B + 16 B pad]
+    float *q_s = reinterpret_cast<float *>(psm + kSlots * kPrepSlotStride);  // [4][128]
+    float *red = q_s + kRep * kDim;                                          // [warp][slot][min x4, max x4]
+    const int pair = blockIdx.x, h = pair / B, b = pair % B;
+    const int Hq = Hkv * kRep;
+    {   // the head's K tables are one contiguous 128 KB block [stage][group][word]: coalesced copy, padded rows
+        const unsigned char *src = reinterpret_cast<const unsigned char *>(ktab + (size_t)h * kStages * kGroups * kWords * kSub);
+        for (int u = tid; u < kSlots * kWords; u += kPrepThreads)
+            cp_async16(smem_u32(ktab_s) + (u >> 8) * kPrepSlotStride + (u & 255) * 16, src + (size_t)u * 16);
+    }
+    for (int i = tid; i < kRep * kDim; i += kPrepThreads)
+        q_s[i] = __half2float(q[((size_t)b * Hq + h * kRep + (i >> 7)) * kDim + (i & 127)]);
+    cp_async_wait_all();
+    __syncthreads();
+    const int slot = lane, g = slot & 15;
+    float qv[kRep][kSub];
+#pragma unroll
+    for (int r = 0; r < kRep; ++r)
+#pragma unroll
+        for (int i = 0; i < kSub; ++i) qv[r][i] = q_s[r * kDim + g * kSub + i];
+    const uint32_t tab_u32 = smem_u32(ktab_s) + slot * kPrepSlotStride;
+    float val[kPrepCodes][kRep];
+    float mn[kRep], mx[kRep];
+#pragma unroll
+    for (int r = 0; r < kRep; ++r) { mn[r] = INFINITY; mx[r] = -INFINITY; }
+#pragma unroll
+    for (int c = 0; c < kPrepCodes; ++c) {
+        const int code = warp + kPrepWarps * c;
+        const uint4 raw = lds128(tab_u32 + code * 16);
+        const __half2 *hp = reinterpret_cast<const __half2 *>(&raw);
+        float w[kSub];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(hp[i]);
+            w[2 * i] = f.x;
+            w[2 * i + 1] = f.y;
+        }
+#pragma unroll
+        for (int r = 0; r < kRep; ++r) {
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kSub; ++i) dot = fmaf(qv[r][i], w[i], dot);
+            val[c][r] = dot;
+            mn[r] = fminf(mn[r], dot);
+            mx[r] = fmaxf(mx[r], dot);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kRep; ++r) {
+        red[(warp * kSlots + slot) * 8 + r] = mn[r];
+        red[(warp * kSlots + slot) * 8 + 4 + r] = mx[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < kRep; ++r) { mn[r] = INFINITY; mx[r] = -INFINITY; }
+    for (int w = 0; w < kPrepWarps; ++w) {
+#pragma unroll
+        for (int r = 0; r < kRep; ++r) {
+            mn[r] = fminf(mn[r], red[(w * kSlots + slot) * 8 + r]);
+            mx[r] = fmaxf(mx[r], red[(w * kSlots + slot) * 8 + 4 + r]);
+        }
+    }
+    float inv_step[kRep];
+#pragma unroll
+    for (int r = 0; r < kRep; ++r) {
+        float range = mx[r] - mn[r];
+        float offs = mn[r];
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            range = fmaxf(range, __shfl_xor_sync(0xffffffffu, range, off));
+            offs += __shfl_xor_sync(0xffffffffu, offs, off);
+        }
+        const float step = range > 0.0f ? range / (float)kEntryMax : 1.0f;
+        inv_step[r] = 1.0f / step;
+        if (tid == 0) {
+            scale_g[(size_t)pair * 8 + r] = step * kLog2e;
+            scale_g[(size_t)pair * 8 + 4 + r] = offs * kLog2e;
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < kPrepCodes; ++c) {
+        const int code = warp + kPrepWarps * c;
+        uint32_t e[kRep];
+#pragma unroll
+        for (int r = 0; r < kRep; ++r)
+            e[r] = min((uint32_t)kEntryMax, __float2uint_rn((val[c][r] - mn[r]) * inv_step[r]));
+        uint2 packed;
+        packed.x = e[0] | (e[1] << 16);
+        packed.y = e[2] | (e[3] << 16);
+        lut_g[((size_t)pair * kWords + code) * kSlots + slot] = packed;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // scan kernel
 // ------------------------------------------------------------------------------------------------
 
 __global__ void __launch_bounds__(kThreads, 1)
-attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ kcodes,
-                      const uint8_t *__restrict__ vcodes, const __half *__restrict__ ktab,
-                      const __half *__restrict__ vtab, const int32_t *__restrict__ seq_start,
-                      const int32_t *__restrict__ seq_end, float *__restrict__ part, int B, int Hkv, int T_cap) {
+attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
+                      const uint8_t *__restrict__ vcodes, const uint2 *__restrict__ lut_g,
+                      const uint4 *__restrict__ vperm_g, const float *__restrict__ scale_g,
+                      const int32_t *__restrict__ seq_start, const int32_t *__restrict__ seq_end,
+                      float *__restrict__ part, int B, int Hkv, int T_cap) {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char *lut_s = smem;
     unsigned char *vtab_s = smem + kLutBytes;
     unsigned char *stage_s = vtab_s + kVtabBytes;
-    float *q_s = reinterpret_cast<float *>(stage_s + kStageBytes);
-    int *prefix_s = reinterpret_cast<int *>(reinterpret_cast<unsigned char *>(q_s) + kQBytes);
+    int *prefix_s = reinterpret_cast<int *>(stage_s + kStageBytes);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int Hq = Hkv * kRep;
 
     // ---- tile prefix over batch rows ---------------------------------------------------------
     if (warp == 0) {
@@ -234,112 +360,25 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
 
         __syncthreads();  // previous item fully merged: tables and staging may be overwritten
 
-        // ---- value codewords of this KV head -> shared memory (bank-striped) ------------------
+        // ---- tables of this item: both were laid out for shared memory by the prepare kernel, so
+        //      they arrive as plain coalesced 16-byte asynchronous copies
         if (h != loaded_head) {
-            for (int j = tid; j < kWords * kSlots; j += kThreads) {
-                const int code = j >> 5, pos = j & 31;
-                const int bq = pos & 7, u = pos >> 3;
-                const int s = bq >> 2, gh = (bq >> 1) & 1;
-                const int g = (bq & 1) | (u << 1) | (gh << 3);
-                const __half *src = vtab + ((((size_t)h * kStages + s) * kGroups + g) * kWords + code) * kSub;
-                cp_async16(smem_u32(vtab_s) + j * 16, src);
-            }
+            const unsigned char *src = reinterpret_cast<const unsigned char *>(vperm_g) + (size_t)h * kVtabBytes;
+            for (int j = tid; j < kVtabBytes / 16; j += kThreads) cp_async16(smem_u32(vtab_s) + j * 16, src + (size_t)j * 16);
             loaded_head = h;
         }
-
-        // ---- score table for (b, h): lane = slot, warp w owns codes [16w, 16w+16) -------------
-        for (int i = tid; i < kRep * kDim; i += kThreads)
-            q_s[i] = __half2float(q[((size_t)b * Hq + h * kRep + (i >> 7)) * kDim + (i & 127)]);
-        __syncthreads();
-        float step_l2[kRep], offs_l2[kRep];
         {
-            const int slot = lane, s = slot >> 4, g = slot & 15;
-            float qv[kRep][kSub];
+            const unsigned char *src = reinterpret_cast<const unsigned char *>(lut_g) + (size_t)pair * kLutBytes;
+            for (int j = tid; j < kLutBytes / 16; j += kThreads) cp_async16(lut_base + j * 16, src + (size_t)j * 16);
+        }
+        float step_l2[kRep], offs_l2[kRep];
 #pragma unroll
-            for (int r = 0; r < kRep; ++r)
-#pragma unroll
-                for (int i = 0; i < kSub; ++i) qv[r][i] = q_s[r * kDim + g * kSub + i];
-            float mn[kRep], mx[kRep];
-#pragma unroll
-            for (int r = 0; r < kRep; ++r) { mn[r] = INFINITY; mx[r] = -INFINITY; }
-            const __half *tab = ktab + ((((size_t)h * kStages + s) * kGroups + g) * kWords ) * kSub;
-            // the four partial scores of codeword c of this lane's slot (computed twice: once for the
-            // value range, once to quantise - cheaper than keeping 64 values in registers)
-            auto dots = [&](int c, float (&out)[kRep]) {
-                const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(tab + (size_t)c * kSub));
-                const __half2 *hp = reinterpret_cast<const __half2 *>(&raw);
-                float w[kSub];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __half22float2(hp[i]);
-                    w[2 * i] = f.x;
-                    w[2 * i + 1] = f.y;
-                }
-#pragma unroll
-                for (int r = 0; r < kRep; ++r) {
-                    float dot = 0.0f;
-#pragma unroll
-                    for (int i = 0; i < kSub; ++i) dot = fmaf(qv[r][i], w[i], dot);
-                    out[r] = dot;
-                }
-            };
-#pragma unroll 4
-            for (int c = warp; c < kWords; c += kWarps) {  // codes dealt round-robin to the warps
-                float d4[kRep];
-                dots(c, d4);
-#pragma unroll
-                for (int r = 0; r < kRep; ++r) {
-                    mn[r] = fminf(mn[r], d4[r]);
-                    mx[r] = fmaxf(mx[r], d4[r]);
-                }
-            }
-            float *red = reinterpret_cast<float *>(stage_s);  // [warp][slot][8]
-#pragma unroll
-            for (int r = 0; r < kRep; ++r) {
-                red[(warp * kSlots + slot) * 8 + r] = mn[r];
-                red[(warp * kSlots + slot) * 8 + 4 + r] = mx[r];
-            }
-            __syncthreads();
-#pragma unroll
-            for (int r = 0; r < kRep; ++r) { mn[r] = INFINITY; mx[r] = -INFINITY; }
-            for (int w = 0; w < kWarps; ++w) {
-#pragma unroll
-                for (int r = 0; r < kRep; ++r) {
-                    mn[r] = fminf(mn[r], red[(w * kSlots + slot) * 8 + r]);
-                    mx[r] = fmaxf(mx[r], red[(w * kSlots + slot) * 8 + 4 + r]);
-                }
-            }
-            float inv_step[kRep];
-#pragma unroll
-            for (int r = 0; r < kRep; ++r) {
-                float range = mx[r] - mn[r];
-                float offs = mn[r];
-#pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) {
-                    range = fmaxf(range, __shfl_xor_sync(0xffffffffu, range, off));
-                    offs += __shfl_xor_sync(0xffffffffu, offs, off);
-                }
-                const float step = range > 0.0f ? range / (float)kEntryMax : 1.0f;
-                inv_step[r] = 1.0f / step;
-                step_l2[r] = step * kLog2e;
-                offs_l2[r] = offs * kLog2e;
-            }
-#pragma unroll 4
-            for (int c = warp; c < kWords; c += kWarps) {
-                float d4[kRep];
-                dots(c, d4);
-                uint32_t e[kRep];
-#pragma unroll
-                for (int r = 0; r < kRep; ++r)
-                    e[r] = min((uint32_t)kEntryMax, __float2uint_rn((d4[r] - mn[r]) * inv_step[r]));
-                uint2 packed;
-                packed.x = e[0] | (e[1] << 16);
-                packed.y = e[2] | (e[3] << 16);
-                *reinterpret_cast<uint2 *>(lut_s + (size_t)c * 256 + slot * 8) = packed;
-            }
+        for (int r = 0; r < kRep; ++r) {
+            step_l2[r] = __ldg(scale_g + (size_t)pair * 8 + r);
+            offs_l2[r] = __ldg(scale_g + (size_t)pair * 8 + 4 + r);
         }
         cp_async_wait_all();
-        __syncthreads();  // tables ready; min/max scratch free again (it is the staging area)
+        __syncthreads();  // tables ready
 
         // ---- scan this block's tiles of the pair ----------------------------------------------
         float acc[8][4];
@@ -510,10 +549,11 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
             fin[r] = (m_true[r] == -INFINITY) ? 0.0f : fast_exp2(m_ref[r] - m_true[r]);  // re-reference to the true maximum
             l_warp[r] = t * fin[r];
         }
-        __syncthreads();  // every warp is done with the score table: reuse it as merge scratch
-        float *wm = reinterpret_cast<float *>(lut_s);      // [warps][4]
+        __syncthreads();  // every warp is done with the tables' score part and the staging area
+        static_assert(kWarps * 32 * 32 * 4 <= kLutBytes, "merge scratch must fit in the score table");
+        float *wm = reinterpret_cast<float *>(stage_s);    // [warps][4]
         float *wl = wm + kWarps * kRep;                     // [warps][4]
-        float *wacc = wl + kWarps * kRep;                   // [warps][4][128]
+        float *wacc = reinterpret_cast<float *>(lut_s);    // [warps][8 products x 4 registers][32 lanes]
         if (lane == 0) {
 #pragma unroll
             for (int r = 0; r < kRep; ++r) {
@@ -522,37 +562,26 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
             }
         }
         {
-            // column n = 2kq (+1): head n&3, class n>>2 = x_class; rows 0-7 hold group r8+8*x_class, rows 8-15 the other
-            const int h0 = (2 * kq) & 3, h1 = h0 + 1;
+            // accumulator register j of product mm: column 2kq + (j&1) -> head, row half j>>1; stored lane-major
             const float fin0 = (kq & 1) ? fin[2] : fin[0], fin1 = (kq & 1) ? fin[3] : fin[1];
-            const int g_lo = r8 + 8 * x_class, g_hi = r8 + 8 * (1 - x_class);
-            float *base = wacc + (size_t)warp * kRep * kDim;
+            float *base = wacc + (size_t)warp * 1024 + lane;
 #pragma unroll
-            for (int pass = 0; pass < 2; ++pass) {
-                if (x_class == pass) {
-#pragma unroll
-                    for (int mm = 0; mm < 8; ++mm) {
-                        float *p0 = base + h0 * kDim, *p1 = base + h1 * kDim;
-                        if (pass == 0) {
-                            p0[g_lo * 8 + mm] = acc[mm][0] * fin0;
-                            p1[g_lo * 8 + mm] = acc[mm][1] * fin1;
-                            p0[g_hi * 8 + mm] = acc[mm][2] * fin0;
-                            p1[g_hi * 8 + mm] = acc[mm][3] * fin1;
-                        } else {
-                            p0[g_lo * 8 + mm] += acc[mm][0] * fin0;
-                            p1[g_lo * 8 + mm] += acc[mm][1] * fin1;
-                            p0[g_hi * 8 + mm] += acc[mm][2] * fin0;
-                            p1[g_hi * 8 + mm] += acc[mm][3] * fin1;
-                        }
-                    }
-                }
-                __syncwarp();
+            for (int mm = 0; mm < 8; ++mm) {
+                base[(mm * 4 + 0) * 32] = acc[mm][0] * fin0;
+                base[(mm * 4 + 1) * 32] = acc[mm][1] * fin1;
+                base[(mm * 4 + 2) * 32] = acc[mm][2] * fin0;
+                base[(mm * 4 + 3) * 32] = acc[mm][3] * fin1;
             }
         }
         __syncthreads();
-        {
         for (int o = tid; o < kRep * kDim; o += kThreads) {
-            const int r = o >> 7, dim = o & 127;  // 4 heads x 128 channels
+            // output o <-> (product mm, register j, lane of visiting-order class 0); its class-1 twin is
+            // (mm, j^2, lane^2): same head and channel (see the B-operand column assignment above)
+            const int mm = o >> 6, j = (o >> 4) & 3, l16 = o & 15;
+            const int src_r8 = l16 >> 1, src_kq = l16 & 1;
+            const int lane0 = src_r8 * 4 + src_kq;
+            const int r = 2 * src_kq + (j & 1);
+            const int dim = (src_r8 + 8 * (j >> 1)) * 8 + mm;
             float top = -INFINITY;
             for (int w = 0; w < kWarps; ++w) top = fmaxf(top, wm[w * kRep + r]);
             float lsum = 0.0f, asum = 0.0f;
@@ -561,7 +590,8 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
                 if (mw == -INFINITY) continue;
                 const float sc = fast_exp2(mw - top);
                 lsum += sc * wl[w * kRep + r];
-                asum += sc * wacc[((size_t)w * kRep + r) * kDim + dim];
+                const float *src = wacc + (size_t)w * 1024;
+                asum += sc * (src[(mm * 4 + j) * 32 + lane0] + src[(mm * 4 + (j ^ 2)) * 32 + (lane0 ^ 2)]);
             }
             float *dst = part + ((size_t)(pair + blockIdx.x) * kRep + r) * kStateWidth;
             if (dim == 0) {
@@ -569,7 +599,6 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
                 dst[1] = lsum;
             }
             dst[2 + dim] = asum;
-        }
         }
         cursor = item_end;
     }
@@ -579,13 +608,14 @@ attn_gsrq_scan_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
 // merge of the per-block partial states of each (batch row, KV head) pair
 // ------------------------------------------------------------------------------------------------
 
-__global__ void __launch_bounds__(kDim)
+constexpr int kMaxScanBlocks = 256;  // persistent grid size (one block per SM) never exceeds this
+
+__global__ void __launch_bounds__(kRep * kDim)
 attn_gsrq_merge_kernel(const float *__restrict__ part, const int32_t *__restrict__ seq_start,
                        const int32_t *__restrict__ seq_end, __half *__restrict__ out, float *__restrict__ state_out,
                        int B, int Hkv, int T_cap, int scan_blocks) {
     const int pair = blockIdx.x;  // h * B + b
     const int h = pair / B, b = pair % B;
-    const int dim = threadIdx.x;
     // tiles before this pair, tiles of this pair, tiles per head (every thread computes the same numbers)
     int before = 0, mine = 0, per_head = 0;
     for (int i = 0; i < B; ++i) {
@@ -599,43 +629,45 @@ attn_gsrq_merge_kernel(const float *__restrict__ part, const int32_t *__restrict
     const int Hq = Hkv * kRep;
 
     // scan blocks whose tile share [start_c, start_{c+1}) overlaps this pair; a block with an empty
-    // share (more blocks than tiles) wrote nothing and must not be read
-    int c_first = 0;
-    if (mine > 0) {
-        c_first = (int)((first * scan_blocks) / total);
-        while (c_first > 0 && block_first_tile(total, c_first, scan_blocks) > first) --c_first;
+    // share (more blocks than tiles) wrote nothing and must not be read.  One thread lists them.
+    __shared__ int n_parts_s;
+    __shared__ int parts_s[kMaxScanBlocks];
+    if (threadIdx.x == 0) {
+        int n = 0;
+        if (mine > 0) {
+            int c = (int)((first * scan_blocks) / total);
+            while (c > 0 && block_first_tile(total, c, scan_blocks) > first) --c;
+            long long s0 = block_first_tile(total, c, scan_blocks);
+            for (; c < scan_blocks && s0 < last; ++c) {
+                const long long s1 = block_first_tile(total, c + 1, scan_blocks);
+                if (s1 > s0 && s1 > first && n < kMaxScanBlocks) parts_s[n++] = pair + c;
+                s0 = s1;
+            }
+        }
+        n_parts_s = n;
     }
-    auto overlaps = [&](int c) {
-        const long long s0 = block_first_tile(total, c, scan_blocks), s1 = block_first_tile(total, c + 1, scan_blocks);
-        return s1 > s0 && s1 > first && s0 < last;
-    };
-    for (int r = 0; r < kRep; ++r) {
-        float top = -INFINITY;
-        if (mine > 0) {
-            for (int c = c_first; c < scan_blocks && block_first_tile(total, c, scan_blocks) < last; ++c)
-                if (overlaps(c)) top = fmaxf(top, part[((size_t)(pair + c) * kRep + r) * kStateWidth]);
+    __syncthreads();
+    const int n_parts = n_parts_s;
+    const int r = threadIdx.x >> 7, dim = threadIdx.x & 127;  // 512 threads = 4 heads x 128 channels
+    float top = -INFINITY;
+    for (int i = 0; i < n_parts; ++i) top = fmaxf(top, part[((size_t)parts_s[i] * kRep + r) * kStateWidth]);
+    float lsum = 0.0f, asum = 0.0f;
+    for (int i = 0; i < n_parts; ++i) {
+        const float *st = part + ((size_t)parts_s[i] * kRep + r) * kStateWidth;
+        if (st[0] == -INFINITY) continue;
+        const float sc = __expf(st[0] - top);
+        lsum += sc * st[1];
+        asum += sc * st[2 + dim];
+    }
+    const size_t row = (size_t)b * Hq + h * kRep + r;
+    if (out) out[row * kDim + dim] = __float2half_rn(lsum > 0.0f ? asum / lsum : 0.0f);
+    if (state_out) {
+        float *dst = state_out + row * kStateWidth;
+        if (dim == 0) {
+            dst[0] = top;
+            dst[1] = lsum;
         }
-        float lsum = 0.0f, asum = 0.0f;
-        if (mine > 0) {
-            for (int c = c_first; c < scan_blocks && block_first_tile(total, c, scan_blocks) < last; ++c) {
-                if (!overlaps(c)) continue;
-                const float *st = part + ((size_t)(pair + c) * kRep + r) * kStateWidth;
-                if (st[0] == -INFINITY) continue;
-                const float sc = __expf(st[0] - top);
-                lsum += sc * st[1];
-                asum += sc * st[2 + dim];
-            }
-        }
-        const size_t row = (size_t)b * Hq + h * kRep + r;
-        if (out) out[row * kDim + dim] = __float2half_rn(lsum > 0.0f ? asum / lsum : 0.0f);
-        if (state_out) {
-            float *dst = state_out + row * kStateWidth;
-            if (dim == 0) {
-                dst[0] = top;
-                dst[1] = lsum;
-            }
-            dst[2 + dim] = asum;
-        }
+        dst[2 + dim] = asum;
     }
 }
 
@@ -645,10 +677,24 @@ bool attn_gsrq_supported(int Hq, int Hkv, int D, int G, int S, int K) {
     return D == gsrq::kDim && G == gsrq::kGroups && S == gsrq::kStages && K == gsrq::kWords && Hq == Hkv * gsrq::kRep;
 }
 
+static size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+struct GsrqWorkspace {
+    size_t part, lut, vperm, scale, total;
+    GsrqWorkspace(int B, int Hkv, int sms) {
+        const size_t pairs = (size_t)B * Hkv;
+        part = 0;
+        lut = align256((pairs + (size_t)sms) * gsrq::kRep * gsrq::kStateWidth * sizeof(float));
+        vperm = lut + pairs * gsrq::kLutBytes;
+        scale = vperm + (size_t)Hkv * gsrq::kVtabBytes;
+        total = align256(scale + pairs * 8 * sizeof(float));
+    }
+};
+
 size_t attn_gsrq_workspace_bytes(int B, int Hq, int Hkv, int D, int sms) {
     (void)Hq;
     (void)D;
-    return ((size_t)B * Hkv + (size_t)sms) * gsrq::kRep * gsrq::kStateWidth * sizeof(float);
+    return GsrqWorkspace(B, Hkv, sms).total;
 }
 
 int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
@@ -656,7 +702,7 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
                        __half *out, float *state_out, int B, int Hq, int Hkv, int64_t T_cap, int sms,
                        cudaStream_t stream) {
     (void)Hq;
-    if (B > gsrq::kMaxBatch) return TACVQ_ERR_UNSUPPORTED;
+    if (B > gsrq::kMaxBatch || sms > gsrq::kMaxScanBlocks) return TACVQ_ERR_UNSUPPORTED;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -664,14 +710,26 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
         cudaError_t e = cudaFuncSetAttribute(gsrq::attn_gsrq_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              gsrq::kSmemBytes);
         if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(gsrq::attn_gsrq_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 gsrq::kPrepSmemBytes);
+        if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
-    gsrq::attn_gsrq_scan_kernel<<<sms, gsrq::kThreads, gsrq::kSmemBytes, stream>>>(
-        q, kcodes, vcodes, ktab, vtab, seq_start, seq_end, (float *)workspace, B, Hkv, (int)T_cap);
+    const GsrqWorkspace ws(B, Hkv, sms);
+    unsigned char *base = (unsigned char *)workspace;
+    float *part = (float *)(base + ws.part);
+    uint2 *lut = (uint2 *)(base + ws.lut);
+    uint4 *vperm = (uint4 *)(base + ws.vperm);
+    float *scale = (float *)(base + ws.scale);
+    gsrq::attn_gsrq_prepare_kernel<<<B * Hkv + Hkv, gsrq::kPrepThreads, gsrq::kPrepSmemBytes, stream>>>(q, ktab, vtab, lut, vperm, scale, B, Hkv);
     int st = launch_status();
     if (st != TACVQ_OK) return st;
-    gsrq::attn_gsrq_merge_kernel<<<B * Hkv, gsrq::kDim, 0, stream>>>((const float *)workspace, seq_start, seq_end, out,
-                                                                     state_out, B, Hkv, (int)T_cap, sms);
+    gsrq::attn_gsrq_scan_kernel<<<sms, gsrq::kThreads, gsrq::kSmemBytes, stream>>>(
+        kcodes, vcodes, lut, vperm, scale, seq_start, seq_end, part, B, Hkv, (int)T_cap);
+    st = launch_status();
+    if (st != TACVQ_OK) return st;
+    gsrq::attn_gsrq_merge_kernel<<<B * Hkv, gsrq::kRep * gsrq::kDim, 0, stream>>>(part, seq_start, seq_end, out, state_out, B, Hkv,
+                                                                     (int)T_cap, sms);
     return launch_status();
 }
 
