@@ -155,6 +155,32 @@ TACVQ_API int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, co
                       int G, int S, int K, int64_t T_cap, tacvq_stream_t stream);
 
 /*
+ * tacvq_attn_decode for callers that must not allocate device memory.  It has no counterpart in the
+ * reference.  Some hosts of this library cannot call cudaMalloc at the point where they need
+ * attention: a plugin running inside another runtime's memory pool, a callback on a thread that is
+ * not allowed to touch the allocator, a process whose device memory was handed out in full at start-up.
+ * For them the scratch is a fixed 16 MiB array inside the library image
+ * (tacvq_attn_static_scratch_bytes() returns that figure); the caller passes only inputs and outputs.
+ * The call allocates and frees nothing, on the device or through any library.
+ *
+ *   - Limit: geometries whose tacvq_attn_workspace_bytes(...) exceeds 16 MiB are refused with
+ *     TACVQ_ERR_WORKSPACE (nothing is launched).  The benchmark geometry at batch 8 needs 8.1 MiB.
+ *   - The first call on each device looks up the array's device address (one cudaGetSymbolAddress
+ *     with that device current).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels may overlap on the GPU
+ *     (different streams without ordering between them) race on it.  Calls on one stream are safe.
+ *     The array keeps the previous call's contents; nothing in it has to start at zero, because
+ *     every word a call reads is written earlier by the same call.
+ *   - Every GPU that loads the library holds the 16 MiB until the process ends.
+ * Arguments, results and status codes are those of tacvq_attn_decode without the workspace pair.
+ */
+TACVQ_API size_t tacvq_attn_static_scratch_bytes(void);
+TACVQ_API int tacvq_attn_decode_static(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_t *vcodes,
+                                       const uint16_t *ktab_f16, const uint16_t *vtab_f16, const int32_t *seq_start,
+                                       const int32_t *seq_end, uint16_t *out_f16, float *state_out, int B, int Hq,
+                                       int Hkv, int D, int G, int S, int K, int64_t T_cap, tacvq_stream_t stream);
+
+/*
  * Log-sum-exp merge of n_parts partial softmax states [n_parts,B,Hq,2+D] fp32 (for example the
  * all-gathered per-GPU states of a sequence-split decode): M = max m_r, L = sum l_r e^(m_r-M),
  * A = sum acc_r e^(m_r-M).  out_f16 (NULL or [B,Hq,D]) receives A/L; merged (NULL or [B,Hq,2+D])

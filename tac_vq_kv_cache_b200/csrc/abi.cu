@@ -52,6 +52,29 @@ static int check_code_geometry(int B, int H, int T, int D, int G, int S, int K, 
     return TACVQ_OK;
 }
 
+// Scratch for tacvq_attn_decode_static: lives in the library image, so every GPU that loads the
+// library carries these 16 MiB until the process exits.  In host code the name of a __device__ array
+// is only a handle; the address a kernel may use comes from cudaGetSymbolAddress, asked once per
+// device while that device is current.
+constexpr size_t kStaticScratchBytes = (size_t)16 << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+static int static_scratch_for_current_device(void **ptr) {
+    static void *cached[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return TACVQ_ERR_DEVICE;
+    if (cached[dev] == nullptr) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        cached[dev] = p;
+    }
+    *ptr = cached[dev];
+    return TACVQ_OK;
+}
+
 }  // namespace tacvq
 
 using namespace tacvq;
@@ -180,6 +203,22 @@ int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_
                                    S, K, T_cap, splits, s);
     if (st != TACVQ_OK) return st;
     return attn_combine_dispatch((const float *)workspace, splits, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);
+}
+
+size_t tacvq_attn_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int tacvq_attn_decode_static(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_t *vcodes,
+                             const uint16_t *ktab_f16, const uint16_t *vtab_f16, const int32_t *seq_start,
+                             const int32_t *seq_end, uint16_t *out_f16, float *state_out, int B, int Hq, int Hkv, int D,
+                             int G, int S, int K, int64_t T_cap, tacvq_stream_t stream) {
+    const int g = check_attn_geometry(B, Hq, Hkv, D, G, S, K);
+    if (g != TACVQ_OK) return g;
+    if (tacvq_attn_workspace_bytes(B, Hq, Hkv, D, G, S) > kStaticScratchBytes) return TACVQ_ERR_WORKSPACE;
+    void *scratch = nullptr;
+    const int st = static_scratch_for_current_device(&scratch);
+    if (st != TACVQ_OK) return st;
+    return tacvq_attn_decode(q_f16, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, scratch, kStaticScratchBytes,
+                             out_f16, state_out, B, Hq, Hkv, D, G, S, K, T_cap, stream);
 }
 
 int tacvq_attn_combine(const float *states, int n_parts, uint16_t *out_f16, float *merged, int B, int Hq, int D,

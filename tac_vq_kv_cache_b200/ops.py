@@ -224,3 +224,36 @@ def attn_combine(states: torch.Tensor, *, want_out: bool = True, want_state: boo
         status = _lib.load().tacvq_attn_combine(_ptr(states), n, _ptr(out), _ptr(merged), b, hq, w - 2, _stream(device))
     _lib.check("tacvq_attn_combine", status)
     return out, merged
+
+
+def attn_decode_static(
+    q: torch.Tensor,
+    kcodes: torch.Tensor,
+    vcodes: torch.Tensor,
+    ktab_f16: torch.Tensor,
+    vtab_f16: torch.Tensor,
+    seq_start: torch.Tensor | None,
+    seq_end: torch.Tensor | None,
+    out: torch.Tensor | None = None,
+    state: torch.Tensor | None = None,
+) -> None:
+    """``attn_decode`` through the entry point that allocates nothing: scratch is a fixed array in the library.
+
+    For hosts that cannot allocate device memory where they call attention.  The
+    caller supplies every buffer (``out`` fp16 ``[B,Hq,D]`` and/or ``state`` fp32
+    ``[B,Hq,2+D]``, all inputs contiguous); geometries needing more than
+    ``tacvq_attn_static_scratch_bytes()`` of scratch raise ``TacvqError`` (status -5).
+    Calls on one stream are ordered; calls that may overlap on the GPU race on the shared array.
+    """
+    device = _require_cuda(q, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, out, state)
+    tensors = [t for t in (q, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, out, state) if t is not None]
+    if not all(t.is_contiguous() for t in tensors) or (out is None and state is None):
+        raise ValueError("all tensors must be contiguous and at least one of out/state must be given")
+    b, hq, dim = map(int, q.shape)
+    _b, hkv, t_cap, s, g = map(int, kcodes.shape)
+    with torch.cuda.device(device):
+        status = _lib.load().tacvq_attn_decode_static(
+            _ptr(q), _ptr(kcodes), _ptr(vcodes), _ptr(ktab_f16), _ptr(vtab_f16), _ptr(seq_start), _ptr(seq_end), _ptr(out),
+            _ptr(state), b, hq, hkv, dim, g, s, int(ktab_f16.shape[-2]), t_cap, _stream(device),
+        )
+    _lib.check("tacvq_attn_decode_static", status)
