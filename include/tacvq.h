@@ -144,9 +144,11 @@ TACVQ_API size_t tacvq_attn_workspace_bytes(int B, int Hq, int Hkv, int D, int G
  *                      NULL means 0 resp. T_cap.  An empty range yields out = 0, m = -inf, l = 0.
  *   workspace          scratch of at least tacvq_attn_workspace_bytes(...) bytes, 256-byte aligned
  *   out_f16            NULL or [B,Hq,D] fp16: acc / l
- *   state_out          NULL or [B,Hq,2+D] fp32: (m, l, acc[D]) with m the maximum score (natural
- *                      log units), l = sum exp(s-m), acc = sum exp(s-m) v  - the partial softmax
- *                      state that ranks exchange when the sequence is split across GPUs
+ *   state_out          NULL or [B,Hq,2+D] fp32: (m, l, acc[D]) with l = sum exp(s-m), acc = sum exp(s-m) v
+ *                      - the partial softmax state that ranks exchange when the sequence is split
+ *                      across GPUs.  m (natural log units) is the reference the sums are taken
+ *                      against: never above the maximum score and at most 8 ln 2 below it; m + ln l
+ *                      (the log-sum-exp) and acc / l do not depend on it
  *   Hq % Hkv == 0, Hq/Hkv <= 8, K == 256, D % 32 == 0, D <= 256.
  */
 TACVQ_API int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_t *vcodes, const uint16_t *ktab_f16,

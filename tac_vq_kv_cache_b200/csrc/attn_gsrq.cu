@@ -49,6 +49,7 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kDim = 128, kGroups = 16, kStages = 2, kSub = 8, kRep = 4, kSlots = 32, kWords = 256;
 constexpr int kTile = 32;          // tokens per warp tile
 constexpr int kMaxBatch = 512;
+constexpr int kMaxScanBlocks = 256;  // persistent grid size (one block per SM) never exceeds this
 constexpr int kStateWidth = kDim + 2;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -62,7 +63,6 @@ constexpr int kVBlock = 144;                                // 32 words + 16 B p
 constexpr int kVStage = 8 * kVBlock;                        // 1152
 constexpr int kStagePerWarp = kVStage + 256;                // transposed V codes + fp16 probabilities
 constexpr int kStageBytes = kWarps * kStagePerWarp;         // 20480 (also min/max scratch of the table build)
-constexpr int kQBytes = kRep * kDim * 4;                    // 2048
 constexpr int kPrefixBytes = (kMaxBatch + 1) * 4 + 12;      // 2064
 constexpr int kSmemBytes = kLutBytes + kVtabBytes + kStageBytes + kPrefixBytes;
 
@@ -82,6 +82,12 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void sts16(uint32_t addr, unsigned short v) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t d;
@@ -140,27 +146,34 @@ __device__ __forceinline__ long long block_first_tile(long long total, int block
 // ------------------------------------------------------------------------------------------------
 // prepare kernel: everything that depends only on (query, tables), laid out for shared memory
 // ------------------------------------------------------------------------------------------------
-//   blocks [0, B*Hkv)            score table of pair p = h*B + b: lut_g[p][code][slot] (8 bytes: four 13-bit
-//                                fields) and scale_g[p] = (step_r * log2 e, offset_r * log2 e), r = 0..3
-//   blocks [B*Hkv, B*Hkv + Hkv)  value codewords of head h in the bank-striped order the scan uses
-// Thread t of a score block always works on slot t % 32 (its codes are t/32, t/32 + 16, ...), so the
-// per-slot value range is a reduction over the warps and table writes are coalesced.
+//   blocks [0, 2*B*Hkv)      one residual stage of the score table of pair p = h*B + b:
+//                            lut_g[p][code][slot] (8 bytes: four 13-bit fields) and
+//                            scale_g[p][stage] = (step_r * log2 e, offset_r * log2 e), r = 0..3;
+//                            each stage has its own step, so the finer second stage keeps its precision
+//   blocks [2*B*Hkv, +Hkv)   value codewords of head h in the bank-striped order the scan uses
+// A lane always works on group lane % 16, so the per-group value range is a reduction over warps
+// and the table is written 128 contiguous bytes at a time.
 
 constexpr int kPrepThreads = 512;
 constexpr int kPrepWarps = kPrepThreads / 32;
-constexpr int kPrepCodes = kWords / kPrepWarps;  // codes per thread
-constexpr int kPrepSlotStride = kWords * 16 + 16;   // padded so that lanes (= slots) read different banks
-constexpr int kPrepSmemBytes = kSlots * kPrepSlotStride + kRep * kDim * 4 + kPrepWarps * kSlots * 8 * 4;
+constexpr int kPrepCodes = kWords / (2 * kPrepWarps);  // codes per thread (a warp covers 2 codes x 16 groups per round)
+constexpr int kPrepVBlocks = 8;                          // blocks that reorder one head's value table
+constexpr int kPrepSlotStride = kWords * 16 + 16;      // padded so that lanes (= groups) read different banks
+constexpr int kPrepSmemBytes = kGroups * kPrepSlotStride + kRep * kDim * 4 + kPrepWarps * 32 * 8 * 4;
 
 __global__ void __launch_bounds__(kPrepThreads)
 attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict__ ktab,
                          const __half *__restrict__ vtab, uint2 *__restrict__ lut_g, uint4 *__restrict__ vperm_g,
-                         float *__restrict__ scale_g, int B, int Hkv) {
+                         float *__restrict__ scale_g, int *__restrict__ tickets, const int32_t *__restrict__ seq_start,
+                         const int32_t *__restrict__ seq_end, __half *__restrict__ out, float *__restrict__ state_out,
+                         int B, int Hkv, int T_cap) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int pairs = B * Hkv;
-    if ((int)blockIdx.x >= pairs) {
-        const int h = blockIdx.x - pairs;
-        for (int j = tid; j < kWords * kSlots; j += kPrepThreads) {
+    if ((int)blockIdx.x >= 2 * pairs) {
+        const int h = (blockIdx.x - 2 * pairs) / kPrepVBlocks, part = (blockIdx.x - 2 * pairs) % kPrepVBlocks;
+        constexpr int kPer = kWords * kSlots / kPrepVBlocks;
+#pragma unroll
+        for (int j = part * kPer + tid; j < (part + 1) * kPer; j += kPrepThreads) {
             const int code = j >> 5, pos = j & 31;
             const int bq = pos & 7, u = pos >> 3;
             const int s = bq >> 2, gh = (bq >> 1) & 1;
@@ -171,34 +184,53 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
         return;
     }
     extern __shared__ __align__(128) unsigned char psm[];
-    unsigned char *ktab_s = psm;                                            // [slot][256 words x 16 B + 16 B pad]
-    float *q_s = reinterpret_cast<float *>(psm + kSlots * kPrepSlotStride);  // [4][128]
-    float *red = q_s + kRep * kDim;                                          // [warp][slot][min x4, max x4]
-    const int pair = blockIdx.x, h = pair / B, b = pair % B;
+    unsigned char *ktab_s = psm;                                                   // [group][256 words x 16 B + pad]
+    float *q_s = reinterpret_cast<float *>(psm + kGroups * kPrepSlotStride);        // [4][128]
+    float *red = q_s + kRep * kDim;                                                 // [warp][lane][min x4, max x4]
+    const int pair = blockIdx.x >> 1, stage = blockIdx.x & 1;
+    const int h = pair / B, b = pair % B;
     const int Hq = Hkv * kRep;
-    {   // the head's K tables are one contiguous 128 KB block [stage][group][word]: coalesced copy, padded rows
-        const unsigned char *src = reinterpret_cast<const unsigned char *>(ktab + (size_t)h * kStages * kGroups * kWords * kSub);
-        for (int u = tid; u < kSlots * kWords; u += kPrepThreads)
+    if (stage == 0) {
+        if (tid == 0) tickets[pair] = 0;  // the scan counts finished blocks per pair from zero
+        if (row_tokens(seq_start, seq_end, b, T_cap) == 0) {
+            // an empty range never reaches the scan: its result is defined here (out 0, m -inf, l 0, acc 0)
+            for (int o = tid; o < kRep * kDim; o += kPrepThreads) {
+                const size_t row = (size_t)b * Hq + h * kRep + (o >> 7);
+                if (out) out[row * kDim + (o & 127)] = __float2half_rn(0.0f);
+                if (state_out) {
+                    state_out[row * kStateWidth + 2 + (o & 127)] = 0.0f;
+                    if ((o & 127) == 0) {
+                        state_out[row * kStateWidth] = -INFINITY;
+                        state_out[row * kStateWidth + 1] = 0.0f;
+                    }
+                }
+            }
+        }
+    }
+    {   // one stage of the head's K tables is a contiguous 64 KB block [group][word]: coalesced copy, padded rows
+        const unsigned char *src = reinterpret_cast<const unsigned char *>(
+            ktab + ((size_t)h * kStages + stage) * kGroups * kWords * kSub);
+        for (int u = tid; u < kGroups * kWords; u += kPrepThreads)
             cp_async16(smem_u32(ktab_s) + (u >> 8) * kPrepSlotStride + (u & 255) * 16, src + (size_t)u * 16);
     }
     for (int i = tid; i < kRep * kDim; i += kPrepThreads)
         q_s[i] = __half2float(q[((size_t)b * Hq + h * kRep + (i >> 7)) * kDim + (i & 127)]);
     cp_async_wait_all();
     __syncthreads();
-    const int slot = lane, g = slot & 15;
+    const int g = lane & 15, half = lane >> 4;  // lane = (group, which of the warp's two codes per round)
     float qv[kRep][kSub];
 #pragma unroll
     for (int r = 0; r < kRep; ++r)
 #pragma unroll
         for (int i = 0; i < kSub; ++i) qv[r][i] = q_s[r * kDim + g * kSub + i];
-    const uint32_t tab_u32 = smem_u32(ktab_s) + slot * kPrepSlotStride;
+    const uint32_t tab_u32 = smem_u32(ktab_s) + g * kPrepSlotStride;
     float val[kPrepCodes][kRep];
     float mn[kRep], mx[kRep];
 #pragma unroll
     for (int r = 0; r < kRep; ++r) { mn[r] = INFINITY; mx[r] = -INFINITY; }
 #pragma unroll
     for (int c = 0; c < kPrepCodes; ++c) {
-        const int code = warp + kPrepWarps * c;
+        const int code = warp * 2 + half + 2 * kPrepWarps * c;
         const uint4 raw = lds128(tab_u32 + code * 16);
         const __half2 *hp = reinterpret_cast<const __half2 *>(&raw);
         float w[kSub];
@@ -220,8 +252,8 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
     }
 #pragma unroll
     for (int r = 0; r < kRep; ++r) {
-        red[(warp * kSlots + slot) * 8 + r] = mn[r];
-        red[(warp * kSlots + slot) * 8 + 4 + r] = mx[r];
+        red[(warp * 32 + lane) * 8 + r] = mn[r];
+        red[(warp * 32 + lane) * 8 + 4 + r] = mx[r];
     }
     __syncthreads();
 #pragma unroll
@@ -229,8 +261,8 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
     for (int w = 0; w < kPrepWarps; ++w) {
 #pragma unroll
         for (int r = 0; r < kRep; ++r) {
-            mn[r] = fminf(mn[r], red[(w * kSlots + slot) * 8 + r]);
-            mx[r] = fmaxf(mx[r], red[(w * kSlots + slot) * 8 + 4 + r]);
+            mn[r] = fminf(mn[r], fminf(red[(w * 32 + g) * 8 + r], red[(w * 32 + g + 16) * 8 + r]));
+            mx[r] = fmaxf(mx[r], fmaxf(red[(w * 32 + g) * 8 + 4 + r], red[(w * 32 + g + 16) * 8 + 4 + r]));
         }
     }
     float inv_step[kRep];
@@ -239,20 +271,20 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
         float range = mx[r] - mn[r];
         float offs = mn[r];
 #pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) {
+        for (int off = 8; off >= 1; off >>= 1) {  // over the 16 groups (both lane halves hold the same values)
             range = fmaxf(range, __shfl_xor_sync(0xffffffffu, range, off));
             offs += __shfl_xor_sync(0xffffffffu, offs, off);
         }
         const float step = range > 0.0f ? range / (float)kEntryMax : 1.0f;
         inv_step[r] = 1.0f / step;
         if (tid == 0) {
-            scale_g[(size_t)pair * 8 + r] = step * kLog2e;
-            scale_g[(size_t)pair * 8 + 4 + r] = offs * kLog2e;
+            scale_g[((size_t)pair * kStages + stage) * 8 + r] = step * kLog2e;
+            scale_g[((size_t)pair * kStages + stage) * 8 + 4 + r] = offs * kLog2e;
         }
     }
 #pragma unroll
     for (int c = 0; c < kPrepCodes; ++c) {
-        const int code = warp + kPrepWarps * c;
+        const int code = warp * 2 + half + 2 * kPrepWarps * c;
         uint32_t e[kRep];
 #pragma unroll
         for (int r = 0; r < kRep; ++r)
@@ -260,7 +292,7 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
         uint2 packed;
         packed.x = e[0] | (e[1] << 16);
         packed.y = e[2] | (e[3] << 16);
-        lut_g[((size_t)pair * kWords + code) * kSlots + slot] = packed;
+        lut_g[((size_t)pair * kWords + code) * kSlots + stage * kGroups + g] = packed;
     }
 }
 
@@ -273,8 +305,11 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
                       const uint8_t *__restrict__ vcodes, const uint2 *__restrict__ lut_g,
                       const uint4 *__restrict__ vperm_g, const float *__restrict__ scale_g,
                       const int32_t *__restrict__ seq_start, const int32_t *__restrict__ seq_end,
-                      float *__restrict__ part, int B, int Hkv, int T_cap) {
+                      float *__restrict__ part, int *__restrict__ tickets, __half *__restrict__ out,
+                      float *__restrict__ state_out, int B, int Hkv, int T_cap) {
     extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int n_parts_s;
+    __shared__ int parts_s[kMaxScanBlocks];
     unsigned char *lut_s = smem;
     unsigned char *vtab_s = smem + kLutBytes;
     unsigned char *stage_s = vtab_s + kVtabBytes;
@@ -301,9 +336,9 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
     }
     __syncthreads();
     const int tiles_per_head = prefix_s[B];
-    const long long total_tiles = (long long)tiles_per_head * Hkv;
-    long long cursor = block_first_tile(total_tiles, blockIdx.x, gridDim.x);
-    const long long my_end = block_first_tile(total_tiles, blockIdx.x + 1, gridDim.x);
+    const int total_tiles = tiles_per_head * Hkv;  // fits: checked by the dispatcher
+    int cursor = (int)block_first_tile(total_tiles, blockIdx.x, gridDim.x);
+    const int my_end = (int)block_first_tile(total_tiles, blockIdx.x + 1, gridDim.x);
 
     // ---- per-lane constants ------------------------------------------------------------------
     // score side: lane = token, slot visiting order permuted by XOR so a half warp covers 16 bank pairs
@@ -330,17 +365,15 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
     const int b_head = r8 & 3;                   // B-fragment column n = r8: head n&3, class n>>2
     const bool b_valid = (r8 >> 2) == x_class;
     const uint32_t lut_base = smem_u32(lut_s);
-    unsigned char *my_stage = stage_s + warp * kStagePerWarp;
-    const uint32_t vstage_u32 = smem_u32(my_stage);
+    const uint32_t vstage_u32 = smem_u32(stage_s) + warp * kStagePerWarp;
     const uint32_t pstage_u32 = vstage_u32 + kVStage;
-    __half *pstage = reinterpret_cast<__half *>(my_stage + kVStage);
 
     int loaded_head = -1;
 
     while (cursor < my_end) {
         // ---- which (head, batch row) does the cursor fall in ---------------------------------
         const int h = (int)(cursor / tiles_per_head);
-        const int rem = (int)(cursor - (long long)h * tiles_per_head);
+        const int rem = cursor - h * tiles_per_head;
         int b = 0;
         {
             int lo = 0, hi = B;  // largest b with prefix[b] <= rem and a non-empty row
@@ -350,9 +383,9 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
             }
             b = lo;
         }
-        const long long pair_first = (long long)h * tiles_per_head + prefix_s[b];
-        const long long pair_end = (long long)h * tiles_per_head + prefix_s[b + 1];
-        const long long item_end = pair_end < my_end ? pair_end : my_end;
+        const int pair_first = h * tiles_per_head + prefix_s[b];
+        const int pair_end = h * tiles_per_head + prefix_s[b + 1];
+        const int item_end = pair_end < my_end ? pair_end : my_end;
         const int tile_lo = (int)(cursor - pair_first), tile_hi = (int)(item_end - pair_first);
         const int tok_lo_row = max(seq_start ? seq_start[b] : 0, 0);
         const int n_tokens = row_tokens(seq_start, seq_end, b, T_cap);
@@ -371,11 +404,12 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
             const unsigned char *src = reinterpret_cast<const unsigned char *>(lut_g) + (size_t)pair * kLutBytes;
             for (int j = tid; j < kLutBytes / 16; j += kThreads) cp_async16(lut_base + j * 16, src + (size_t)j * 16);
         }
-        float step_l2[kRep], offs_l2[kRep];
+        float step_l2[kStages][kRep], offs_l2[kRep];
 #pragma unroll
         for (int r = 0; r < kRep; ++r) {
-            step_l2[r] = __ldg(scale_g + (size_t)pair * 8 + r);
-            offs_l2[r] = __ldg(scale_g + (size_t)pair * 8 + 4 + r);
+            step_l2[0][r] = __ldg(scale_g + (size_t)pair * 16 + r);
+            step_l2[1][r] = __ldg(scale_g + (size_t)pair * 16 + 8 + r);
+            offs_l2[r] = __ldg(scale_g + (size_t)pair * 16 + 4 + r) + __ldg(scale_g + (size_t)pair * 16 + 12 + r);
         }
         cp_async_wait_all();
         __syncthreads();  // tables ready
@@ -386,23 +420,21 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
         for (int mm = 0; mm < 8; ++mm)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[mm][i] = 0.0f;
-        float m_ref[kRep], m_true[kRep], l_lane[kRep];
+        float m_ref[kRep], l_lane[kRep];
 #pragma unroll
-        for (int r = 0; r < kRep; ++r) { m_ref[r] = -INFINITY; m_true[r] = -INFINITY; l_lane[r] = 0.0f; }
+        for (int r = 0; r < kRep; ++r) { m_ref[r] = -INFINITY; l_lane[r] = 0.0f; }
 
         const size_t row_base = ((size_t)b * Hkv + h) * (size_t)T_cap;
 
         // codes of a tile: lane = token; rows past the end of the range re-read the last valid row
-        auto code_ptrs = [&](int tile, const uint4 *&kp, const uint4 *&vp) {
+        auto code_offset = [=](int tile) -> size_t {  // byte offset of this lane's 32-byte code row
             const int tok = tile * kTile + lane;
-            const size_t tok_abs = row_base + (size_t)(tok_lo_row + min(tok, n_tokens - 1));
-            kp = reinterpret_cast<const uint4 *>(kcodes + tok_abs * 32);
-            vp = reinterpret_cast<const uint4 *>(vcodes + tok_abs * 32);
+            return (row_base + (size_t)(tok_lo_row + min(tok, n_tokens - 1))) * 32;
         };
         uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0, v0 = k0, v1 = k0;
         if (tile_lo + warp < tile_hi) {
-            const uint4 *kp, *vp;
-            code_ptrs(tile_lo + warp, kp, vp);
+            const size_t off = code_offset(tile_lo + warp);
+            const uint4 *kp = reinterpret_cast<const uint4 *>(kcodes + off), *vp = reinterpret_cast<const uint4 *>(vcodes + off);
             k0 = ldg_stream(kp); k1 = ldg_stream(kp + 1);
             v0 = ldg_stream(vp); v1 = ldg_stream(vp + 1);
         }
@@ -423,16 +455,16 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
                     tw[half * 4 + 3] = prmt(t1, t3, 0x7632u);
                 }
                 __syncwarp();  // previous tile's readers are done with the staging area
-                unsigned char *dst = my_stage + (((lane >> 3) * 2 + (lane & 1)) * kVBlock) + (((lane >> 1) & 3) * 32);
-                *reinterpret_cast<uint4 *>(dst) = make_uint4(tw[0], tw[1], tw[2], tw[3]);
-                *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(tw[4], tw[5], tw[6], tw[7]);
+                const uint32_t dst = vstage_u32 + (((lane >> 3) * 2 + (lane & 1)) * kVBlock) + (((lane >> 1) & 3) * 32);
+                sts128(dst, tw[0], tw[1], tw[2], tw[3]);
+                sts128(dst + 16, tw[4], tw[5], tw[6], tw[7]);
             }
 
             // -- scores: 32 look-ups of 8 bytes, four 13-bit fields each, flushed every 8 look-ups
             uint32_t kw[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
             if (tile + kWarps < tile_hi) {  // next tile's codes travel while this tile is computed
-                const uint4 *kp, *vp;
-                code_ptrs(tile + kWarps, kp, vp);
+                const size_t off = code_offset(tile + kWarps);
+                const uint4 *kp = reinterpret_cast<const uint4 *>(kcodes + off), *vp = reinterpret_cast<const uint4 *>(vcodes + off);
                 k0 = ldg_stream(kp); k1 = ldg_stream(kp + 1);
                 v0 = ldg_stream(vp); v1 = ldg_stream(vp + 1);
                 if (tile + 3 * kWarps < tile_hi) {  // and warm L2 two more rounds ahead
@@ -450,39 +482,46 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
                     if ((i & 2) == 0) { const uint32_t t = kw[i]; kw[i] = kw[i + 2]; kw[i + 2] = t; }
                 }
             }
-            uint32_t isum[kRep] = {0u, 0u, 0u, 0u};
+            float sc[kRep];
 #pragma unroll
-            for (int wp = 0; wp < 4; ++wp) {
-                uint32_t lo = 0u, hi = 0u;
+            for (int r = 0; r < kRep; ++r) sc[r] = offs_l2[r];
 #pragma unroll
-                for (int wj = 0; wj < 2; ++wj) {
-                    const int wi = wp * 2 + wj;
+            for (int st = 0; st < kStages; ++st) {  // words 0-3 hold stage 0, words 4-7 stage 1
+                uint32_t isum[kRep] = {0u, 0u, 0u, 0u};
 #pragma unroll
-                    for (int bi = 0; bi < 4; ++bi) {
-                        const uint32_t code256 = prmt(kw[wi], 0u, k_sel[bi]);
-                        const uint32_t addr = ((code256 | (uint32_t)(wi * 32 + bi * 8)) ^ k_lane_xor) + lut_base;
-                        const uint2 e = lds64(addr);
-                        lo += e.x;
-                        hi += e.y;
+                for (int wp = 0; wp < 2; ++wp) {
+                    uint32_t lo = 0u, hi = 0u;
+#pragma unroll
+                    for (int wj = 0; wj < 2; ++wj) {
+                        const int wi = st * 4 + wp * 2 + wj;
+#pragma unroll
+                        for (int bi = 0; bi < 4; ++bi) {
+                            const uint32_t code256 = prmt(kw[wi], 0u, k_sel[bi]);
+                            const uint32_t addr = ((code256 | (uint32_t)(wi * 32 + bi * 8)) ^ k_lane_xor) + lut_base;
+                            const uint2 e = lds64(addr);
+                            lo += e.x;
+                            hi += e.y;
+                        }
                     }
+                    isum[0] += lo & 0xffffu;
+                    isum[1] += lo >> 16;
+                    isum[2] += hi & 0xffffu;
+                    isum[3] += hi >> 16;
                 }
-                isum[0] += lo & 0xffffu;
-                isum[1] += lo >> 16;
-                isum[2] += hi & 0xffffu;
-                isum[3] += hi >> 16;
+#pragma unroll
+                for (int r = 0; r < kRep; ++r) sc[r] = fmaf((float)isum[r], step_l2[st][r], sc[r]);
             }
 
             // -- softmax bookkeeping (log2 domain), lazy rescale of the running reference
-            float sc[kRep], tmax[kRep];
+            float tmax[kRep];
             bool grow = false;
 #pragma unroll
             for (int r = 0; r < kRep; ++r) {
-                sc[r] = live ? fmaf((float)isum[r], step_l2[r], offs_l2[r]) : -INFINITY;
+                if (!live) sc[r] = -INFINITY;
                 float t = sc[r];
 #pragma unroll
                 for (int off = 16; off >= 1; off >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, off));
                 tmax[r] = t;
-                m_true[r] = fmaxf(m_true[r], t);
                 grow = grow || (t > m_ref[r] + kRescaleGap);
             }
             if (grow) {  // warp-uniform
@@ -506,7 +545,7 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
             for (int r = 0; r < kRep; ++r) {
                 const float p = fast_exp2(sc[r] - m_ref[r]);
                 l_lane[r] += p;
-                pstage[r * kTile + lane] = __float2half_rn(p);
+                sts16(pstage_u32 + (uint32_t)(r * kTile + lane) * 2, __half_as_ushort(__float2half_rn(p)));
             }
             __syncwarp();
 
@@ -540,14 +579,13 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
         }
 
         // ---- merge the warps of this block into one partial state of the pair ------------------
-        float l_warp[kRep], fin[kRep];
+        float l_warp[kRep];
 #pragma unroll
         for (int r = 0; r < kRep; ++r) {
             float t = l_lane[r];
 #pragma unroll
             for (int off = 16; off >= 1; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
-            fin[r] = (m_true[r] == -INFINITY) ? 0.0f : fast_exp2(m_ref[r] - m_true[r]);  // re-reference to the true maximum
-            l_warp[r] = t * fin[r];
+            l_warp[r] = t;
         }
         __syncthreads();  // every warp is done with the tables' score part and the staging area
         static_assert(kWarps * 32 * 32 * 4 <= kLutBytes, "merge scratch must fit in the score table");
@@ -557,20 +595,19 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
         if (lane == 0) {
 #pragma unroll
             for (int r = 0; r < kRep; ++r) {
-                wm[warp * kRep + r] = m_true[r];
+                wm[warp * kRep + r] = m_ref[r];  // reference of this warp's sums: within the rescale gap of its maximum
                 wl[warp * kRep + r] = l_warp[r];
             }
         }
         {
             // accumulator register j of product mm: column 2kq + (j&1) -> head, row half j>>1; stored lane-major
-            const float fin0 = (kq & 1) ? fin[2] : fin[0], fin1 = (kq & 1) ? fin[3] : fin[1];
             float *base = wacc + (size_t)warp * 1024 + lane;
 #pragma unroll
             for (int mm = 0; mm < 8; ++mm) {
-                base[(mm * 4 + 0) * 32] = acc[mm][0] * fin0;
-                base[(mm * 4 + 1) * 32] = acc[mm][1] * fin1;
-                base[(mm * 4 + 2) * 32] = acc[mm][2] * fin0;
-                base[(mm * 4 + 3) * 32] = acc[mm][3] * fin1;
+                base[(mm * 4 + 0) * 32] = acc[mm][0];
+                base[(mm * 4 + 1) * 32] = acc[mm][1];
+                base[(mm * 4 + 2) * 32] = acc[mm][2];
+                base[(mm * 4 + 3) * 32] = acc[mm][3];
             }
         }
         __syncthreads();
@@ -600,74 +637,56 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
             }
             dst[2 + dim] = asum;
         }
-        cursor = item_end;
-    }
-}
 
-// ------------------------------------------------------------------------------------------------
-// merge of the per-block partial states of each (batch row, KV head) pair
-// ------------------------------------------------------------------------------------------------
-
-constexpr int kMaxScanBlocks = 256;  // persistent grid size (one block per SM) never exceeds this
-
-__global__ void __launch_bounds__(kRep * kDim)
-attn_gsrq_merge_kernel(const float *__restrict__ part, const int32_t *__restrict__ seq_start,
-                       const int32_t *__restrict__ seq_end, __half *__restrict__ out, float *__restrict__ state_out,
-                       int B, int Hkv, int T_cap, int scan_blocks) {
-    const int pair = blockIdx.x;  // h * B + b
-    const int h = pair / B, b = pair % B;
-    // tiles before this pair, tiles of this pair, tiles per head (every thread computes the same numbers)
-    int before = 0, mine = 0, per_head = 0;
-    for (int i = 0; i < B; ++i) {
-        const int tiles = (row_tokens(seq_start, seq_end, i, T_cap) + kTile - 1) / kTile;
-        if (i < b) before += tiles;
-        if (i == b) mine = tiles;
-        per_head += tiles;
-    }
-    const long long total = (long long)per_head * Hkv;
-    const long long first = (long long)h * per_head + before, last = first + mine;
-    const int Hq = Hkv * kRep;
-
-    // scan blocks whose tile share [start_c, start_{c+1}) overlaps this pair; a block with an empty
-    // share (more blocks than tiles) wrote nothing and must not be read.  One thread lists them.
-    __shared__ int n_parts_s;
-    __shared__ int parts_s[kMaxScanBlocks];
-    if (threadIdx.x == 0) {
-        int n = 0;
-        if (mine > 0) {
-            int c = (int)((first * scan_blocks) / total);
-            while (c > 0 && block_first_tile(total, c, scan_blocks) > first) --c;
-            long long s0 = block_first_tile(total, c, scan_blocks);
-            for (; c < scan_blocks && s0 < last; ++c) {
-                const long long s1 = block_first_tile(total, c + 1, scan_blocks);
-                if (s1 > s0 && s1 > first && n < kMaxScanBlocks) parts_s[n++] = pair + c;
+        // ---- the block that finishes a pair last merges the pair's partial states -----------------
+        __threadfence();   // this block's partial state is visible device-wide before its ticket is drawn
+        __syncthreads();
+        if (tid == 0) {
+            // contributing blocks: those whose (non-empty) tile share overlaps [pair_first, pair_end)
+            const int c_lo = (int)(((long long)(pair_first + 1) * gridDim.x - 1) / total_tiles);
+            const int c_hi = (int)(((long long)pair_end * gridDim.x - 1) / total_tiles);
+            int n = 0;
+            long long s0 = block_first_tile(total_tiles, c_lo, gridDim.x);
+            for (int c = c_lo; c <= c_hi; ++c) {
+                const long long s1 = block_first_tile(total_tiles, c + 1, gridDim.x);
+                if (s1 > s0 && n < kMaxScanBlocks) parts_s[n++] = pair + c;
                 s0 = s1;
             }
+            const int drawn = atomicAdd(tickets + pair, 1);
+            n_parts_s = (drawn == n - 1) ? n : 0;  // 0: another block will finish this pair
+            __threadfence();
         }
-        n_parts_s = n;
-    }
-    __syncthreads();
-    const int n_parts = n_parts_s;
-    const int r = threadIdx.x >> 7, dim = threadIdx.x & 127;  // 512 threads = 4 heads x 128 channels
-    float top = -INFINITY;
-    for (int i = 0; i < n_parts; ++i) top = fmaxf(top, part[((size_t)parts_s[i] * kRep + r) * kStateWidth]);
-    float lsum = 0.0f, asum = 0.0f;
-    for (int i = 0; i < n_parts; ++i) {
-        const float *st = part + ((size_t)parts_s[i] * kRep + r) * kStateWidth;
-        if (st[0] == -INFINITY) continue;
-        const float sc = __expf(st[0] - top);
-        lsum += sc * st[1];
-        asum += sc * st[2 + dim];
-    }
-    const size_t row = (size_t)b * Hq + h * kRep + r;
-    if (out) out[row * kDim + dim] = __float2half_rn(lsum > 0.0f ? asum / lsum : 0.0f);
-    if (state_out) {
-        float *dst = state_out + row * kStateWidth;
-        if (dim == 0) {
-            dst[0] = top;
-            dst[1] = lsum;
+        __syncthreads();
+        const int n_parts = n_parts_s;
+        if (n_parts > 0) {
+            const int Hq = Hkv * kRep;
+            for (int o = tid; o < kRep * kDim; o += kThreads) {
+                const int r = o >> 7, dim = o & 127;
+                float top = -INFINITY;
+                for (int i = 0; i < n_parts; ++i)
+                    top = fmaxf(top, __ldcg(part + ((size_t)parts_s[i] * kRep + r) * kStateWidth));
+                float lsum = 0.0f, asum = 0.0f;
+                for (int i = 0; i < n_parts; ++i) {
+                    const float *st = part + ((size_t)parts_s[i] * kRep + r) * kStateWidth;
+                    const float mc = __ldcg(st);
+                    if (mc == -INFINITY) continue;
+                    const float sc = __expf(mc - top);
+                    lsum += sc * __ldcg(st + 1);
+                    asum += sc * __ldcg(st + 2 + dim);
+                }
+                const size_t row = (size_t)b * Hq + h * kRep + r;
+                if (out) out[row * kDim + dim] = __float2half_rn(lsum > 0.0f ? asum / lsum : 0.0f);
+                if (state_out) {
+                    float *dst = state_out + row * kStateWidth;
+                    if (dim == 0) {
+                        dst[0] = top;
+                        dst[1] = lsum;
+                    }
+                    dst[2 + dim] = asum;
+                }
+            }
         }
-        dst[2 + dim] = asum;
+        cursor = item_end;
     }
 }
 
@@ -680,14 +699,15 @@ bool attn_gsrq_supported(int Hq, int Hkv, int D, int G, int S, int K) {
 static size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
 
 struct GsrqWorkspace {
-    size_t part, lut, vperm, scale, total;
+    size_t part, lut, vperm, scale, tickets, total;
     GsrqWorkspace(int B, int Hkv, int sms) {
         const size_t pairs = (size_t)B * Hkv;
         part = 0;
         lut = align256((pairs + (size_t)sms) * gsrq::kRep * gsrq::kStateWidth * sizeof(float));
         vperm = lut + pairs * gsrq::kLutBytes;
         scale = vperm + (size_t)Hkv * gsrq::kVtabBytes;
-        total = align256(scale + pairs * 8 * sizeof(float));
+        tickets = align256(scale + pairs * gsrq::kStages * 8 * sizeof(float));
+        total = align256(tickets + pairs * sizeof(int));
     }
 };
 
@@ -703,6 +723,7 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
                        cudaStream_t stream) {
     (void)Hq;
     if (B > gsrq::kMaxBatch || sms > gsrq::kMaxScanBlocks) return TACVQ_ERR_UNSUPPORTED;
+    if (((T_cap + gsrq::kTile - 1) / gsrq::kTile) * B * Hkv > 0x7fffffffLL) return TACVQ_ERR_UNSUPPORTED;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -713,6 +734,14 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
         e = cudaFuncSetAttribute(gsrq::attn_gsrq_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  gsrq::kPrepSmemBytes);
         if (e != cudaSuccess) return (int)e;
+        // both kernels ask for the largest shared-memory carve-out, so the SMs are not re-partitioned
+        // between the prepare and the scan launch of every step
+        e = cudaFuncSetAttribute(gsrq::attn_gsrq_prepare_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(gsrq::attn_gsrq_scan_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
     const GsrqWorkspace ws(B, Hkv, sms);
@@ -721,15 +750,13 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
     uint2 *lut = (uint2 *)(base + ws.lut);
     uint4 *vperm = (uint4 *)(base + ws.vperm);
     float *scale = (float *)(base + ws.scale);
-    gsrq::attn_gsrq_prepare_kernel<<<B * Hkv + Hkv, gsrq::kPrepThreads, gsrq::kPrepSmemBytes, stream>>>(q, ktab, vtab, lut, vperm, scale, B, Hkv);
+    int *tickets = (int *)(base + ws.tickets);
+    gsrq::attn_gsrq_prepare_kernel<<<2 * B * Hkv + gsrq::kPrepVBlocks * Hkv, gsrq::kPrepThreads, gsrq::kPrepSmemBytes, stream>>>(
+        q, ktab, vtab, lut, vperm, scale, tickets, seq_start, seq_end, out, state_out, B, Hkv, (int)T_cap);
     int st = launch_status();
     if (st != TACVQ_OK) return st;
     gsrq::attn_gsrq_scan_kernel<<<sms, gsrq::kThreads, gsrq::kSmemBytes, stream>>>(
-        kcodes, vcodes, lut, vperm, scale, seq_start, seq_end, part, B, Hkv, (int)T_cap);
-    st = launch_status();
-    if (st != TACVQ_OK) return st;
-    gsrq::attn_gsrq_merge_kernel<<<B * Hkv, gsrq::kRep * gsrq::kDim, 0, stream>>>(part, seq_start, seq_end, out, state_out, B, Hkv,
-                                                                     (int)T_cap, sms);
+        kcodes, vcodes, lut, vperm, scale, seq_start, seq_end, part, tickets, out, state_out, B, Hkv, (int)T_cap);
     return launch_status();
 }
 
