@@ -157,6 +157,33 @@ TACVQ_API int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, co
                       int G, int S, int K, int64_t T_cap, tacvq_stream_t stream);
 
 /*
+ * Fill seq_start[0..B) = start and seq_end[0..B) = end on the stream: the visible range of a batch
+ * whose sequences advance in lockstep, i.e. LayerCache.visible() of the reference
+ * (experiments_followup_mistral/evaluate_mistral_longbench.py:62-70) for every row at once.
+ */
+TACVQ_API int tacvq_set_ranges(int32_t *seq_start, int32_t *seq_end, int B, int start, int end, tacvq_stream_t stream);
+
+/*
+ * One decode step of one layer in a single call: encode the new token rows of K and V into the code
+ * buffers at position `length` (tacvq_encode, in place), set every row's visible range to the last
+ * `window` tokens (window = 0: all stored tokens), attend.  Replaces the body of the reference's decode
+ * adapter per layer: cache.codec(...) + LayerCache.append + LayerCache.visible + attention
+ * (experiments_followup_mistral/evaluate_mistral_longbench.py:94-98, 112-122), without its torch.cat
+ * of the code tensors and without a decoded fp16 window.
+ *
+ *   k_rows, v_rows       [B,Hkv,T_new,D] contiguous, fp16 or fp32 (rows_dtype)
+ *   kcodes, vcodes       [B,Hkv,T_cap,S,G]; rows length .. length+T_new-1 are written
+ *   seq_start, seq_end   int32 [B] device scratch that receives the visible range
+ *   length               tokens already stored per sequence (host value; sequences advance in lockstep)
+ * All other arguments as in tacvq_attn_decode.
+ */
+TACVQ_API int tacvq_decode_step(const uint16_t *q_f16, const void *k_rows, const void *v_rows, int rows_dtype,
+                                const uint16_t *ktab_f16, const uint16_t *vtab_f16, uint8_t *kcodes, uint8_t *vcodes,
+                                int32_t *seq_start, int32_t *seq_end, int64_t length, int64_t window, void *workspace,
+                                size_t workspace_bytes, uint16_t *out_f16, float *state_out, int B, int Hq, int Hkv,
+                                int D, int G, int S, int K, int T_new, int64_t T_cap, tacvq_stream_t stream);
+
+/*
  * tacvq_attn_decode for callers that must not allocate device memory.  It has no counterpart in the
  * reference.  Some hosts of this library cannot call cudaMalloc at the point where they need
  * attention: a plugin running inside another runtime's memory pool, a callback on a thread that is

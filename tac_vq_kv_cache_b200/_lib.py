@@ -27,6 +27,9 @@ _SIGNATURES = {
     "tacvq_codeword_grad": (c_int, [c_void_p, c_void_p, c_void_p] + [c_int] * 8 + [c_int64, c_int64, c_void_p]),
     "tacvq_attn_workspace_bytes": (c_size_t, [c_int] * 6),
     "tacvq_attn_decode": (c_int, [c_void_p] * 8 + [c_size_t, c_void_p, c_void_p] + [c_int] * 7 + [c_int64, c_void_p]),
+    "tacvq_decode_step": (c_int, [c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 6 + [c_int64, c_int64, c_void_p, c_size_t,
+                                  c_void_p, c_void_p] + [c_int] * 8 + [c_int64, c_void_p]),
+    "tacvq_set_ranges": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tacvq_attn_static_scratch_bytes": (c_size_t, []),
     "tacvq_attn_decode_static": (c_int, [c_void_p] * 7 + [c_void_p, c_void_p] + [c_int] * 7 + [c_int64, c_void_p]),
     "tacvq_attn_combine": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),

@@ -53,8 +53,8 @@ class VQCodeCache:
         self.key = torch.zeros(shape, dtype=torch.uint8, device=self.device)
         self.value = torch.zeros(shape, dtype=torch.uint8, device=self.device)
         self.length = 0
-        self._start = torch.zeros(batch, dtype=torch.int32, device=self.device)
-        self._end = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self._range = torch.zeros(2, batch, dtype=torch.int32, device=self.device)  # [start; end) per row
+        self._range_is = (0, 0)
         self._workspace: torch.Tensor | None = None
 
     def reset(self) -> None:
@@ -91,15 +91,52 @@ class VQCodeCache:
         With ``want_state`` also returns the partial softmax state ``[B,Hq,2+D]``.
         """
         start, end = self.visible()
-        self._start.fill_(start)
-        self._end.fill_(end)
+        if (start, end) != self._range_is:
+            ops.set_ranges(self._range[0], self._range[1], start, end)
+            self._range_is = (start, end)
         if self._workspace is None:
             need = ops.attn_workspace_bytes(self.batch, int(query.shape[1]), self.heads, self.dim, self.groups, self.stages)
             if need == 0:
                 raise ValueError("attention geometry not supported")
             self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
         out, state = ops.attn_decode(
-            query, self.key, self.value, self.key_tables, self.value_tables, self._start, self._end,
+            query, self.key, self.value, self.key_tables, self.value_tables, self._range[0], self._range[1],
             workspace=self._workspace, want_state=want_state,
         )
         return (out, state) if want_state else out
+
+    def decode_step(self, query: torch.Tensor, raw_key: torch.Tensor, raw_value: torch.Tensor, out: torch.Tensor | None = None):
+        """Append the new token rows and attend, in one library call (``append`` + ``attend`` fused).
+
+        ``query [B,Hq,D]`` fp16 scaled, ``raw_key`` / ``raw_value`` ``[B,H,T_new,D]`` contiguous fp16 or fp32.
+        """
+        from . import _lib
+
+        tokens = int(raw_key.shape[2])
+        if raw_key.shape != raw_value.shape or tuple(raw_key.shape[:2]) != (self.batch, self.heads) or raw_key.shape[3] != self.dim:
+            raise ValueError("rows must be [B,H,T,D] matching the cache geometry")
+        if raw_key.dtype != raw_value.dtype or not (raw_key.is_contiguous() and raw_value.is_contiguous() and query.is_contiguous()):
+            raise ValueError("query and rows must be contiguous, rows of one dtype")
+        if self.length + tokens > self.max_tokens:
+            raise ValueError("code cache is full")
+        ops._require_cuda(query, raw_key, raw_value)
+        hq = int(query.shape[1])
+        if self._workspace is None:
+            need = ops.attn_workspace_bytes(self.batch, hq, self.heads, self.dim, self.groups, self.stages)
+            if need == 0:
+                raise ValueError("attention geometry not supported")
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        if out is None:
+            out = torch.empty(self.batch, hq, self.dim, dtype=torch.float16, device=self.device)
+        with ops._on(self.device):
+            status = _lib.load().tacvq_decode_step(
+                query.data_ptr(), raw_key.data_ptr(), raw_value.data_ptr(), ops._DTYPE_TAG[raw_key.dtype],
+                self.key_tables.data_ptr(), self.value_tables.data_ptr(), self.key.data_ptr(), self.value.data_ptr(),
+                self._range[0].data_ptr(), self._range[1].data_ptr(), self.length, 0 if self.window is None else self.window,
+                self._workspace.data_ptr(), self._workspace.numel(), out.data_ptr(), 0, self.batch, hq, self.heads, self.dim,
+                self.groups, self.stages, int(self.key_tables.shape[-2]), tokens, self.max_tokens, ops._stream(self.device),
+            )
+        _lib.check("tacvq_decode_step", status)
+        self.length += tokens
+        self._range_is = self.visible()
+        return out

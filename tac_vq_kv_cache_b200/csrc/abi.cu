@@ -52,6 +52,14 @@ static int check_code_geometry(int B, int H, int T, int D, int G, int S, int K, 
     return TACVQ_OK;
 }
 
+__global__ void set_ranges_kernel(int32_t *seq_start, int32_t *seq_end, int B, int start, int end) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < B) {
+        seq_start[i] = start;
+        seq_end[i] = end;
+    }
+}
+
 // Scratch for tacvq_attn_decode_static: lives in the library image, so every GPU that loads the
 // library carries these 16 MiB until the process exits.  In host code the name of a __device__ array
 // is only a handle; the address a kernel may use comes from cudaGetSymbolAddress, asked once per
@@ -203,6 +211,35 @@ int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_
                                    S, K, T_cap, splits, s);
     if (st != TACVQ_OK) return st;
     return attn_combine_dispatch((const float *)workspace, splits, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);
+}
+
+int tacvq_set_ranges(int32_t *seq_start, int32_t *seq_end, int B, int start, int end, tacvq_stream_t stream) {
+    if (!seq_start || !seq_end) return TACVQ_ERR_NULL;
+    if (B <= 0 || start < 0 || end < start) return TACVQ_ERR_GEOMETRY;
+    set_ranges_kernel<<<(B + 255) / 256, 256, 0, (cudaStream_t)stream>>>(seq_start, seq_end, B, start, end);
+    return launch_status();
+}
+
+int tacvq_decode_step(const uint16_t *q_f16, const void *k_rows, const void *v_rows, int rows_dtype,
+                      const uint16_t *ktab_f16, const uint16_t *vtab_f16, uint8_t *kcodes, uint8_t *vcodes,
+                      int32_t *seq_start, int32_t *seq_end, int64_t length, int64_t window, void *workspace,
+                      size_t workspace_bytes, uint16_t *out_f16, float *state_out, int B, int Hq, int Hkv, int D, int G,
+                      int S, int K, int T_new, int64_t T_cap, tacvq_stream_t stream) {
+    if (!k_rows || !v_rows || !seq_start || !seq_end) return TACVQ_ERR_NULL;
+    if (length < 0 || window < 0 || T_new <= 0 || length + T_new > T_cap) return TACVQ_ERR_RANGE;
+    const int64_t row = (int64_t)T_new * D;
+    int st = tacvq_encode(k_rows, rows_dtype, (int64_t)Hkv * row, row, D, ktab_f16, nullptr, kcodes, nullptr, TACVQ_F16, B,
+                          Hkv, T_new, D, G, S, K, length, T_cap, stream);
+    if (st != TACVQ_OK) return st;
+    st = tacvq_encode(v_rows, rows_dtype, (int64_t)Hkv * row, row, D, vtab_f16, nullptr, vcodes, nullptr, TACVQ_F16, B, Hkv,
+                      T_new, D, G, S, K, length, T_cap, stream);
+    if (st != TACVQ_OK) return st;
+    const int64_t end = length + T_new;
+    const int64_t start = (window > 0 && end > window) ? end - window : 0;
+    st = tacvq_set_ranges(seq_start, seq_end, B, (int)start, (int)end, stream);
+    if (st != TACVQ_OK) return st;
+    return tacvq_attn_decode(q_f16, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, workspace, workspace_bytes,
+                             out_f16, state_out, B, Hq, Hkv, D, G, S, K, T_cap, stream);
 }
 
 size_t tacvq_attn_static_scratch_bytes(void) { return kStaticScratchBytes; }

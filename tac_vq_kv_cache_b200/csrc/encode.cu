@@ -144,6 +144,90 @@ encode_small_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t 
 }
 
 // ------------------------------------------------------------------------------------------------
+// d <= 16, a handful of rows (decode steps): one warp per (row, head, group), lanes share the codewords
+// ------------------------------------------------------------------------------------------------
+// With only B*T rows (one new token per sequence) the kernel above would leave every thread alone
+// with a 256-word scan.  Here lane l scores words l, l+32, ... (ascending, strict '<' keeps the
+// lowest index per lane) and the warp takes the lexicographic minimum of (distance, index), which is
+// the same first-minimum as a sequential scan.  Arithmetic per distance is identical to the kernels
+// above, so the codes are too.
+
+template <int DSUB, typename XT>
+__global__ void __launch_bounds__(256)
+encode_rows_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const __half *__restrict__ tables,
+                   const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
+                   int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap) {
+    const int lane = threadIdx.x & 31;
+    const int64_t unit = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (unit >= (int64_t)B * T * H * G) return;
+    const int g = (int)(unit % G);
+    const int h = (int)((unit / G) % H);
+    const int64_t row = unit / ((int64_t)G * H);
+    const int64_t b = row / T, t = row % T;
+    const XT *src = x + b * sxb + (int64_t)h * sxh + t * sxt + (int64_t)g * DSUB;
+    float res[DSUB], dec[DSUB];
+#pragma unroll
+    for (int i = 0; i < DSUB; ++i) {
+        res[i] = to_float<XT>(src[i]);
+        dec[i] = 0.0f;
+    }
+    for (int s = 0; s < S; ++s) {
+        const int64_t base = (((int64_t)h * S + s) * G + g) * K;
+        const float xx = sqnorm_ordered<DSUB>([&](int i) { return res[i]; });
+        float best = __int_as_float(0x7f800000);
+        int arg = 0x7fffffff;
+        for (int k = lane; k < K; k += 32) {
+            float c[DSUB];
+#pragma unroll
+            for (int i = 0; i < DSUB; ++i) c[i] = __half2float(tables[(base + k) * DSUB + i]);
+            const float cc = sqnorm_in ? sqnorm_in[base + k] : sqnorm_ordered<DSUB>([&](int i) { return c[i]; });
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DSUB; ++i) dot = __fmaf_rn(res[i], c[i], dot);
+            const float dist = distance_expr(xx, cc, dot);
+            if (dist < best) {
+                best = dist;
+                arg = k;
+            }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
+            if (ob < best || (ob == best && oa < arg)) {
+                best = ob;
+                arg = oa;
+            }
+        }
+        if (arg >= K) arg = 0;  // every distance was +inf or NaN
+#pragma unroll
+        for (int i = 0; i < DSUB; ++i) {
+            const float w = __half2float(tables[(base + arg) * DSUB + i]);
+            res[i] = __fsub_rn(res[i], w);
+            dec[i] = __fadd_rn(dec[i], w);
+        }
+        if (lane == 0) codes[((((int64_t)b * H + h) * T_cap + t0 + t) * S + s) * G + g] = (uint8_t)arg;
+    }
+    if (recon != nullptr && lane == 0) {
+        const int64_t o = ((b * H + h) * T + t) * ((int64_t)G * DSUB) + (int64_t)g * DSUB;
+#pragma unroll
+        for (int i = 0; i < DSUB; ++i) {
+            if (recon_dtype == TACVQ_F16) store_as<__half>((__half *)recon + o + i, dec[i]);
+            else store_as<float>((float *)recon + o + i, dec[i]);
+        }
+    }
+}
+
+template <int DSUB, typename XT>
+static int launch_rows(const EncodeArgs &a) {
+    const int64_t units = (int64_t)a.B * a.T * a.H * a.G;
+    encode_rows_kernel<DSUB, XT><<<(unsigned)((units + 7) / 8), 256, 0, a.stream>>>(
+        (const XT *)a.x, a.sxb, a.sxh, a.sxt, (const __half *)a.tables, a.sqnorm, a.codes, a.recon, a.recon_dtype, a.B, a.H,
+        a.T, a.G, a.S, a.K, a.t0, a.T_cap);
+    return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
 // d >= 32
 // ------------------------------------------------------------------------------------------------
 
@@ -340,8 +424,20 @@ static int launch_large(const EncodeArgs &a) {
     return launch_status();
 }
 
+constexpr int kFewRows = 32;  // at or below this many rows a warp per (row, head, group) wins
+
 template <typename XT, typename TT>
 static int dispatch_d(const EncodeArgs &a) {
+    if constexpr (sizeof(TT) == 2) {
+        if ((int64_t)a.B * a.T <= kFewRows) {
+            switch (a.D / a.G) {
+                case 4: return launch_rows<4, XT>(a);
+                case 8: return launch_rows<8, XT>(a);
+                case 16: return launch_rows<16, XT>(a);
+                default: break;
+            }
+        }
+    }
     switch (a.D / a.G) {
         case 1: return launch_small<1, 4, XT, TT>(a);
         case 2: return launch_small<2, 4, XT, TT>(a);

@@ -7,6 +7,9 @@ libtacvq.so.  Canonical layouts: tables ``[H,S,G,K,d]`` fp16, codes
 
 from __future__ import annotations
 
+import contextlib
+import functools
+
 import torch
 
 from . import _lib
@@ -25,10 +28,24 @@ def _require_cuda(*tensors: torch.Tensor) -> torch.device:
             device = t.device
         elif t.device != device:
             raise RuntimeError("tensors live on different devices")
-    major, _minor = torch.cuda.get_device_capability(device)
+    if device is None:
+        raise RuntimeError("no tensor given")
+    major = _capability_major(device.index if device.index is not None else torch.cuda.current_device())
     if major != 10:
         raise RuntimeError(f"libtacvq.so holds sm_100a code only; device capability is {major}.x")
     return device
+
+
+@functools.lru_cache(maxsize=None)
+def _capability_major(index: int) -> int:
+    return torch.cuda.get_device_capability(index)[0]
+
+
+def _on(device: torch.device):
+    """Context that makes ``device`` current; free when it already is (the common case)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return contextlib.nullcontext()
+    return torch.cuda.device(device)
 
 
 def _ptr(t: torch.Tensor | None) -> int:
@@ -56,7 +73,7 @@ def table_sqnorm(tables_f16: torch.Tensor) -> torch.Tensor:
     device = _require_cuda(tables_f16)
     tables_f16 = tables_f16.contiguous()
     out = torch.empty(tables_f16.shape[:-1], dtype=torch.float32, device=device)
-    with torch.cuda.device(device):
+    with _on(device):
         _lib.check("tacvq_table_sqnorm", _lib.load().tacvq_table_sqnorm(_ptr(tables_f16), _ptr(out), out.numel(), tables_f16.shape[-1], _stream(device)))
     return out
 
@@ -91,7 +108,7 @@ def encode(
         raise ValueError("codes must be contiguous uint8 [B,H,T_cap,S,G]")
     recon = torch.empty(b, h, t, dim, dtype=states.dtype, device=device) if want_recon else None
     lib = _lib.load()
-    with torch.cuda.device(device):
+    with _on(device):
         if whitener is None:
             status = lib.tacvq_encode(
                 _ptr(x), _DTYPE_TAG[x.dtype], x.stride(0), x.stride(1), x.stride(2), _ptr(tables_f16), _ptr(table_sqnorm),
@@ -132,7 +149,7 @@ def decode(
     k, d = map(int, tables_f16.shape[-2:])
     t = t_cap - t0 if tokens is None else int(tokens)
     out = torch.empty(b, h, t, g * d, dtype=dtype, device=device)
-    with torch.cuda.device(device):
+    with _on(device):
         status = _lib.load().tacvq_decode(
             _ptr(codes), _ptr(tables_f16), _ptr(out), _DTYPE_TAG[dtype], b, h, t, g * d, g, s, s if depth is None else int(depth), k,
             t0, t_cap, _stream(device),
@@ -149,7 +166,7 @@ def codeword_grad(codes: torch.Tensor, grad_out: torch.Tensor, table_shape, *, d
     b, h, t, s, g = map(int, codes.shape)
     _h, _s, _g, k, d = map(int, table_shape)
     grad = torch.zeros(tuple(table_shape), dtype=torch.float32, device=device)
-    with torch.cuda.device(device):
+    with _on(device):
         status = _lib.load().tacvq_codeword_grad(
             _ptr(codes), _ptr(grad_out), _ptr(grad), b, h, t, g * d, g, s, s if depth is None else int(depth), k, 0, t, _stream(device)
         )
@@ -157,6 +174,7 @@ def codeword_grad(codes: torch.Tensor, grad_out: torch.Tensor, table_shape, *, d
     return grad
 
 
+@functools.lru_cache(maxsize=256)
 def attn_workspace_bytes(b: int, hq: int, hkv: int, dim: int, g: int, s: int) -> int:
     return int(_lib.load().tacvq_attn_workspace_bytes(b, hq, hkv, dim, g, s))
 
@@ -201,7 +219,7 @@ def attn_decode(
         out = torch.empty(b, hq, dim, dtype=torch.float16, device=device)
     if want_state and state is None:
         state = torch.empty(b, hq, dim + 2, dtype=torch.float32, device=device)
-    with torch.cuda.device(device):
+    with _on(device):
         status = _lib.load().tacvq_attn_decode(
             _ptr(q), _ptr(kcodes), _ptr(vcodes), _ptr(ktab_f16.contiguous()), _ptr(vtab_f16.contiguous()), _ptr(seq_start),
             _ptr(seq_end), _ptr(workspace), workspace.numel() * workspace.element_size(), _ptr(out), _ptr(state), b, hq, hkv,
@@ -209,6 +227,14 @@ def attn_decode(
         )
     _lib.check("tacvq_attn_decode", status)
     return out, state
+
+
+def set_ranges(seq_start: torch.Tensor, seq_end: torch.Tensor, start: int, end: int) -> None:
+    """Fill int32 ``[B]`` device tensors with one visible range for every row (one small launch)."""
+    device = _require_cuda(seq_start, seq_end)
+    with _on(device):
+        status = _lib.load().tacvq_set_ranges(_ptr(seq_start), _ptr(seq_end), seq_start.numel(), int(start), int(end), _stream(device))
+    _lib.check("tacvq_set_ranges", status)
 
 
 def attn_combine(states: torch.Tensor, *, want_out: bool = True, want_state: bool = False):
@@ -220,7 +246,7 @@ def attn_combine(states: torch.Tensor, *, want_out: bool = True, want_state: boo
     n, b, hq, w = map(int, states.shape)
     out = torch.empty(b, hq, w - 2, dtype=torch.float16, device=device) if want_out else None
     merged = torch.empty(b, hq, w, dtype=torch.float32, device=device) if want_state else None
-    with torch.cuda.device(device):
+    with _on(device):
         status = _lib.load().tacvq_attn_combine(_ptr(states), n, _ptr(out), _ptr(merged), b, hq, w - 2, _stream(device))
     _lib.check("tacvq_attn_combine", status)
     return out, merged
@@ -251,7 +277,7 @@ def attn_decode_static(
         raise ValueError("all tensors must be contiguous and at least one of out/state must be given")
     b, hq, dim = map(int, q.shape)
     _b, hkv, t_cap, s, g = map(int, kcodes.shape)
-    with torch.cuda.device(device):
+    with _on(device):
         status = _lib.load().tacvq_attn_decode_static(
             _ptr(q), _ptr(kcodes), _ptr(vcodes), _ptr(ktab_f16), _ptr(vtab_f16), _ptr(seq_start), _ptr(seq_end), _ptr(out),
             _ptr(state), b, hq, hkv, dim, g, s, int(ktab_f16.shape[-2]), t_cap, _stream(device),
