@@ -139,6 +139,13 @@ def run_ours(args) -> dict:
 
     gen = torch.Generator().manual_seed(8601 + rank)  # rank r holds layer r
     ktab, vtab = (t.to(device) for t in make_tables(gen))
+    if args.encode_only:  # profiler case: the 2-stage layer encode alone (one K tensor, reduced batch)
+        rows = torch.randn(2, KV_HEADS, 8192, DIM, generator=gen).half().to(device)
+        codes = torch.empty(2, KV_HEADS, 8192, STAGES, GROUPS, dtype=torch.uint8, device=device)
+        for _ in range(args.warmup + args.steps):
+            ops.encode(rows, ktab, codes=codes)
+        torch.cuda.synchronize(device)
+        return {"encode_only": True, "rows": 2 * 8192, "steps": args.steps}
     dgen = torch.Generator(device=device).manual_seed(8601 + rank)
     code_sets = [
         tuple(torch.randint(0, 256, (BATCH, KV_HEADS, CONTEXT, STAGES, GROUPS), dtype=torch.uint8, device=device, generator=dgen) for _ in range(2))
@@ -156,13 +163,14 @@ def run_ours(args) -> dict:
         step(i)
     barrier()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
-        barrier()
-        start.record()
-        for i in range(args.steps):
-            step(i)
-        end.record()
-        barrier()
+    clocks = ClockSampler(local)
+    clocks.__enter__()  # samples through the timed region and the end-to-end / encode sections after it
+    barrier()
+    start.record()
+    for i in range(args.steps):
+        step(i)
+    end.record()
+    barrier()
     elapsed_ms = start.elapsed_time(end)
     if world > 1:
         t = torch.tensor([elapsed_ms], device=device)
@@ -177,7 +185,7 @@ def run_ours(args) -> dict:
     roofline = {
         "bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
         "peak_source": f"{peak_kind} copy bandwidth", "algorithmic_bytes_per_launch": alg,
-        "kernel": "attention scan + split merge (one step = both launches, timed together)",
+        "kernel": "attn_gsrq_scan_kernel; the timed step also holds the prepare and merge launches (3 launches per step)",
         "traffic": TRAFFIC_BYTES_PER_LAUNCH,
     }
 
@@ -265,6 +273,7 @@ def run_ours(args) -> dict:
         if world == 1:
             cpu = cpu_decode_baseline(sample_seconds=12.0)
 
+    clocks.__exit__(None, None, None)
     result = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
@@ -278,7 +287,7 @@ def run_ours(args) -> dict:
         },
         "kv_tokens_scanned_per_s": round(BATCH * CONTEXT * world / (ms_per_step * 1e-3), 1),
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "encode": encode,
-        "gpu_launches": 2 * args.steps, "clocks": clocks.summary(),
+        "gpu_launches": 3 * args.steps, "clocks": clocks.summary(),
     }
     if world > 1:
         dist.destroy_process_group()
@@ -286,8 +295,8 @@ def run_ours(args) -> dict:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the scan kernel for one full-size launch, from the
-# ncu capture summarised under profiles/ (None until a capture of the current kernel exists).
-TRAFFIC_BYTES_PER_LAUNCH = None
+# ncu capture summarised under profiles/.
+TRAFFIC_BYTES_PER_LAUNCH = 143_500_000  # 139.5 MB read + 4.0 MB written (profiles/attn_gsrq_scan_32k.md)
 
 
 # ------------------------------------------------------------------------------------- CPU legs
@@ -392,6 +401,7 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--encode-only", action="store_true", help="run only the layer encode (used for profiler captures)")
     parser.add_argument("--kernel-only", action="store_true", help="time the decode-attention launches only (used for profiler captures)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)

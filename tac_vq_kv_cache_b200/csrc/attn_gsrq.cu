@@ -49,6 +49,16 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kDim = 128, kGroups = 16, kStages = 2, kSub = 8, kRep = 4, kSlots = 32, kWords = 256;
 constexpr int kTile = 32;          // tokens per warp tile
 constexpr int kMaxBatch = 512;
+#ifndef TACVQ_FUSED_MERGE
+#define TACVQ_FUSED_MERGE 0  // 1: the last scan block of a pair merges it (no merge launch); measured slower
+#endif
+#ifndef TACVQ_PDL
+#define TACVQ_PDL 1  // scan and merge are launched as programmatic dependents of their predecessor
+#endif
+#ifndef TACVQ_ITEM_COST
+#define TACVQ_ITEM_COST 32
+#endif
+constexpr int kItemCost = TACVQ_ITEM_COST;         // fixed cost of starting a (row, head) pair in a block, in 32-token tiles
 constexpr int kMaxScanBlocks = 256;  // persistent grid size (one block per SM) never exceeds this
 constexpr int kStateWidth = kDim + 2;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -111,6 +121,9 @@ __device__ __forceinline__ uint4 ldg_stream(const void *p) {
                  : "l"(p));
     return v;
 }
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may start
+// before its predecessor has finished; it must not touch the predecessor's results before this wait.
+__device__ __forceinline__ void wait_for_previous_kernel() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {  // 2^x, ex2.approx: 2^-inf = +0
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -252,8 +265,8 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
     }
 #pragma unroll
     for (int r = 0; r < kRep; ++r) {
-        red[(warp * 32 + lane) * 8 + r] = mn[r];
-        red[(warp * 32 + lane) * 8 + 4 + r] = mx[r];
+        red[(warp * 8 + r) * 32 + lane] = mn[r];       // lane-major: conflict-free writes and reads
+        red[(warp * 8 + 4 + r) * 32 + lane] = mx[r];
     }
     __syncthreads();
 #pragma unroll
@@ -261,17 +274,20 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
     for (int w = 0; w < kPrepWarps; ++w) {
 #pragma unroll
         for (int r = 0; r < kRep; ++r) {
-            mn[r] = fminf(mn[r], fminf(red[(w * 32 + g) * 8 + r], red[(w * 32 + g + 16) * 8 + r]));
-            mx[r] = fmaxf(mx[r], fmaxf(red[(w * 32 + g) * 8 + 4 + r], red[(w * 32 + g + 16) * 8 + 4 + r]));
+            mn[r] = fminf(mn[r], red[(w * 8 + r) * 32 + lane]);
+            mx[r] = fmaxf(mx[r], red[(w * 8 + 4 + r) * 32 + lane]);
         }
     }
     float inv_step[kRep];
 #pragma unroll
     for (int r = 0; r < kRep; ++r) {
+        // the two lane halves hold the two codes of a round for the same group: fold them first
+        mn[r] = fminf(mn[r], __shfl_xor_sync(0xffffffffu, mn[r], 16));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
         float range = mx[r] - mn[r];
         float offs = mn[r];
 #pragma unroll
-        for (int off = 8; off >= 1; off >>= 1) {  // over the 16 groups (both lane halves hold the same values)
+        for (int off = 8; off >= 1; off >>= 1) {  // over the 16 groups
             range = fmaxf(range, __shfl_xor_sync(0xffffffffu, range, off));
             offs += __shfl_xor_sync(0xffffffffu, offs, off);
         }
@@ -296,6 +312,53 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
     }
 }
 
+// Scan blocks whose share of work units [start_c, start_{c+1}) gives them at least one tile of the pair
+// occupying units [pair_first, pair_end): the partial states that exist for this pair.  Index = pair + c.
+__device__ int list_pair_parts(int pair_first, int pair_end, int total_units, int blocks, int pair, int *parts) {
+    const int c_lo = (int)(((long long)(pair_first + 1) * blocks - 1) / total_units);
+    const int c_hi = (int)(((long long)pair_end * blocks - 1) / total_units);
+    int n = 0;
+    long long s0 = block_first_tile(total_units, c_lo, blocks);
+    for (int c = c_lo; c <= c_hi; ++c) {
+        const long long s1 = block_first_tile(total_units, c + 1, blocks);
+        const long long lo = s0 > pair_first ? s0 : pair_first, hi = s1 < pair_end ? s1 : pair_end;
+        const long long t_lo = lo - pair_first - kItemCost, t_hi = hi - pair_first - kItemCost;
+        if (hi > lo && t_hi > (t_lo > 0 ? t_lo : 0) && n < kMaxScanBlocks) parts[n++] = pair + c;
+        s0 = s1;
+    }
+    return n;
+}
+
+// log-sum-exp merge of the listed partial states of one pair by a 512-thread block (4 heads x 128 channels)
+__device__ void merge_pair_parts(const float *part, const int *parts, int n_parts, int b, int h, int Hkv,
+                                 __half *out, float *state_out) {
+    const int Hq = Hkv * kRep;
+    for (int o = threadIdx.x; o < kRep * kDim; o += blockDim.x) {
+        const int r = o >> 7, dim = o & 127;
+        float top = -INFINITY;
+        for (int i = 0; i < n_parts; ++i) top = fmaxf(top, __ldcg(part + ((size_t)parts[i] * kRep + r) * kStateWidth));
+        float lsum = 0.0f, asum = 0.0f;
+        for (int i = 0; i < n_parts; ++i) {
+            const float *st = part + ((size_t)parts[i] * kRep + r) * kStateWidth;
+            const float mc = __ldcg(st);
+            if (mc == -INFINITY) continue;
+            const float sc = __expf(mc - top);
+            lsum += sc * __ldcg(st + 1);
+            asum += sc * __ldcg(st + 2 + dim);
+        }
+        const size_t row = (size_t)b * Hq + h * kRep + r;
+        if (out) out[row * kDim + dim] = __float2half_rn(lsum > 0.0f ? asum / lsum : 0.0f);
+        if (state_out) {
+            float *dst = state_out + row * kStateWidth;
+            if (dim == 0) {
+                dst[0] = top;
+                dst[1] = lsum;
+            }
+            dst[2 + dim] = asum;
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // scan kernel
 // ------------------------------------------------------------------------------------------------
@@ -308,8 +371,10 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
                       float *__restrict__ part, int *__restrict__ tickets, __half *__restrict__ out,
                       float *__restrict__ state_out, int B, int Hkv, int T_cap) {
     extern __shared__ __align__(128) unsigned char smem[];
+#if TACVQ_FUSED_MERGE
     __shared__ int n_parts_s;
     __shared__ int parts_s[kMaxScanBlocks];
+#endif
     unsigned char *lut_s = smem;
     unsigned char *vtab_s = smem + kLutBytes;
     unsigned char *stage_s = vtab_s + kVtabBytes;
@@ -317,19 +382,21 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-    // ---- tile prefix over batch rows ---------------------------------------------------------
+    // ---- work prefix over batch rows: a non-empty row costs its tiles plus kItemCost units (table
+    //      copies, pipeline fill and drain, merge), so blocks that enter more pairs get fewer tiles ------
     if (warp == 0) {
         int running = 0;
         for (int b0 = 0; b0 < B; b0 += 32) {
             const int b = b0 + lane;
             int tiles = (b < B) ? (row_tokens(seq_start, seq_end, b, T_cap) + kTile - 1) / kTile : 0;
+            if (tiles > 0) tiles += kItemCost;
             int incl = tiles;
 #pragma unroll
             for (int off = 1; off < 32; off <<= 1) {
                 const int n = __shfl_up_sync(0xffffffffu, incl, off);
                 if (lane >= off) incl += n;
             }
-            if (b < B) prefix_s[b] = running + incl - tiles;
+            if (b < B) prefix_s[b] = running + incl - tiles;  // 'tiles' already includes the item cost, see below
             running += __shfl_sync(0xffffffffu, incl, 31);
         }
         if (lane == 0) prefix_s[B] = running;
@@ -369,6 +436,7 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
     const uint32_t pstage_u32 = vstage_u32 + kVStage;
 
     int loaded_head = -1;
+    wait_for_previous_kernel();  // everything above used only kernel arguments and the range arrays
 
     while (cursor < my_end) {
         // ---- which (head, batch row) does the cursor fall in ---------------------------------
@@ -386,7 +454,12 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
         const int pair_first = h * tiles_per_head + prefix_s[b];
         const int pair_end = h * tiles_per_head + prefix_s[b + 1];
         const int item_end = pair_end < my_end ? pair_end : my_end;
-        const int tile_lo = (int)(cursor - pair_first), tile_hi = (int)(item_end - pair_first);
+        // work units -> tiles of the pair: the first kItemCost units of a pair carry no tile
+        const int tile_lo = max(cursor - pair_first - kItemCost, 0), tile_hi = max(item_end - pair_first - kItemCost, 0);
+        if (tile_hi <= tile_lo) {  // this block's share ends inside the cost zone: nothing to scan for this pair
+            cursor = item_end;
+            continue;
+        }
         const int tok_lo_row = max(seq_start ? seq_start[b] : 0, 0);
         const int n_tokens = row_tokens(seq_start, seq_end, b, T_cap);
         const int pair = h * B + b;
@@ -638,62 +711,74 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
             dst[2 + dim] = asum;
         }
 
+#if TACVQ_FUSED_MERGE
         // ---- the block that finishes a pair last merges the pair's partial states -----------------
         __threadfence();   // this block's partial state is visible device-wide before its ticket is drawn
         __syncthreads();
         if (tid == 0) {
-            // contributing blocks: those whose (non-empty) tile share overlaps [pair_first, pair_end)
-            const int c_lo = (int)(((long long)(pair_first + 1) * gridDim.x - 1) / total_tiles);
-            const int c_hi = (int)(((long long)pair_end * gridDim.x - 1) / total_tiles);
-            int n = 0;
-            long long s0 = block_first_tile(total_tiles, c_lo, gridDim.x);
-            for (int c = c_lo; c <= c_hi; ++c) {
-                const long long s1 = block_first_tile(total_tiles, c + 1, gridDim.x);
-                if (s1 > s0 && n < kMaxScanBlocks) parts_s[n++] = pair + c;
-                s0 = s1;
-            }
+            const int n = list_pair_parts(pair_first, pair_end, total_tiles, gridDim.x, pair, parts_s);
             const int drawn = atomicAdd(tickets + pair, 1);
             n_parts_s = (drawn == n - 1) ? n : 0;  // 0: another block will finish this pair
             __threadfence();
         }
         __syncthreads();
-        const int n_parts = n_parts_s;
-        if (n_parts > 0) {
-            const int Hq = Hkv * kRep;
-            for (int o = tid; o < kRep * kDim; o += kThreads) {
-                const int r = o >> 7, dim = o & 127;
-                float top = -INFINITY;
-                for (int i = 0; i < n_parts; ++i)
-                    top = fmaxf(top, __ldcg(part + ((size_t)parts_s[i] * kRep + r) * kStateWidth));
-                float lsum = 0.0f, asum = 0.0f;
-                for (int i = 0; i < n_parts; ++i) {
-                    const float *st = part + ((size_t)parts_s[i] * kRep + r) * kStateWidth;
-                    const float mc = __ldcg(st);
-                    if (mc == -INFINITY) continue;
-                    const float sc = __expf(mc - top);
-                    lsum += sc * __ldcg(st + 1);
-                    asum += sc * __ldcg(st + 2 + dim);
-                }
-                const size_t row = (size_t)b * Hq + h * kRep + r;
-                if (out) out[row * kDim + dim] = __float2half_rn(lsum > 0.0f ? asum / lsum : 0.0f);
-                if (state_out) {
-                    float *dst = state_out + row * kStateWidth;
-                    if (dim == 0) {
-                        dst[0] = top;
-                        dst[1] = lsum;
-                    }
-                    dst[2 + dim] = asum;
-                }
-            }
-        }
+        if (n_parts_s > 0) merge_pair_parts(part, parts_s, n_parts_s, b, h, Hkv, out, state_out);
+#endif
         cursor = item_end;
     }
 }
+
+// ------------------------------------------------------------------------------------------------
+// merge kernel: one block per (batch row, KV head) pair merges the partial states its scan blocks wrote
+// ------------------------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(kRep * kDim)
+attn_gsrq_merge_kernel(const float *__restrict__ part, const int32_t *__restrict__ seq_start,
+                       const int32_t *__restrict__ seq_end, __half *__restrict__ out, float *__restrict__ state_out,
+                       int B, int Hkv, int T_cap, int scan_blocks) {
+    __shared__ int n_parts_s;
+    __shared__ int parts_s[kMaxScanBlocks];
+    const int pair = blockIdx.x, h = pair / B, b = pair % B;
+    wait_for_previous_kernel();
+    if (threadIdx.x == 0) {
+        int before = 0, mine = 0, per_head = 0;  // work units, exactly as the scan kernel counts them
+        for (int i = 0; i < B; ++i) {
+            int units = (row_tokens(seq_start, seq_end, i, T_cap) + kTile - 1) / kTile;
+            if (units > 0) units += kItemCost;
+            if (i < b) before += units;
+            if (i == b) mine = units;
+            per_head += units;
+        }
+        const int first = h * per_head + before;
+        n_parts_s = mine > 0 ? list_pair_parts(first, first + mine, per_head * Hkv, scan_blocks, pair, parts_s) : 0;
+    }
+    __syncthreads();
+    if (n_parts_s > 0) merge_pair_parts(part, parts_s, n_parts_s, b, h, Hkv, out, state_out);
+}
+
 
 }  // namespace gsrq
 
 bool attn_gsrq_supported(int Hq, int Hkv, int D, int G, int S, int K) {
     return D == gsrq::kDim && G == gsrq::kGroups && S == gsrq::kStages && K == gsrq::kWords && Hq == Hkv * gsrq::kRep;
+}
+
+// Launch `kernel` so that it may be scheduled while the previous kernel of the stream drains
+// (the kernel itself waits, see wait_for_previous_kernel).
+template <typename... Params, typename... Args>
+static cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
 }
 
 static size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
@@ -723,7 +808,7 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
                        cudaStream_t stream) {
     (void)Hq;
     if (B > gsrq::kMaxBatch || sms > gsrq::kMaxScanBlocks) return TACVQ_ERR_UNSUPPORTED;
-    if (((T_cap + gsrq::kTile - 1) / gsrq::kTile) * B * Hkv > 0x7fffffffLL) return TACVQ_ERR_UNSUPPORTED;
+    if (((T_cap + gsrq::kTile - 1) / gsrq::kTile + gsrq::kItemCost) * B * Hkv > 0x7fffffffLL) return TACVQ_ERR_UNSUPPORTED;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -755,9 +840,33 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
         q, ktab, vtab, lut, vperm, scale, tickets, seq_start, seq_end, out, state_out, B, Hkv, (int)T_cap);
     int st = launch_status();
     if (st != TACVQ_OK) return st;
+#if TACVQ_PDL
+    {
+        cudaError_t e = launch_dependent(gsrq::attn_gsrq_scan_kernel, dim3(sms), dim3(gsrq::kThreads), gsrq::kSmemBytes, stream,
+                                         kcodes, vcodes, lut, vperm, scale, seq_start, seq_end, part, tickets, out, state_out,
+                                         B, Hkv, (int)T_cap);
+        st = e == cudaSuccess ? launch_status() : (int)e;
+    }
+#else
     gsrq::attn_gsrq_scan_kernel<<<sms, gsrq::kThreads, gsrq::kSmemBytes, stream>>>(
         kcodes, vcodes, lut, vperm, scale, seq_start, seq_end, part, tickets, out, state_out, B, Hkv, (int)T_cap);
-    return launch_status();
+    st = launch_status();
+#endif
+#if !TACVQ_FUSED_MERGE
+    if (st != TACVQ_OK) return st;
+#if TACVQ_PDL
+    {
+        cudaError_t e = launch_dependent(gsrq::attn_gsrq_merge_kernel, dim3(B * Hkv), dim3(gsrq::kRep * gsrq::kDim), 0, stream,
+                                         (const float *)part, seq_start, seq_end, out, state_out, B, Hkv, (int)T_cap, sms);
+        st = e == cudaSuccess ? launch_status() : (int)e;
+    }
+#else
+    gsrq::attn_gsrq_merge_kernel<<<B * Hkv, gsrq::kRep * gsrq::kDim, 0, stream>>>(part, seq_start, seq_end, out, state_out, B, Hkv,
+                                                                     (int)T_cap, sms);
+    st = launch_status();
+#endif
+#endif
+    return st;
 }
 
 }  // namespace tacvq
