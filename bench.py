@@ -294,6 +294,82 @@ def run_ours(args) -> dict:
     return result if rank == 0 else {}
 
 
+
+# --------------------------------------------------------------------- sequence split (extra workload)
+
+
+def run_sequence_split(args) -> dict:
+    """One long sequence split across the ranks: batch 1, 32 query / 8 KV heads, 131072 stored tokens.
+
+    Every rank scans its token range and produces partial softmax states; one NCCL all-gather of
+    [1,32,130] fp32 per rank and the merge kernel give every rank the result.  Scan and exchange+merge
+    are timed separately (the exchange is latency bound: 16,640 bytes per rank).
+    """
+    import torch.distributed as dist
+
+    from tac_vq_kv_cache_b200 import _lib, ops
+    from tac_vq_kv_cache_b200.dist import exchange_states, sequence_split
+
+    _lib.load()
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    context = 131072
+    lo, hi = sequence_split(context, rank, world) if world > 1 else (0, context)
+    gen = torch.Generator().manual_seed(8601)
+    ktab, vtab = (t.to(device) for t in make_tables(gen))
+    dgen = torch.Generator(device=device).manual_seed(8601 + rank)
+    own = hi - lo
+    sets = [tuple(torch.randint(0, 256, (1, KV_HEADS, own, STAGES, GROUPS), dtype=torch.uint8, device=device, generator=dgen) for _ in range(2)) for _ in range(8)]
+    q = (torch.randn(1, Q_HEADS, DIM, device=device, generator=dgen) / DIM**0.5).half()
+    workspace = torch.empty(ops.attn_workspace_bytes(1, Q_HEADS, KV_HEADS, DIM, GROUPS, STAGES), dtype=torch.uint8, device=device)
+    state = torch.empty(1, Q_HEADS, DIM + 2, dtype=torch.float32, device=device)
+
+    def scan(i):
+        ops.attn_decode(q, *sets[i % 8], ktab, vtab, workspace=workspace, want_out=False, want_state=True, state=state)
+
+    def merge():
+        gathered = exchange_states(state) if world > 1 else state[None]
+        return ops.attn_combine(gathered)[0]
+
+    for i in range(args.warmup):
+        scan(i)
+        merge()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    scan_ms = merge_ms = 0.0
+    for i in range(args.steps):  # per-step events: a decode step cannot pipeline across its own exchange
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        ev[0].record()
+        scan(i)
+        ev[1].record()
+        merge()
+        ev[2].record()
+        torch.cuda.synchronize(device)
+        scan_ms += ev[0].elapsed_time(ev[1])
+        merge_ms += ev[1].elapsed_time(ev[2])
+    t = torch.tensor([scan_ms / args.steps, merge_ms / args.steps], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.destroy_process_group()
+    scan_ms, merge_ms = (float(x) for x in t.tolist())
+    if rank != 0:
+        return {}
+    total = scan_ms + merge_ms
+    return {
+        "metric": "vq_kv_sequence_split_decode_tokens_per_s_at_131k_ctx", "value": round(1e3 / total, 1), "unit": "decode tokens/s (one layer, batch 1, 131072-token context split by sequence)",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total, 5), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "sequence-split decode attention over GSRQ 2-stage codes, batch 1, 32 query / 8 KV heads, head_dim 128, 131072 tokens",
+                   "tokens_per_rank": own, "l2": "8 code sets rotated between steps"},
+        "scan_ms": round(scan_ms, 5), "exchange_and_merge_ms": round(merge_ms, 5),
+        "exchange_bytes_per_rank": Q_HEADS * (DIM + 2) * 4, "gpu_launches": 4 * args.steps,
+    }
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of the scan kernel for one full-size launch, from the
 # ncu capture summarised under profiles/.
 TRAFFIC_BYTES_PER_LAUNCH = 143_500_000  # 139.5 MB read + 4.0 MB written (profiles/attn_gsrq_scan_32k.md)
@@ -401,11 +477,16 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--workload", choices=("decode32k", "seqsplit131k"), default="decode32k",
+                        help="decode32k: the headline configuration; seqsplit131k: one sequence split across the ranks (extra)")
     parser.add_argument("--encode-only", action="store_true", help="run only the layer encode (used for profiler captures)")
     parser.add_argument("--kernel-only", action="store_true", help="time the decode-attention launches only (used for profiler captures)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.workload == "seqsplit131k" and args.impl == "ours":
+        result = run_sequence_split(args)
+    else:
+        result = run_reference(args) if args.impl == "reference" else run_ours(args)
     if result:
         print(json.dumps(result), flush=True)
 
