@@ -53,7 +53,8 @@ encode_small_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t 
     __syncthreads();
 
     const int64_t rows = (int64_t)B * T;
-    const int64_t tile = (int64_t)blockIdx.x * (128 * TPT);
+    // a block keeps its tables and walks over row tiles, so the table load is paid once per block
+    for (int64_t tile = (int64_t)blockIdx.x * (128 * TPT); tile < rows; tile += (int64_t)gridDim.x * (128 * TPT)) {
 
     float res[TPT][DSUB];
     float dec[TPT][DSUB];
@@ -86,7 +87,7 @@ encode_small_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t 
             best[j] = __int_as_float(0x7f800000);
             arg[j] = 0;
         }
-#pragma unroll 2
+#pragma unroll 4
         for (int k = 0; k < K; ++k) {
             float c[DSUB];
 #pragma unroll
@@ -141,6 +142,7 @@ encode_small_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t 
             }
         }
     }
+    }  // row tiles
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -401,7 +403,11 @@ static int launch_small(const EncodeArgs &a) {
         if (e != cudaSuccess) return (int)e;
     }
     const int64_t rows = (int64_t)a.B * a.T;
-    dim3 grid((unsigned)((rows + 128 * TPT - 1) / (128 * TPT)), (unsigned)(a.H * a.G));
+    // about 8 resident blocks per SM in total; each block walks over the row tiles of its (head, group)
+    int64_t tiles = (rows + 128 * TPT - 1) / (128 * TPT);
+    const int64_t want = (148 * 8 + a.H * a.G - 1) / (a.H * a.G);
+    if (tiles > want) tiles = want;
+    dim3 grid((unsigned)tiles, (unsigned)(a.H * a.G));
     // The search tables are the plain tables unless a whitened search is running.
     const __half *plain = a.tables_f32 ? a.recon_tables : nullptr;
     kernel<<<grid, 128, smem, a.stream>>>((const XT *)a.x, a.sxb, a.sxh, a.sxt, (const TT *)a.tables, a.sqnorm, a.codes,
