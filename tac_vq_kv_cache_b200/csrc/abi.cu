@@ -20,6 +20,10 @@ int attn_generic_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t 
                           int Hq, int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits, cudaStream_t stream);
 int attn_combine_dispatch(const float *states, int n_parts, __half *out, float *merged, int64_t rows, int D,
                           cudaStream_t stream);
+bool attn_fullwidth_supported(int Hq, int Hkv, int D, int G, int S, int K);
+int attn_fullwidth_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
+                            const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, float *part, int B,
+                            int Hq, int Hkv, int S, int64_t T_cap, int splits, cudaStream_t stream);
 bool attn_gsrq_supported(int Hq, int Hkv, int D, int G, int S, int K);
 size_t attn_gsrq_workspace_bytes(int B, int Hq, int Hkv, int D, int sms);
 int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
@@ -205,7 +209,23 @@ int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_
                                   (const __half *)vtab_f16, seq_start, seq_end, workspace, (__half *)out_f16, state_out,
                                   B, Hq, Hkv, T_cap, sm_count(), s);
     }
-    const int splits = attn_generic_splits(B, Hkv, T_cap, sm_count());
+    int splits = attn_generic_splits(B, Hkv, T_cap, sm_count());
+    if (attn_fullwidth_supported(Hq, Hkv, D, G, S, K) && (T_cap + 8191) / 8192 <= kGenericMaxSplits) {
+        // every block builds its own score table and multiplies its histogram by the V tables (2 x S x 64 KB of
+        // table reads), so few, long splits are cheaper than many short ones
+        splits = (sm_count() + B * Hkv - 1) / (B * Hkv);
+        if (splits > kGenericMaxSplits) splits = kGenericMaxSplits;
+        if ((int64_t)splits * 1024 > T_cap) splits = (int)((T_cap + 1023) / 1024);
+        if (splits < 1) splits = 1;
+        const int64_t by_range = (T_cap + 8191) / 8192;  // a block's histogram holds at most 8192 tokens
+        if (splits < by_range) splits = (int)by_range;
+
+        int fw = attn_fullwidth_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
+                                         (const __half *)vtab_f16, seq_start, seq_end, (float *)workspace, B, Hq, Hkv, S,
+                                         T_cap, splits, s);
+        if (fw != TACVQ_OK) return fw;
+        return attn_combine_dispatch((const float *)workspace, splits, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);
+    }
     int st = attn_generic_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
                                    (const __half *)vtab_f16, seq_start, seq_end, (float *)workspace, B, Hq, Hkv, D, G,
                                    S, K, T_cap, splits, s);

@@ -87,7 +87,9 @@ def test_sliding_window_and_empty_rows(device):
 @pytest.mark.parametrize(
     "b,hq,hkv,t,groups,stages,sub",
     [
-        (2, 8, 2, 700, 1, 2, 128),   # two additive full-width codebooks
+        (2, 8, 2, 700, 1, 2, 128),   # two additive full-width codebooks (histogram kernel)
+        (2, 8, 2, 1, 1, 2, 128),     # ... a single token
+        (1, 32, 8, 5000, 1, 16, 128),  # the reference's own GSRQ layout at depth 16, 4 query heads per KV head
         (1, 8, 8, 300, 1, 16, 128),  # the reference's own GSRQ layout, depth 16, no query-head sharing
         (2, 4, 2, 500, 16, 1, 8),    # one-stage grouped CQ
         (1, 4, 1, 400, 32, 1, 4),    # 32 groups of 4
