@@ -82,8 +82,154 @@ static int launch_decode(const uint8_t *codes, const __half *tables, OT *out, in
     return launch_status();
 }
 
+// ------------------------------------------------------------------------------------------------
+// decode with the head's tables staged in shared memory by bulk asynchronous copies (TMA)
+// ------------------------------------------------------------------------------------------------
+// When all stages of one head's tables fit in shared memory (S*G*K*d*2 bytes <= 160 KB), a block takes
+// one head, pulls its tables in with cp.async.bulk (one elected thread issues the copies, an mbarrier
+// counts the bytes) and then streams rows: code bytes in, 16-byte fp16/fp32 chunks out, fully coalesced.
+// The wait on the mbarrier is bounded; if it ever ran out the block would simply read the tables from
+// global memory instead, so results do not depend on the copy engine.
+
+constexpr int kStagedThreads = 1024;
+constexpr int kStagedMaxBytes = 160 * 1024;
+constexpr int kBulkPiece = 16 * 1024;
+
+template <typename OT>
+__global__ void __launch_bounds__(kStagedThreads)
+decode_staged_kernel(const uint8_t *__restrict__ codes, const __half *__restrict__ tables, OT *__restrict__ out, int B,
+                     int H, int T, int D, int G, int S, int S_use, int K, int64_t t0, int64_t T_cap) {
+    extern __shared__ __align__(128) unsigned char staged[];
+    __shared__ __align__(8) unsigned long long mbar;
+    __shared__ int ready_s;
+    const int h = blockIdx.y;
+    const int d = D / G;
+    const uint32_t table_bytes = (uint32_t)S * G * K * d * 2;
+    const unsigned char *src = reinterpret_cast<const unsigned char *>(tables) + (size_t)h * table_bytes;
+    const uint32_t mbar_a = (uint32_t)__cvta_generic_to_shared(&mbar);
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_a));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar_a), "r"(table_bytes) : "memory");
+        for (uint32_t off = 0; off < table_bytes; off += kBulkPiece) {
+            const uint32_t n = min((uint32_t)kBulkPiece, table_bytes - off);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(staged + off)),
+                         "l"(src + off), "r"(n), "r"(mbar_a)
+                         : "memory");
+        }
+        int ok = 0;
+        for (int spin = 0; spin < (1 << 22) && !ok; ++spin) {  // bounded: a few milliseconds at most
+            asm volatile(
+                "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\nselp.s32 %0, 1, 0, p;\n}"
+                : "=r"(ok)
+                : "r"(mbar_a)
+                : "memory");
+        }
+        ready_s = ok;
+    }
+    __syncthreads();
+    const __half *tab = ready_s ? reinterpret_cast<const __half *>(staged) : tables + (size_t)h * (table_bytes / 2);
+
+    // thread = (row lane, 8-channel chunk): chunk, group and table offset are fixed per thread; a block owns a
+    // contiguous range of the head's rows and walks it with additive updates (no division in the loop)
+    const int chunks = D / 8;
+    const int rows_per_pass = kStagedThreads / chunks;
+    const int chunk = threadIdx.x % chunks, row_lane = threadIdx.x / chunks;
+    const int c0 = chunk * 8, g = c0 / d, i0 = c0 % d;
+    const int rows = B * T;  // the launcher keeps this below 2^31
+    const int per_block = (rows + gridDim.x - 1) / gridDim.x;
+    const int r_begin = blockIdx.x * per_block, r_end = min(rows, r_begin + per_block);
+    const __half *tab_g = tab + (size_t)g * K * d + i0;   // + (s*G*K + code) * d
+    const size_t stage_stride = (size_t)G * K * d;
+    int row = r_begin + row_lane;
+    int b = row / T, t = row - b * T;
+    for (; row < r_end; row += rows_per_pass) {
+        const size_t rid = ((size_t)b * H + h);
+        const uint8_t *cd = codes + ((rid * T_cap + t0 + t) * S) * G + g;
+        float sum[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
+        for (int s = 0; s < S_use; ++s) {
+            const int c = cd[s * G];
+            const uint4 raw = *reinterpret_cast<const uint4 *>(tab_g + s * stage_stride + (size_t)c * d);
+            const __half2 *hv = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(hv[i]);
+                sum[2 * i] = __fadd_rn(sum[2 * i], f.x);
+                sum[2 * i + 1] = __fadd_rn(sum[2 * i + 1], f.y);
+            }
+        }
+        OT *dst = out + (rid * T + t) * (size_t)D + c0;
+        if constexpr (sizeof(OT) == 2) {
+            uint4 packed;
+            __half2 *pv = reinterpret_cast<__half2 *>(&packed);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pv[i] = __floats2half2_rn(sum[2 * i], sum[2 * i + 1]);  // one convert per pair
+            *reinterpret_cast<uint4 *>(dst) = packed;
+        } else {
+            *reinterpret_cast<float4 *>(dst) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+            *reinterpret_cast<float4 *>(dst + 4) = make_float4(sum[4], sum[5], sum[6], sum[7]);
+        }
+        t += rows_per_pass;
+        while (t >= T) {
+            t -= T;
+            ++b;
+        }
+    }
+    if (threadIdx.x == 0 && !ready_s) {
+        // the copy did not report completion in time: give it one more bounded wait so that no bulk copy
+        // is still writing this block's shared memory when the block retires
+        int ok = 0;
+        for (int spin = 0; spin < (1 << 22) && !ok; ++spin) {
+            asm volatile(
+                "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\nselp.s32 %0, 1, 0, p;\n}"
+                : "=r"(ok)
+                : "r"(mbar_a)
+                : "memory");
+        }
+    }
+}
+
+template <typename OT>
+static int launch_decode_staged(const uint8_t *codes, const __half *tables, OT *out, int B, int H, int T, int D, int G,
+                                int S, int S_use, int K, int64_t t0, int64_t T_cap, cudaStream_t stream) {
+    const size_t bytes = (size_t)S * G * K * (D / G) * 2;
+    auto kernel = decode_staged_kernel<OT>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return (int)e;
+    // whole waves of blocks (one 1024-thread block per SM), as long as a block keeps >= 512 rows to
+    // amortise its table copy
+    int sms = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t rows = (int64_t)B * T;
+    int64_t per_head = 1;
+    for (int waves = 4; waves >= 1; --waves) {
+        const int64_t cand = ((int64_t)waves * sms) / H;
+        if (cand >= 1 && rows / cand >= 512) {
+            per_head = cand;
+            break;
+        }
+    }
+    dim3 grid((unsigned)per_head, (unsigned)H);
+    kernel<<<grid, kStagedThreads, bytes, stream>>>(codes, tables, out, B, H, T, D, G, S, S_use, K, t0, T_cap);
+    return launch_status();
+}
+
 int decode_dispatch(const uint8_t *codes, const __half *tables, void *out, int out_dtype, int B, int H, int T, int D,
                     int G, int S, int S_use, int K, int64_t t0, int64_t T_cap, cudaStream_t stream) {
+    const int d = D / G;
+    const size_t head_bytes = (size_t)S * G * K * d * 2;
+    const bool staged = d % 8 == 0 && kStagedThreads % (D / 8) == 0 && (int64_t)B * T < 0x7fffffff &&
+                        head_bytes <= (size_t)kStagedMaxBytes && head_bytes % 16 == 0 &&
+                        ((uintptr_t)tables & 15) == 0 && ((uintptr_t)out & 15) == 0 && (int64_t)B * T >= 1024;
+    if (staged) {
+        if (out_dtype == TACVQ_F16)
+            return launch_decode_staged<__half>(codes, tables, (__half *)out, B, H, T, D, G, S, S_use, K, t0, T_cap, stream);
+        return launch_decode_staged<float>(codes, tables, (float *)out, B, H, T, D, G, S, S_use, K, t0, T_cap, stream);
+    }
     if (out_dtype == TACVQ_F16)
         return launch_decode<__half>(codes, tables, (__half *)out, B, H, T, D, G, S, S_use, K, t0, T_cap, stream);
     return launch_decode<float>(codes, tables, (float *)out, B, H, T, D, G, S, S_use, K, t0, T_cap, stream);

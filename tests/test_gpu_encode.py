@@ -226,3 +226,17 @@ def test_argument_errors_are_reported_before_any_launch(device):
                                soft_backward_temperature=1.0, soft_backward_beta=0.5)
     with pytest.raises(RuntimeError):
         hard_grouped_cq(x.cpu(), torch.zeros(1, 16, 256, 8))
+
+
+@pytest.mark.parametrize("groups,stages,sub,dtype", [(16, 2, 8, torch.float16), (1, 2, 128, torch.float32), (16, 1, 8, torch.float16), (1, 16, 128, torch.float16)])
+def test_decode_of_long_rows_matches_the_oracle(device, groups, stages, sub, dtype):
+    """Row counts large enough for the kernel that stages a head's tables in shared memory (when they fit)."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(77)
+    tables = make_tables(gen, 3, stages, groups, sub)
+    codes = torch.randint(0, 256, (2, 3, 1500, stages, groups), generator=gen, dtype=torch.uint8)
+    got = ops.decode(codes.to(device), tables.to(device), dtype, t0=100, tokens=1300)
+    assert torch.equal(got.cpu(), C.decode(codes, tables, dtype, t0=100, tokens=1300))
+    if stages > 1:
+        got = ops.decode(codes.to(device), tables.to(device), dtype, depth=1)
+        assert torch.equal(got.cpu(), C.decode(codes, tables, dtype, depth=1))
