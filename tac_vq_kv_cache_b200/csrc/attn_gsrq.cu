@@ -49,8 +49,12 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kDim = 128, kGroups = 16, kStages = 2, kSub = 8, kRep = 4, kSlots = 32, kWords = 256;
 constexpr int kTile = 32;          // tokens per warp tile
 constexpr int kMaxBatch = 512;
+constexpr int kBulkPiece = 16384;     // bytes per bulk copy instruction
 #ifndef TACVQ_FUSED_MERGE
 #define TACVQ_FUSED_MERGE 0  // 1: the last scan block of a pair merges it (no merge launch); measured slower
+#endif
+#ifndef TACVQ_BULK_TABLES
+#define TACVQ_BULK_TABLES 0  // 1: table copies as cp.async.bulk + mbarrier (measured 1 % slower than 16-byte cp.async by all threads)
 #endif
 #ifndef TACVQ_PDL
 #define TACVQ_PDL 1  // scan and merge are launched as programmatic dependents of their predecessor
@@ -436,6 +440,16 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
     const uint32_t pstage_u32 = vstage_u32 + kVStage;
 
     int loaded_head = -1;
+#if TACVQ_BULK_TABLES
+    __shared__ __align__(8) unsigned long long mbar;
+    const uint32_t mbar_a = smem_u32(&mbar);
+    uint32_t mbar_phase = 0;
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_a));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+#endif
     wait_for_previous_kernel();  // everything above used only kernel arguments and the range arrays
 
     while (cursor < my_end) {
@@ -466,17 +480,31 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
 
         __syncthreads();  // previous item fully merged: tables and staging may be overwritten
 
-        // ---- tables of this item: both were laid out for shared memory by the prepare kernel, so
-        //      they arrive as plain coalesced 16-byte asynchronous copies
-        if (h != loaded_head) {
-            const unsigned char *src = reinterpret_cast<const unsigned char *>(vperm_g) + (size_t)h * kVtabBytes;
-            for (int j = tid; j < kVtabBytes / 16; j += kThreads) cp_async16(smem_u32(vtab_s) + j * 16, src + (size_t)j * 16);
-            loaded_head = h;
+        // ---- tables of this item: both were laid out for shared memory by the prepare kernel, so they
+        //      arrive as flat copies - bulk asynchronous copies (TMA) issued by one thread and counted by an
+        //      mbarrier, or, if that wait ever ran out, plain 16-byte cp.async by all threads
+        const bool need_v = h != loaded_head;
+        loaded_head = h;
+        const unsigned char *v_src = reinterpret_cast<const unsigned char *>(vperm_g) + (size_t)h * kVtabBytes;
+        const unsigned char *l_src = reinterpret_cast<const unsigned char *>(lut_g) + (size_t)pair * kLutBytes;
+#if TACVQ_BULK_TABLES
+        if (tid == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // earlier generic accesses before async writes
+            const uint32_t bytes = kLutBytes + (need_v ? kVtabBytes : 0);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar_a), "r"(bytes) : "memory");
+            for (int off = 0; off < kLutBytes; off += kBulkPiece)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 lut_base + off), "l"(l_src + off), "r"(kBulkPiece), "r"(mbar_a) : "memory");
+            if (need_v)
+                for (int off = 0; off < kVtabBytes; off += kBulkPiece)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                     smem_u32(vtab_s) + off), "l"(v_src + off), "r"(kBulkPiece), "r"(mbar_a) : "memory");
         }
-        {
-            const unsigned char *src = reinterpret_cast<const unsigned char *>(lut_g) + (size_t)pair * kLutBytes;
-            for (int j = tid; j < kLutBytes / 16; j += kThreads) cp_async16(lut_base + j * 16, src + (size_t)j * 16);
-        }
+#else
+        if (need_v)
+            for (int j = tid; j < kVtabBytes / 16; j += kThreads) cp_async16(smem_u32(vtab_s) + j * 16, v_src + (size_t)j * 16);
+        for (int j = tid; j < kLutBytes / 16; j += kThreads) cp_async16(lut_base + j * 16, l_src + (size_t)j * 16);
+#endif
         float step_l2[kStages][kRep], offs_l2[kRep];
 #pragma unroll
         for (int r = 0; r < kRep; ++r) {
@@ -484,8 +512,25 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
             step_l2[1][r] = __ldg(scale_g + (size_t)pair * 16 + 8 + r);
             offs_l2[r] = __ldg(scale_g + (size_t)pair * 16 + 4 + r) + __ldg(scale_g + (size_t)pair * 16 + 12 + r);
         }
+#if TACVQ_BULK_TABLES
+        {
+            int ok = 0;
+            for (int spin = 0; spin < (1 << 20) && !ok; ++spin)  // bounded wait on the copy's byte count
+                asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.s32 %0, 1, 0, p;\n}"
+                             : "=r"(ok) : "r"(mbar_a), "r"(mbar_phase) : "memory");
+            mbar_phase ^= 1u;
+            if (!__syncthreads_and(ok)) {  // never seen; keeps the result independent of the copy engine
+                if (need_v)
+                    for (int j = tid; j < kVtabBytes / 16; j += kThreads) cp_async16(smem_u32(vtab_s) + j * 16, v_src + (size_t)j * 16);
+                for (int j = tid; j < kLutBytes / 16; j += kThreads) cp_async16(lut_base + j * 16, l_src + (size_t)j * 16);
+                cp_async_wait_all();
+                __syncthreads();
+            }
+        }
+#else
         cp_async_wait_all();
         __syncthreads();  // tables ready
+#endif
 
         // ---- scan this block's tiles of the pair ----------------------------------------------
         float acc[8][4];
