@@ -45,6 +45,10 @@ static int sm_count() {
     return cached[dev];
 }
 
+// the specialised scan keeps one 64 KB score table per (batch row, KV head) pair in scratch: beyond 1024
+// pairs (64 MB) the generic kernel serves the call instead
+static bool gsrq_batch_ok(int B, int Hkv) { return B <= 512 && (int64_t)B * Hkv <= 1024; }
+
 static bool dtype_ok(int t) { return t == TACVQ_F16 || t == TACVQ_F32; }
 
 static bool sub_dim_ok(int d) { return (d >= 1 && d <= 8) || d == 16 || d == 32 || d == 64 || d == 128; }
@@ -186,7 +190,7 @@ static int check_attn_geometry(int B, int Hq, int Hkv, int D, int G, int S, int 
 size_t tacvq_attn_workspace_bytes(int B, int Hq, int Hkv, int D, int G, int S) {
     if (check_attn_geometry(B, Hq, Hkv, D, G, S, 256) != TACVQ_OK) return 0;
     size_t generic = (size_t)kGenericMaxSplits * B * Hq * (D + 2) * sizeof(float);
-    size_t fast = attn_gsrq_supported(Hq, Hkv, D, G, S, 256) ? attn_gsrq_workspace_bytes(B, Hq, Hkv, D, sm_count()) : 0;
+    size_t fast = (attn_gsrq_supported(Hq, Hkv, D, G, S, 256) && gsrq_batch_ok(B, Hkv)) ? attn_gsrq_workspace_bytes(B, Hq, Hkv, D, sm_count()) : 0;
     size_t need = generic > fast ? generic : fast;
     return (need + 255) & ~(size_t)255;
 }
@@ -204,7 +208,7 @@ int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_
         return TACVQ_ERR_WORKSPACE;
     if ((((uintptr_t)kcodes | (uintptr_t)vcodes) & 15) != 0) return TACVQ_ERR_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
-    if (attn_gsrq_supported(Hq, Hkv, D, G, S, K)) {
+    if (attn_gsrq_supported(Hq, Hkv, D, G, S, K) && gsrq_batch_ok(B, Hkv)) {
         return attn_gsrq_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
                                   (const __half *)vtab_f16, seq_start, seq_end, workspace, (__half *)out_f16, state_out,
                                   B, Hq, Hkv, T_cap, sm_count(), s);

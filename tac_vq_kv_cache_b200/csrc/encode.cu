@@ -233,8 +233,8 @@ static int launch_rows(const EncodeArgs &a) {
 // d >= 32
 // ------------------------------------------------------------------------------------------------
 
-constexpr int kLargeRows = 64;    // rows (tokens) per block
-constexpr int kLargeThreads = 256;
+constexpr int kLargeRows = 128;   // rows (tokens) per block
+constexpr int kLargeThreads = 512;
 
 template <int DSUB>
 struct LargeLayout {
@@ -256,12 +256,12 @@ encode_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t 
     using L = LargeLayout<DSUB>;
     constexpr int STR = L::kStride;
     extern __shared__ __align__(16) float smem[];
-    float *res = smem;                      // [64][STR]
+    float *res = smem;                      // [rows][STR]
     float *tab = res + L::kResFloats;       // [256][STR]
     float *nrm = tab + L::kTabFloats;       // [256]
-    float *xxs = nrm + kMaxWords;           // [64]
-    int *pick = (int *)(xxs + kLargeRows);  // [64]
-    uint8_t *hist = (uint8_t *)(pick + kLargeRows);  // [64][S] codes chosen so far
+    float *xxs = nrm + kMaxWords;           // [rows]
+    int *pick = (int *)(xxs + kLargeRows);  // [rows]
+    uint8_t *hist = (uint8_t *)(pick + kLargeRows);  // [rows][S] codes chosen so far
 
     const int hg = blockIdx.y;
     const int h = hg / G, g = hg % G;

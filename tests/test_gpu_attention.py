@@ -143,3 +143,11 @@ def test_attention_argument_errors(device):
         ops.attn_decode(work[0].float(), *work[1:])
     with pytest.raises(ValueError):
         ops.attn_decode(work[0][:, :3].contiguous(), *work[1:])  # 3 query heads over 1 KV head is fine? no: rep=3 unsupported
+
+
+def test_very_large_batch_uses_the_generic_kernel(device):
+    """More than 1024 (row, head) pairs: the specialised scan steps aside (its per-pair tables would need > 64 MB)."""
+    work = _workload(21, 300, 16, 4, 70, 16, 2, 8)
+    out, _ = _run(device, work)
+    want, _ = C.attention(*work)
+    _check(out, want)
