@@ -13,6 +13,7 @@ from collections.abc import Sequence
 import torch
 import torch.nn as nn
 
+from . import _layers
 from .closed_loop_vq import QuantizedKV, grouped_residual_vq, is_identity_whitener
 
 
@@ -59,20 +60,16 @@ class ClosedLoopGroupedCQ(nn.Module):
         token_chunk_size: int = 64,
     ) -> None:
         super().__init__()
-        if not key_codebooks or not (len(key_codebooks) == len(value_codebooks) == len(key_selector_whiteners)):
+        layers = len(key_codebooks)
+        if layers == 0 or len(value_codebooks) != layers or len(key_selector_whiteners) != layers:
             raise ValueError("CQ layer payloads differ")
-        shape = tuple(key_codebooks[0].shape)
-        if len(shape) != 4 or any(tuple(t.shape) != shape for t in (*key_codebooks, *value_codebooks)):
+        shape = tuple(key_codebooks[0].shape)  # [heads, groups, words, sub-dimension]
+        if len(shape) != 4 or not _layers.same_shape([*key_codebooks, *value_codebooks], shape):
             raise ValueError("CQ codebook layers have inconsistent geometry")
-        whitener_shape = (shape[0], shape[1], shape[3], shape[3])
-        if any(tuple(w.shape) != whitener_shape for w in key_selector_whiteners):
+        if not _layers.same_shape(key_selector_whiteners, (shape[0], shape[1], shape[3], shape[3])):
             raise ValueError("CQ key selector layers have inconsistent geometry")
-        self.key_tables = nn.ParameterList(
-            nn.Parameter(t.detach().float().contiguous(), requires_grad=False) for t in key_codebooks
-        )
-        self.value_tables = nn.ParameterList(nn.Parameter(t.detach().float().contiguous()) for t in value_codebooks)
-        for layer, w in enumerate(key_selector_whiteners):
-            self.register_buffer(f"key_selector_whitener_{layer:02d}", w.detach().float().contiguous(), persistent=True)
+        _layers.register_tables(self, key_codebooks, value_codebooks)
+        _layers.register_per_layer(self, "key_selector_whitener_{:02d}", key_selector_whiteners)
         self.dynamic_bpa = float(dynamic_bpa)
         self.token_chunk_size = int(token_chunk_size)
         self._identity: dict[int, tuple[int, bool]] = {}  # layer -> (buffer version, whitener is I)

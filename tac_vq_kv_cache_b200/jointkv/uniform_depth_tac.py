@@ -1,8 +1,10 @@
 """Uniform-depth residual VQ for all layers, CUDA-backed, reference-compatible.
 
-Mirrors ``ClosedLoopUniformResidualVQ`` (src/jointkv/uniform_depth_tac.py:19-101):
-same constructor, the 8-bit stage-index contract (:42-43), parameter/buffer
-names, ``forward(layer, raw_key, raw_value, *, mode="uniform") -> QuantizedKV``.
+Counterpart of ``ClosedLoopUniformResidualVQ`` in the reference
+(src/jointkv/uniform_depth_tac.py:19-101): the deployable hard residual-VQ codec with frozen key
+tables (and optional key whiteners) and trainable value tables.  Constructor arguments, the 8-bit
+stage-index contract (:42-43), parameter and buffer names, the ``forward`` signature and the
+``ValueError`` conditions are the reference's; the arithmetic runs in libtacvq.so.
 """
 
 from __future__ import annotations
@@ -12,11 +14,14 @@ from collections.abc import Sequence
 import torch
 import torch.nn as nn
 
+from . import _layers
 from .closed_loop_vq import QuantizedKV, hard_residual_vq_exits
+
+_WHITENER = "key_whitener_{:02d}"
 
 
 class ClosedLoopUniformResidualVQ(nn.Module):
-    """Hard residual VQ at one fixed depth: frozen K tables (and K whiteners), trainable V tables."""
+    """Hard residual VQ at one fixed depth for every layer of a model."""
 
     def __init__(
         self,
@@ -29,47 +34,39 @@ class ClosedLoopUniformResidualVQ(nn.Module):
         token_chunk_size: int = 1024,
     ) -> None:
         super().__init__()
-        if depth <= 0 or dynamic_bpa <= 0 or token_chunk_size <= 0:
+        if min(depth, token_chunk_size) <= 0 or dynamic_bpa <= 0:
             raise ValueError("invalid uniform residual-VQ configuration")
-        if not key_tables or not (len(key_tables) == len(value_tables) == len(key_whiteners)):
+        layers = len(key_tables)
+        if layers == 0 or len(value_tables) != layers or len(key_whiteners) != layers:
             raise ValueError("uniform residual-VQ layer payloads differ")
-        shape = tuple(key_tables[0].shape)
+        shape = tuple(key_tables[0].shape)  # [heads, stages, words, dim]
         if len(shape) != 4 or shape[1] != depth:
             raise ValueError("uniform residual-VQ tables have the wrong depth")
         if shape[2] != 256:
             raise ValueError("this deployment contract requires 8-bit stage indices")
-        if any(tuple(t.shape) != shape for t in (*key_tables, *value_tables)):
+        if not _layers.same_shape([*key_tables, *value_tables], shape):
             raise ValueError("uniform residual-VQ layer geometries differ")
-        self.key_tables = nn.ParameterList(
-            nn.Parameter(t.detach().float().contiguous(), requires_grad=False) for t in key_tables
-        )
-        self.value_tables = nn.ParameterList(nn.Parameter(t.detach().float().contiguous()) for t in value_tables)
-        heads, dimension = shape[0], shape[3]
-        for layer, w in enumerate(key_whiteners):
-            if w is not None and tuple(w.shape) != (heads, dimension, dimension):
-                raise ValueError("key assignment whitener geometry differs")
-            stored = torch.empty(0, dtype=torch.float32) if w is None else w.detach().float().contiguous()
-            self.register_buffer(f"key_whitener_{layer:02d}", stored, persistent=True)
-        self.depth = int(depth)
-        self.dynamic_bpa = float(dynamic_bpa)
-        self.token_chunk_size = int(token_chunk_size)
+        heads, dim = shape[0], shape[3]
+        if not _layers.same_shape([w for w in key_whiteners if w is not None], (heads, dim, dim)):
+            raise ValueError("key assignment whitener geometry differs")
+        _layers.register_tables(self, key_tables, value_tables)
+        _layers.register_per_layer(self, _WHITENER, key_whiteners)
+        self.depth, self.dynamic_bpa, self.token_chunk_size = int(depth), float(dynamic_bpa), int(token_chunk_size)
 
     def whitener(self, layer: int) -> torch.Tensor | None:
-        stored = getattr(self, f"key_whitener_{layer:02d}")
+        """The layer's key assignment whitener ``[H,D,D]``, or ``None`` when the layer has none."""
+        stored = getattr(self, _WHITENER.format(layer))
         return stored if stored.numel() else None
+
+    def _encode(self, states: torch.Tensor, tables: torch.Tensor, whitener: torch.Tensor | None):
+        exits, codes = hard_residual_vq_exits(
+            states, tables, prefixes=(self.depth,), assignment_whiteners=whitener, token_chunk_size=self.token_chunk_size
+        )
+        return exits[self.depth], codes
 
     def forward(self, layer: int, raw_key: torch.Tensor, raw_value: torch.Tensor, *, mode: str = "uniform") -> QuantizedKV:
         if mode != "uniform":
             raise ValueError("uniform residual VQ exposes only uniform mode")
-        key_exits, key_indices = hard_residual_vq_exits(
-            raw_key, self.key_tables[layer], prefixes=(self.depth,), assignment_whiteners=self.whitener(layer),
-            token_chunk_size=self.token_chunk_size,
-        )
-        value_exits, value_indices = hard_residual_vq_exits(
-            raw_value, self.value_tables[layer], prefixes=(self.depth,), assignment_whiteners=None,
-            token_chunk_size=self.token_chunk_size,
-        )
-        return QuantizedKV(
-            key=key_exits[self.depth], value=value_exits[self.depth], key_indices=key_indices, value_indices=value_indices,
-            projected_depths=None,
-        )
+        key, key_codes = self._encode(raw_key, self.key_tables[layer], self.whitener(layer))
+        value, value_codes = self._encode(raw_value, self.value_tables[layer], None)
+        return QuantizedKV(key=key, value=value, key_indices=key_codes, value_indices=value_codes, projected_depths=None)
