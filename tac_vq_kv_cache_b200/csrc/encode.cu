@@ -14,7 +14,13 @@
 
 #include "common.cuh"
 
+#ifndef TACVQ_ENCODE_TC
+#define TACVQ_ENCODE_TC 1  // 8-wide groups go to the tensor-core filtered kernel (encode_tc.cu)
+#endif
+
 namespace tacvq {
+
+int encode_tc8_launch(const EncodeArgs &a);
 
 // ------------------------------------------------------------------------------------------------
 // d <= 16
@@ -442,6 +448,10 @@ static int dispatch_d(const EncodeArgs &a) {
                 case 16: return launch_rows<16, XT>(a);
                 default: break;
             }
+        }
+        if (TACVQ_ENCODE_TC && a.D / a.G == 8) {
+            const int st = encode_tc8_launch(a);
+            if (st != TACVQ_ERR_UNSUPPORTED) return st;
         }
     }
     switch (a.D / a.G) {
