@@ -29,6 +29,10 @@
 
 #include "common.cuh"
 
+#ifndef TACVQ_TC_MINBLOCKS
+#define TACVQ_TC_MINBLOCKS 4  // resident blocks per SM the register budget is set for
+#endif
+
 namespace tacvq {
 
 constexpr int kTcThreads = 128;
@@ -89,7 +93,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 constexpr size_t kTcStageBytes = 4096 + 1024 + 8192 + 1024;
 
 template <typename XT>
-__global__ void __launch_bounds__(kTcThreads, 4)
+__global__ void __launch_bounds__(kTcThreads, TACVQ_TC_MINBLOCKS)
 encode_tc8_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const __half *__restrict__ tables,
                   const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
                   int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap) {

@@ -147,6 +147,49 @@ def test_encode_is_bit_exact_with_the_c_oracle(device, name, shape, dtype, stage
         assert torch.equal(recon.cpu(), ref_recon)
 
 
+@pytest.mark.parametrize("regime", ["ties", "midpoints", "tiny", "huge", "mixed_scale"])
+def test_filtered_search_is_exact_on_adversarial_rows(device, regime):
+    """8-wide groups go through the tensor-core filter; the exact re-evaluation must still decide every
+    tie, near tie and out-of-range row exactly like a full scan (the C oracle)."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(len(regime) * 131)
+    heads, groups, stages, tokens = 2, 16, 2, 700
+    tables = make_tables(gen, heads, stages, groups, 8)
+    dtype = torch.float32
+    if regime == "ties":
+        tables[:, :, :, 100:140] = tables[:, :, :, 20:60]        # duplicated words: the lower index must win
+        tables[:, :, :, 200] = -tables[:, :, :, 10]
+        pick = torch.randint(0, 256, (1, heads, tokens, groups), generator=gen)
+        states = torch.gather(
+            tables[:, 0].float().permute(0, 2, 1, 3)[None].expand(1, heads, 256, groups, 8), 2,
+            pick[..., None].expand(1, heads, tokens, groups, 8),
+        ).reshape(1, heads, tokens, 128)                          # rows that ARE codewords (distance 0)
+    elif regime == "midpoints":
+        first = tables[:, 0].float()                              # [H,G,256,8]
+        i = torch.randint(0, 256, (heads, groups, tokens), generator=gen)
+        j = torch.randint(0, 256, (heads, groups, tokens), generator=gen)
+        a = torch.gather(first, 2, i[..., None].expand(-1, -1, -1, 8))
+        b = torch.gather(first, 2, j[..., None].expand(-1, -1, -1, 8))
+        mid = 0.5 * (a + b) + torch.randn(heads, groups, tokens, 8, generator=gen) * 1e-6
+        states = mid.permute(0, 2, 1, 3).reshape(1, heads, tokens, 128)
+    elif regime == "tiny":
+        tables = (tables.float() * 1e-3).half()
+        states = make_states(gen, (1, heads, tokens, 128), dtype) * 1e-3
+    elif regime == "huge":
+        states = make_states(gen, (1, heads, tokens, 128), dtype) * 3.0e4   # beyond fp16: every word is re-evaluated
+        states[:, :, ::3] *= 1e-4
+    else:
+        scale = torch.logspace(-4, 3, tokens)[None, None, :, None]
+        states = make_states(gen, (1, heads, tokens, 128), dtype) * scale
+    states = states.to(dtype).contiguous()
+    want_codes, want_recon = C.encode(states, tables)
+    codes, recon = ops.encode(states.to(device), tables.to(device))
+    assert torch.equal(codes.cpu(), want_codes), int((codes.cpu() != want_codes).sum())
+    assert torch.equal(recon.cpu(), want_recon)
+    if regime == "ties":
+        assert not bool(((codes[:, :, :, 0] >= 100) & (codes[:, :, :, 0] < 140)).any())
+
+
 @pytest.mark.parametrize("tokens", [0, 1, 31, 33, 127, 129, 513])
 def test_ragged_token_counts_and_in_place_append(device, tokens):
     ops = _ops()
