@@ -21,6 +21,7 @@
 namespace tacvq {
 
 int encode_tc8_launch(const EncodeArgs &a);
+int encode_tc_large_launch(const EncodeArgs &a);
 
 // ------------------------------------------------------------------------------------------------
 // d <= 16
@@ -451,6 +452,10 @@ static int dispatch_d(const EncodeArgs &a) {
         }
         if (TACVQ_ENCODE_TC && a.D / a.G == 8) {
             const int st = encode_tc8_launch(a);
+            if (st != TACVQ_ERR_UNSUPPORTED) return st;
+        }
+        if (TACVQ_ENCODE_TC && a.D / a.G >= 32) {
+            const int st = encode_tc_large_launch(a);
             if (st != TACVQ_ERR_UNSUPPORTED) return st;
         }
     }

@@ -1,0 +1,357 @@
+// Encode for wide groups (d = 32, 64, 128; fp16 tables): tensor cores filter, exact fp32 decides.
+//
+// Same idea as the 8-wide kernel in encode_tc.cu, shaped as a block-level GEMM.  A block owns 128
+// rows of one (head, group).  Per stage it
+//   1. splits the fp32 residual tile into fp16 hi + lo tiles in shared memory,
+//   2. scores all 128 x 256 (row, word) pairs with mma.sync.m16n8k16 (fragments by ldmatrix; each of
+//      16 warps owns 32 rows x 64 words; the accumulators start at -|c|^2/2, so a score is
+//      t = r.c - |c|^2/2 and the distance is |r|^2 - 2t),
+//   3. takes the row maxima over the four word quarters and lists every pair whose score lies within
+//      a margin of its row's maximum,
+//   4. re-evaluates the listed pairs in the library's exact fp32 order (one 128-step FMA chain each,
+//      one pair per thread) and keeps the lowest (distance, index) per row with a 64-bit shared atomicMin,
+//   5. subtracts the chosen words from the fp32 residual tile.
+// The margin argument is the one in encode_tc.cu with d-dependent constants: the approximate and the
+// exact distance differ by at most about 2^-17 (|r|^2 + |c|^2) for d = 128 (hi/lo split 2^-22, sixteen
+// chained accumulations of sixteen exact products, the exact chain's own 128 roundings), the kernel
+// allows 2^-13 (|r|^2 + max |c|^2) plus 2^-17 sqrt(max |c|^2) for fp16 subnormals.  If the list
+// overflows, or a residual is too large for fp16, the block re-evaluates every pair of that stage:
+// slow, still exact.
+//
+// Reference statements: src/jointkv/closed_loop_vq.py:52-76 (search), :343-395 (stage recursion).
+
+#include "common.cuh"
+
+namespace tacvq {
+
+namespace {
+
+constexpr int kRows = 128;     // rows per block
+constexpr int kThreads = 512;  // 16 warps = 4 row blocks of 32 x 4 word quarters of 64
+constexpr int kListCap = 2048;
+
+template <int DSUB>
+struct TcLargeLayout {
+    static constexpr int kHalfStride = DSUB + 8;  // halves: 16-byte rows that land on distinct banks for ldmatrix
+    static constexpr int kResStride = DSUB + 4;   // floats
+    static constexpr size_t kTab = 0;                                                 // [256][kHalfStride] half
+    static constexpr size_t kHi = kTab + (size_t)kMaxWords * kHalfStride * 2;         // [kRows][kHalfStride] half
+    static constexpr size_t kLo = kHi + (size_t)kRows * kHalfStride * 2;              // [kRows][kHalfStride] half
+    static constexpr size_t kRes = kLo + (size_t)kRows * kHalfStride * 2;             // [kRows][kResStride] float
+    static constexpr size_t kNrm = kRes + (size_t)kRows * kResStride * 4;             // [256] float
+    static constexpr size_t kSeed = kNrm + kMaxWords * 4;                             // [256] float: -|c|^2/2
+    static constexpr size_t kXx = kSeed + kMaxWords * 4;                              // [kRows] float
+    static constexpr size_t kRowMax = kXx + kRows * 4;                                // [4][kRows] float
+    static constexpr size_t kThr = kRowMax + 4 * kRows * 4;                           // [kRows] float
+    static constexpr size_t kBest = kThr + kRows * 4;                                 // [kRows] u64
+    static constexpr size_t kList = kBest + kRows * 8;                                // [kListCap] u16
+    static constexpr size_t kMisc = kList + kListCap * 2;                             // count, big flag, cc_max
+    static constexpr size_t kHist = kMisc + 16;                                       // [kRows][S] u8
+    static constexpr size_t bytes(int S) { return kHist + (size_t)kRows * S; }
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *smem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_acc_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// monotone map float -> uint32 (total order of the values, -0 below +0)
+__device__ __forceinline__ uint32_t ordered_bits(float v) {
+    const uint32_t u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+}  // namespace
+
+template <int DSUB, typename XT>
+__global__ void __launch_bounds__(kThreads, 1)
+encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const __half *__restrict__ tables,
+                       const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
+                       int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap) {
+    using L = TcLargeLayout<DSUB>;
+    constexpr int HS = L::kHalfStride, RS = L::kResStride;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half *tab = reinterpret_cast<__half *>(smem_raw + L::kTab);
+    __half *hi = reinterpret_cast<__half *>(smem_raw + L::kHi);
+    __half *lo = reinterpret_cast<__half *>(smem_raw + L::kLo);
+    float *res = reinterpret_cast<float *>(smem_raw + L::kRes);
+    float *nrm = reinterpret_cast<float *>(smem_raw + L::kNrm);
+    float *seed = reinterpret_cast<float *>(smem_raw + L::kSeed);
+    float *xxs = reinterpret_cast<float *>(smem_raw + L::kXx);
+    float *rowmax = reinterpret_cast<float *>(smem_raw + L::kRowMax);
+    float *thr = reinterpret_cast<float *>(smem_raw + L::kThr);
+    unsigned long long *best = reinterpret_cast<unsigned long long *>(smem_raw + L::kBest);
+    uint16_t *list = reinterpret_cast<uint16_t *>(smem_raw + L::kList);
+    int *count = reinterpret_cast<int *>(smem_raw + L::kMisc);
+    int *big = count + 1;
+    float *cc_max = reinterpret_cast<float *>(count + 2);
+    uint8_t *hist = smem_raw + L::kHist;
+
+    const int hg = blockIdx.y;
+    const int h = hg / G, g = hg % G;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int gid = lane >> 2, q = lane & 3;
+    const int wr = warp >> 2, wq = warp & 3;  // row block (32 rows), word quarter (64 words)
+    const int64_t rows = (int64_t)B * T;
+    const int64_t tile = (int64_t)blockIdx.x * kRows;
+    const float inf = __int_as_float(0x7f800000);
+
+    for (int idx = tid; idx < kRows * DSUB; idx += kThreads) {
+        const int r = idx / DSUB, i = idx % DSUB;
+        const int64_t row = tile + r;
+        float v = 0.0f;
+        if (row < rows) {
+            const int64_t b = row / T, t = row % T;
+            v = to_float<XT>(x[b * sxb + (int64_t)h * sxh + t * sxt + (int64_t)g * DSUB + i]);
+        }
+        res[r * RS + i] = v;
+    }
+
+    for (int s = 0; s < S; ++s) {
+        __syncthreads();  // residual tile settled; the previous stage's table is no longer read
+        const __half *src = tables + (((int64_t)h * S + s) * G + g) * (int64_t)K * DSUB;
+        for (int idx = tid; idx < kMaxWords * (DSUB / 8); idx += kThreads) {
+            const int k = idx / (DSUB / 8), c = idx % (DSUB / 8);
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (k < K) v = *reinterpret_cast<const uint4 *>(src + (int64_t)k * DSUB + c * 8);
+            *reinterpret_cast<uint4 *>(tab + k * HS + c * 8) = v;
+        }
+        if (tid == 0) {
+            *count = 0;
+            *big = 0;
+        }
+        __syncthreads();
+        // hi/lo split of the residual tile, |r|^2 per row, |c|^2 per word
+        for (int idx = tid; idx < kRows * (DSUB / 2); idx += kThreads) {
+            const int r = idx / (DSUB / 2), i = (idx % (DSUB / 2)) * 2;
+            const float r0 = res[r * RS + i], r1 = res[r * RS + i + 1];
+            const __half h0 = __float2half_rn(r0), h1 = __float2half_rn(r1);
+            *reinterpret_cast<__half2 *>(hi + r * HS + i) = __halves2half2(h0, h1);
+            *reinterpret_cast<__half2 *>(lo + r * HS + i) =
+                __halves2half2(__float2half_rn(r0 - __half2float(h0)), __float2half_rn(r1 - __half2float(h1)));
+            if (!(fmaxf(fabsf(r0), fabsf(r1)) < 32768.0f)) *big = 1;
+        }
+        if (tid < kMaxWords) {
+            float v;
+            if (tid >= K) v = inf;  // padding words can never be chosen
+            else if (sqnorm_in != nullptr) v = sqnorm_in[(((int64_t)h * S + s) * G + g) * K + tid];
+            else v = sqnorm_ordered<DSUB>([&](int i) { return __half2float(tab[tid * HS + i]); });
+            nrm[tid] = v;
+            seed[tid] = -0.5f * v;
+        } else if (tid < kMaxWords + kRows) {
+            const int r = tid - kMaxWords;
+            xxs[r] = sqnorm_ordered<DSUB>([&](int i) { return res[r * RS + i]; });
+            best[r] = ~0ull;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            float top = 0.0f;
+            for (int k = lane; k < K; k += 32) top = fmaxf(top, nrm[k]);
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+            if (lane == 0) *cc_max = top;
+        }
+
+        // ---- approximate scores: 32 rows x 64 words per warp --------------------------------------
+        float acc[2][8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const float2 sv = *reinterpret_cast<const float2 *>(seed + wq * 64 + n * 8 + 2 * q);
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                acc[m][n][0] = sv.x;
+                acc[m][n][1] = sv.y;
+                acc[m][n][2] = sv.x;
+                acc[m][n][3] = sv.y;
+            }
+        }
+        {
+            // ldmatrix lane addresses: A tiles are [16 rows][16 k], B tiles [16 words][16 k] (two n-tiles)
+            const int a_row = wr * 32 + (lane & 15), a_col = (lane >> 4) * 8;
+            const int b_row = wq * 64 + (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+#pragma unroll 2
+            for (int ks = 0; ks < DSUB / 16; ++ks) {
+                uint32_t ahi[2][4], alo[2][4];
+#pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    ldmatrix_x4(ahi[m], hi + (a_row + m * 16) * HS + ks * 16 + a_col);
+                    ldmatrix_x4(alo[m], lo + (a_row + m * 16) * HS + ks * 16 + a_col);
+                }
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    uint32_t bw[4];
+                    ldmatrix_x4(bw, tab + (b_row + np * 16) * HS + ks * 16 + b_col);
+#pragma unroll
+                    for (int m = 0; m < 2; ++m) {
+                        mma_acc_16816(acc[m][2 * np], ahi[m], bw[0], bw[1]);
+                        mma_acc_16816(acc[m][2 * np], alo[m], bw[0], bw[1]);
+                        mma_acc_16816(acc[m][2 * np + 1], ahi[m], bw[2], bw[3]);
+                        mma_acc_16816(acc[m][2 * np + 1], alo[m], bw[2], bw[3]);
+                    }
+                }
+            }
+        }
+        // row maxima over this warp's 64 words
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float top = fmaxf(acc[m][0][2 * half], acc[m][0][2 * half + 1]);
+#pragma unroll
+                for (int n = 1; n < 8; ++n) top = fmaxf(top, fmaxf(acc[m][n][2 * half], acc[m][n][2 * half + 1]));
+                top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
+                top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
+                if (q == 0) rowmax[wq * kRows + wr * 32 + m * 16 + half * 8 + gid] = top;
+            }
+        }
+        __syncthreads();
+        if (tid < kRows) {
+            const float top = fmaxf(fmaxf(rowmax[tid], rowmax[kRows + tid]), fmaxf(rowmax[2 * kRows + tid], rowmax[3 * kRows + tid]));
+            // margin in units of t (half the distance margin): 2^-14 (xx + cc_max) + 2^-18 sqrt(cc_max)
+            const float margin = 6.103515625e-05f * (xxs[tid] + *cc_max) + 3.814697265625e-06f * sqrtf(*cc_max);
+            thr[tid] = (*big != 0) ? -inf : top - margin;
+        }
+        __syncthreads();
+        // list the pairs within the margin
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = wr * 32 + m * 16 + half * 8 + gid;
+                const float limit = thr[r];
+#pragma unroll
+                for (int n = 0; n < 8; ++n) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        if (acc[m][n][2 * half + e] >= limit) {
+                            const int slot = atomicAdd(count, 1);
+                            if (slot < kListCap) list[slot] = (uint16_t)((r << 8) | (wq * 64 + n * 8 + 2 * q + e));
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        // ---- exact re-evaluation ------------------------------------------------------------------
+        {
+            const int listed = *count;
+            const bool everything = listed > kListCap;
+            const int work = everything ? kRows * K : listed;
+            for (int i = tid; i < work; i += kThreads) {
+                int r, k;
+                if (everything) {
+                    r = i / K, k = i % K;
+                } else {
+                    const int entry = list[i];
+                    r = entry >> 8, k = entry & 255;
+                }
+                if (k >= K) continue;
+                const float *rv = res + r * RS;
+                const __half *cv = tab + k * HS;
+                float dot = 0.0f;
+#pragma unroll 4
+                for (int i8 = 0; i8 < DSUB; i8 += 8) {
+                    const uint4 cw = *reinterpret_cast<const uint4 *>(cv + i8);
+                    const __half2 *c2 = reinterpret_cast<const __half2 *>(&cw);
+                    const float4 r0 = *reinterpret_cast<const float4 *>(rv + i8);
+                    const float4 r1 = *reinterpret_cast<const float4 *>(rv + i8 + 4);
+                    float2 c;
+                    c = __half22float2(c2[0]);
+                    dot = __fmaf_rn(r0.x, c.x, dot);
+                    dot = __fmaf_rn(r0.y, c.y, dot);
+                    c = __half22float2(c2[1]);
+                    dot = __fmaf_rn(r0.z, c.x, dot);
+                    dot = __fmaf_rn(r0.w, c.y, dot);
+                    c = __half22float2(c2[2]);
+                    dot = __fmaf_rn(r1.x, c.x, dot);
+                    dot = __fmaf_rn(r1.y, c.y, dot);
+                    c = __half22float2(c2[3]);
+                    dot = __fmaf_rn(r1.z, c.x, dot);
+                    dot = __fmaf_rn(r1.w, c.y, dot);
+                }
+                const float dist = distance_expr(xxs[r], nrm[k], dot);
+                if (dist == dist) {  // a NaN distance never wins, as in a strict '<' scan
+                    const unsigned long long key = ((unsigned long long)ordered_bits(dist) << 32) | (unsigned)k;
+                    atomicMin(best + r, key);
+                }
+            }
+        }
+        __syncthreads();
+        // ---- update -------------------------------------------------------------------------------
+        for (int idx = tid; idx < kRows * DSUB; idx += kThreads) {
+            const int r = idx / DSUB, i = idx % DSUB;
+            const unsigned long long key = best[r];
+            const int pick = (key == ~0ull) ? 0 : (int)(key & 0xffffffffull);
+            res[r * RS + i] = __fsub_rn(res[r * RS + i], __half2float(tab[pick * HS + i]));
+        }
+        if (tid < kRows) {
+            const unsigned long long key = best[tid];
+            const int pick = (key == ~0ull) ? 0 : (int)(key & 0xffffffffull);
+            const int64_t row = tile + tid;
+            hist[tid * S + s] = (uint8_t)pick;
+            if (row < rows) {
+                const int64_t b = row / T, t = row % T;
+                codes[((((int64_t)b * H + h) * T_cap + t0 + t) * S + s) * G + g] = (uint8_t)pick;
+            }
+        }
+    }
+
+    if (recon != nullptr) {
+        __syncthreads();
+        for (int idx = tid; idx < kRows * DSUB; idx += kThreads) {
+            const int r = idx / DSUB, i = idx % DSUB;
+            const int64_t row = tile + r;
+            if (row >= rows) continue;
+            float sum = 0.0f;
+            for (int s = 0; s < S; ++s) {
+                const int code = hist[r * S + s];
+                sum = __fadd_rn(sum, __half2float(tables[((((int64_t)h * S + s) * G + g) * K + code) * DSUB + i]));
+            }
+            const int64_t b = row / T, t = row % T;
+            const int64_t o = (((int64_t)b * H + h) * T + t) * ((int64_t)G * DSUB) + (int64_t)g * DSUB + i;
+            if (recon_dtype == TACVQ_F16) store_as<__half>((__half *)recon + o, sum);
+            else store_as<float>((float *)recon + o, sum);
+        }
+    }
+}
+
+template <int DSUB>
+static int launch_tc_large(const EncodeArgs &a) {
+    const size_t smem = TcLargeLayout<DSUB>::bytes(a.S);
+    if (smem > 227 * 1024) return TACVQ_ERR_UNSUPPORTED;
+    const int64_t rows = (int64_t)a.B * a.T;
+    dim3 grid((unsigned)((rows + kRows - 1) / kRows), (unsigned)(a.H * a.G));
+    auto launch = [&](auto kernel, auto *xp) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        kernel<<<grid, kThreads, smem, a.stream>>>(xp, a.sxb, a.sxh, a.sxt, (const __half *)a.tables, a.sqnorm, a.codes,
+                                                   a.recon, a.recon_dtype, a.B, a.H, a.T, a.G, a.S, a.K, a.t0, a.T_cap);
+        return launch_status();
+    };
+    if (a.x_dtype == TACVQ_F16) return launch(encode_tc_large_kernel<DSUB, __half>, (const __half *)a.x);
+    return launch(encode_tc_large_kernel<DSUB, float>, (const float *)a.x);
+}
+
+// Returns TACVQ_ERR_UNSUPPORTED when the geometry is not this kernel's, so the caller can go on to
+// the scalar kernels.
+int encode_tc_large_launch(const EncodeArgs &a) {
+    if (a.tables_f32 || a.K > kMaxWords) return TACVQ_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(a.tables) & 15u) != 0) return TACVQ_ERR_UNSUPPORTED;
+    switch (a.D / a.G) {
+        case 32: return launch_tc_large<32>(a);
+        case 64: return launch_tc_large<64>(a);
+        case 128: return launch_tc_large<128>(a);
+        default: return TACVQ_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace tacvq

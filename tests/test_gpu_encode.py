@@ -147,30 +147,31 @@ def test_encode_is_bit_exact_with_the_c_oracle(device, name, shape, dtype, stage
         assert torch.equal(recon.cpu(), ref_recon)
 
 
+@pytest.mark.parametrize("sub", [8, 32, 128])
 @pytest.mark.parametrize("regime", ["ties", "midpoints", "tiny", "huge", "mixed_scale"])
-def test_filtered_search_is_exact_on_adversarial_rows(device, regime):
-    """8-wide groups go through the tensor-core filter; the exact re-evaluation must still decide every
-    tie, near tie and out-of-range row exactly like a full scan (the C oracle)."""
+def test_filtered_search_is_exact_on_adversarial_rows(device, regime, sub):
+    """8-wide and wide groups go through the tensor-core filters; the exact re-evaluation must still
+    decide every tie, near tie and out-of-range row exactly like a full scan (the C oracle)."""
     ops = _ops()
-    gen = torch.Generator().manual_seed(len(regime) * 131)
-    heads, groups, stages, tokens = 2, 16, 2, 700
-    tables = make_tables(gen, heads, stages, groups, 8)
+    gen = torch.Generator().manual_seed(len(regime) * 131 + sub)
+    heads, groups, stages, tokens = 2, 128 // sub, 2, 700 if sub == 8 else 300
+    tables = make_tables(gen, heads, stages, groups, sub, None if sub == 8 else [0.1, 0.05])
     dtype = torch.float32
     if regime == "ties":
         tables[:, :, :, 100:140] = tables[:, :, :, 20:60]        # duplicated words: the lower index must win
         tables[:, :, :, 200] = -tables[:, :, :, 10]
         pick = torch.randint(0, 256, (1, heads, tokens, groups), generator=gen)
         states = torch.gather(
-            tables[:, 0].float().permute(0, 2, 1, 3)[None].expand(1, heads, 256, groups, 8), 2,
-            pick[..., None].expand(1, heads, tokens, groups, 8),
+            tables[:, 0].float().permute(0, 2, 1, 3)[None].expand(1, heads, 256, groups, sub), 2,
+            pick[..., None].expand(1, heads, tokens, groups, sub),
         ).reshape(1, heads, tokens, 128)                          # rows that ARE codewords (distance 0)
     elif regime == "midpoints":
-        first = tables[:, 0].float()                              # [H,G,256,8]
+        first = tables[:, 0].float()                              # [H,G,256,sub]
         i = torch.randint(0, 256, (heads, groups, tokens), generator=gen)
         j = torch.randint(0, 256, (heads, groups, tokens), generator=gen)
-        a = torch.gather(first, 2, i[..., None].expand(-1, -1, -1, 8))
-        b = torch.gather(first, 2, j[..., None].expand(-1, -1, -1, 8))
-        mid = 0.5 * (a + b) + torch.randn(heads, groups, tokens, 8, generator=gen) * 1e-6
+        a = torch.gather(first, 2, i[..., None].expand(-1, -1, -1, sub))
+        b = torch.gather(first, 2, j[..., None].expand(-1, -1, -1, sub))
+        mid = 0.5 * (a + b) + torch.randn(heads, groups, tokens, sub, generator=gen) * 1e-6
         states = mid.permute(0, 2, 1, 3).reshape(1, heads, tokens, 128)
     elif regime == "tiny":
         tables = (tables.float() * 1e-3).half()
