@@ -2,21 +2,24 @@
 //
 // Same idea as the 8-wide kernel in encode_tc.cu, shaped as a block-level GEMM.  A block owns 128
 // rows of one (head, group).  Per stage it
-//   1. splits the fp32 residual tile into fp16 hi + lo tiles in shared memory,
+//   1. keeps, next to the fp32 residual tile, its fp16 rounding in shared memory,
 //   2. scores all 128 x 256 (row, word) pairs with mma.sync.m16n8k16 (fragments by ldmatrix; each of
 //      16 warps owns 32 rows x 64 words; the accumulators start at -|c|^2/2, so a score is
 //      t = r.c - |c|^2/2 and the distance is |r|^2 - 2t),
 //   3. takes the row maxima over the four word quarters and lists every pair whose score lies within
 //      a margin of its row's maximum,
-//   4. re-evaluates the listed pairs in the library's exact fp32 order (one 128-step FMA chain each,
+//   4. re-evaluates the listed pairs in the library's exact fp32 order (one d-step FMA chain each,
 //      one pair per thread) and keeps the lowest (distance, index) per row with a 64-bit shared atomicMin,
-//   5. subtracts the chosen words from the fp32 residual tile.
-// The margin argument is the one in encode_tc.cu with d-dependent constants: the approximate and the
-// exact distance differ by at most about 2^-17 (|r|^2 + |c|^2) for d = 128 (hi/lo split 2^-22, sixteen
-// chained accumulations of sixteen exact products, the exact chain's own 128 roundings), the kernel
-// allows 2^-13 (|r|^2 + max |c|^2) plus 2^-17 sqrt(max |c|^2) for fp16 subnormals.  If the list
-// overflows, or a residual is too large for fp16, the block re-evaluates every pair of that stage:
-// slow, still exact.
+//   5. subtracts the chosen words from the fp32 residual tile and refreshes the fp16 copy.
+//
+// Margin (see encode_tc.cu for the argument that a margin of twice the error bound keeps the exact
+// argmin and everything tied with it on the list).  The fp16 rounding of the residual changes a dot
+// product by at most 2^-11 sum |r_i c_i| <= 2^-11 |r| |c|; the tensor core's fp32 accumulation of the
+// exact products, the exact chain's own roundings and the roundings of the distance expression add at
+// most about 2^-17 (|r|^2 + |c|^2).  In units of t the kernel allows
+//   1.25 * 2^-10 |r| max|c|  +  2^-14 (|r|^2 + max|c|^2)  +  2^-18 max|c|   (fp16 subnormals).
+// On Gaussian data that lists about 1.07 words per row.  If the list overflows, or a residual is too
+// large for fp16, the block re-evaluates every pair of that stage: slow, still exact.
 //
 // Reference statements: src/jointkv/closed_loop_vq.py:52-76 (search), :343-395 (stage recursion).
 
@@ -34,19 +37,18 @@ template <int DSUB>
 struct TcLargeLayout {
     static constexpr int kHalfStride = DSUB + 8;  // halves: 16-byte rows that land on distinct banks for ldmatrix
     static constexpr int kResStride = DSUB + 4;   // floats
-    static constexpr size_t kTab = 0;                                                 // [256][kHalfStride] half
-    static constexpr size_t kHi = kTab + (size_t)kMaxWords * kHalfStride * 2;         // [kRows][kHalfStride] half
-    static constexpr size_t kLo = kHi + (size_t)kRows * kHalfStride * 2;              // [kRows][kHalfStride] half
-    static constexpr size_t kRes = kLo + (size_t)kRows * kHalfStride * 2;             // [kRows][kResStride] float
-    static constexpr size_t kNrm = kRes + (size_t)kRows * kResStride * 4;             // [256] float
-    static constexpr size_t kSeed = kNrm + kMaxWords * 4;                             // [256] float: -|c|^2/2
-    static constexpr size_t kXx = kSeed + kMaxWords * 4;                              // [kRows] float
-    static constexpr size_t kRowMax = kXx + kRows * 4;                                // [4][kRows] float
-    static constexpr size_t kThr = kRowMax + 4 * kRows * 4;                           // [kRows] float
-    static constexpr size_t kBest = kThr + kRows * 4;                                 // [kRows] u64
-    static constexpr size_t kList = kBest + kRows * 8;                                // [kListCap] u16
-    static constexpr size_t kMisc = kList + kListCap * 2;                             // count, big flag, cc_max
-    static constexpr size_t kHist = kMisc + 16;                                       // [kRows][S] u8
+    static constexpr size_t kTab = 0;                                              // [256][kHalfStride] half
+    static constexpr size_t kHi = kTab + (size_t)kMaxWords * kHalfStride * 2;      // [kRows][kHalfStride] half
+    static constexpr size_t kRes = kHi + (size_t)kRows * kHalfStride * 2;          // [kRows][kResStride] float
+    static constexpr size_t kNrm = kRes + (size_t)kRows * kResStride * 4;          // [256] float
+    static constexpr size_t kSeed = kNrm + kMaxWords * 4;                          // [256] float: -|c|^2/2
+    static constexpr size_t kXx = kSeed + kMaxWords * 4;                           // [kRows] float
+    static constexpr size_t kRowMax = kXx + kRows * 4;                             // [4][kRows] float
+    static constexpr size_t kThr = kRowMax + 4 * kRows * 4;                        // [kRows] float
+    static constexpr size_t kBest = kThr + kRows * 4;                              // [kRows] u64
+    static constexpr size_t kList = kBest + kRows * 8;                             // [kListCap] u16
+    static constexpr size_t kMisc = kList + kListCap * 2;                          // count, big flag, cc_max
+    static constexpr size_t kHist = kMisc + 16;                                    // [kRows][S] u8
     static constexpr size_t bytes(int S) { return kHist + (size_t)kRows * S; }
 };
 
@@ -69,6 +71,41 @@ __device__ __forceinline__ uint32_t ordered_bits(float v) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// |v|^2 of a d-vector (d a multiple of 32) by eight neighbouring lanes, in the library's order
+// (four sets of eight running sums: element i goes to set (i/8)%4, sum i%8; per sum the sets are added
+// ((0+1)+2)+3; the eight sums are added 0..7).  Lane j of the group owns sum j.  All eight return the total.
+template <int DSUB, typename Load>
+__device__ __forceinline__ float group8_sqnorm_ordered(Load at, int lane) {
+    const int j = lane & 7;
+    float set[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int i = 0; i < DSUB; i += 8) {
+        const float v = at(i + j);
+        set[(i >> 3) & 3] = __fadd_rn(set[(i >> 3) & 3], __fmul_rn(v, v));
+    }
+    const float mine = __fadd_rn(__fadd_rn(__fadd_rn(set[0], set[1]), set[2]), set[3]);
+    const int first = lane & 24;
+    float total = __shfl_sync(0xffffffffu, mine, first);
+#pragma unroll
+    for (int k = 1; k < 8; ++k) total = __fadd_rn(total, __shfl_sync(0xffffffffu, mine, first + k));
+    return total;
+}
+
+// eight consecutive residual elements -> fp32 tile and its fp16 rounding; returns max |element|
+__device__ __forceinline__ float store_residual8(float *res_at, __half *hi_at, const float (&v)[8]) {
+    *reinterpret_cast<float4 *>(res_at) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4 *>(res_at + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    __half2 h[4];
+    float top = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        top = fmaxf(top, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+    }
+    *reinterpret_cast<uint4 *>(hi_at) = *reinterpret_cast<const uint4 *>(h);
+    return top;
+}
+
 }  // namespace
 
 template <int DSUB, typename XT>
@@ -78,10 +115,10 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
                        int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap) {
     using L = TcLargeLayout<DSUB>;
     constexpr int HS = L::kHalfStride, RS = L::kResStride;
+    constexpr int kChunks = DSUB / 8;  // 8-element pieces per row
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half *tab = reinterpret_cast<__half *>(smem_raw + L::kTab);
     __half *hi = reinterpret_cast<__half *>(smem_raw + L::kHi);
-    __half *lo = reinterpret_cast<__half *>(smem_raw + L::kLo);
     float *res = reinterpret_cast<float *>(smem_raw + L::kRes);
     float *nrm = reinterpret_cast<float *>(smem_raw + L::kNrm);
     float *seed = reinterpret_cast<float *>(smem_raw + L::kSeed);
@@ -91,7 +128,7 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
     unsigned long long *best = reinterpret_cast<unsigned long long *>(smem_raw + L::kBest);
     uint16_t *list = reinterpret_cast<uint16_t *>(smem_raw + L::kList);
     int *count = reinterpret_cast<int *>(smem_raw + L::kMisc);
-    int *big = count + 1;
+    int *big = count + 1;  // some residual element of the coming stage does not fit fp16
     float *cc_max = reinterpret_cast<float *>(count + 2);
     uint8_t *hist = smem_raw + L::kHist;
 
@@ -105,52 +142,65 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
     const int64_t tile = (int64_t)blockIdx.x * kRows;
     const float inf = __int_as_float(0x7f800000);
 
-    for (int idx = tid; idx < kRows * DSUB; idx += kThreads) {
-        const int r = idx / DSUB, i = idx % DSUB;
+    uint8_t *code_at = nullptr;  // this row's first code byte (threads 0..kRows-1)
+    if (tid < kRows && tile + tid < rows) {
+        const int64_t row = tile + tid;
+        const int64_t b = row / T, t = row % T;
+        code_at = codes + (((int64_t)b * H + h) * T_cap + t0 + t) * ((int64_t)S * G) + g;
+    }
+    if (tid == 0) *big = 0;
+    __syncthreads();
+    for (int idx = tid; idx < kRows * kChunks; idx += kThreads) {
+        const int r = idx / kChunks, c8 = (idx % kChunks) * 8;
         const int64_t row = tile + r;
-        float v = 0.0f;
+        float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
         if (row < rows) {
             const int64_t b = row / T, t = row % T;
-            v = to_float<XT>(x[b * sxb + (int64_t)h * sxh + t * sxt + (int64_t)g * DSUB + i]);
+            const XT *src = x + b * sxb + (int64_t)h * sxh + t * sxt + (int64_t)g * DSUB + c8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = to_float<XT>(src[i]);
         }
-        res[r * RS + i] = v;
+        const float top = store_residual8(res + r * RS + c8, hi + r * HS + c8, v);
+        if (!(top < 32768.0f)) *big = 1;
     }
 
     for (int s = 0; s < S; ++s) {
-        __syncthreads();  // residual tile settled; the previous stage's table is no longer read
+        __syncthreads();  // residual tiles settled; the previous stage's table is no longer read
         const __half *src = tables + (((int64_t)h * S + s) * G + g) * (int64_t)K * DSUB;
-        for (int idx = tid; idx < kMaxWords * (DSUB / 8); idx += kThreads) {
-            const int k = idx / (DSUB / 8), c = idx % (DSUB / 8);
+        for (int idx = tid; idx < kMaxWords * kChunks; idx += kThreads) {
+            const int k = idx / kChunks, c = idx % kChunks;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (k < K) v = *reinterpret_cast<const uint4 *>(src + (int64_t)k * DSUB + c * 8);
             *reinterpret_cast<uint4 *>(tab + k * HS + c * 8) = v;
         }
-        if (tid == 0) {
-            *count = 0;
-            *big = 0;
-        }
+        if (tid == 0) *count = 0;
         __syncthreads();
-        // hi/lo split of the residual tile, |r|^2 per row, |c|^2 per word
-        for (int idx = tid; idx < kRows * (DSUB / 2); idx += kThreads) {
-            const int r = idx / (DSUB / 2), i = (idx % (DSUB / 2)) * 2;
-            const float r0 = res[r * RS + i], r1 = res[r * RS + i + 1];
-            const __half h0 = __float2half_rn(r0), h1 = __float2half_rn(r1);
-            *reinterpret_cast<__half2 *>(hi + r * HS + i) = __halves2half2(h0, h1);
-            *reinterpret_cast<__half2 *>(lo + r * HS + i) =
-                __halves2half2(__float2half_rn(r0 - __half2float(h0)), __float2half_rn(r1 - __half2float(h1)));
-            if (!(fmaxf(fabsf(r0), fabsf(r1)) < 32768.0f)) *big = 1;
-        }
-        if (tid < kMaxWords) {
-            float v;
-            if (tid >= K) v = inf;  // padding words can never be chosen
-            else if (sqnorm_in != nullptr) v = sqnorm_in[(((int64_t)h * S + s) * G + g) * K + tid];
-            else v = sqnorm_ordered<DSUB>([&](int i) { return __half2float(tab[tid * HS + i]); });
+        // |c|^2 per word and |r|^2 per row, one warp per vector
+        // (eight lanes per vector, four vectors per warp and trip, placed so that their loads miss each other's banks)
+        if (sqnorm_in == nullptr) {
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                const int k = warp * 16 + it * 4 + (lane >> 3);
+                float v = group8_sqnorm_ordered<DSUB>([&](int i) { return __half2float(tab[k * HS + i]); }, lane);
+                if (k >= K) v = inf;  // padding words can never be chosen
+                if ((lane & 7) == 0) {
+                    nrm[k] = v;
+                    seed[k] = -0.5f * v;
+                }
+            }
+        } else if (tid < kMaxWords) {
+            const float v = tid < K ? sqnorm_in[(((int64_t)h * S + s) * G + g) * K + tid] : inf;
             nrm[tid] = v;
             seed[tid] = -0.5f * v;
-        } else if (tid < kMaxWords + kRows) {
-            const int r = tid - kMaxWords;
-            xxs[r] = sqnorm_ordered<DSUB>([&](int i) { return res[r * RS + i]; });
-            best[r] = ~0ull;
+        }
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int r = warp * 8 + it + 2 * (lane >> 3);
+            const float v = group8_sqnorm_ordered<DSUB>([&](int i) { return res[r * RS + i]; }, lane);
+            if ((lane & 7) == 0) {
+                xxs[r] = v;
+                best[r] = ~0ull;
+            }
         }
         __syncthreads();
         if (warp == 0) {
@@ -180,22 +230,17 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
             const int b_row = wq * 64 + (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
 #pragma unroll 2
             for (int ks = 0; ks < DSUB / 16; ++ks) {
-                uint32_t ahi[2][4], alo[2][4];
+                uint32_t a[2][4];
 #pragma unroll
-                for (int m = 0; m < 2; ++m) {
-                    ldmatrix_x4(ahi[m], hi + (a_row + m * 16) * HS + ks * 16 + a_col);
-                    ldmatrix_x4(alo[m], lo + (a_row + m * 16) * HS + ks * 16 + a_col);
-                }
+                for (int m = 0; m < 2; ++m) ldmatrix_x4(a[m], hi + (a_row + m * 16) * HS + ks * 16 + a_col);
 #pragma unroll
                 for (int np = 0; np < 4; ++np) {
                     uint32_t bw[4];
                     ldmatrix_x4(bw, tab + (b_row + np * 16) * HS + ks * 16 + b_col);
 #pragma unroll
                     for (int m = 0; m < 2; ++m) {
-                        mma_acc_16816(acc[m][2 * np], ahi[m], bw[0], bw[1]);
-                        mma_acc_16816(acc[m][2 * np], alo[m], bw[0], bw[1]);
-                        mma_acc_16816(acc[m][2 * np + 1], ahi[m], bw[2], bw[3]);
-                        mma_acc_16816(acc[m][2 * np + 1], alo[m], bw[2], bw[3]);
+                        mma_acc_16816(acc[m][2 * np], a[m], bw[0], bw[1]);
+                        mma_acc_16816(acc[m][2 * np + 1], a[m], bw[2], bw[3]);
                     }
                 }
             }
@@ -216,26 +261,55 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
         __syncthreads();
         if (tid < kRows) {
             const float top = fmaxf(fmaxf(rowmax[tid], rowmax[kRows + tid]), fmaxf(rowmax[2 * kRows + tid], rowmax[3 * kRows + tid]));
-            // margin in units of t (half the distance margin): 2^-14 (xx + cc_max) + 2^-18 sqrt(cc_max)
-            const float margin = 6.103515625e-05f * (xxs[tid] + *cc_max) + 3.814697265625e-06f * sqrtf(*cc_max);
+            const float cm = *cc_max, xx = xxs[tid];
+            const float margin = 1.220703125e-03f * sqrtf(xx * cm) + 6.103515625e-05f * (xx + cm) + 3.814697265625e-06f * sqrtf(cm);
             thr[tid] = (*big != 0) ? -inf : top - margin;
         }
         __syncthreads();
-        // list the pairs within the margin
+        if (tid == 0) *big = 0;  // read above; the update below raises it for the next stage
+        // List the pairs within the margin.  Per row a thread shifts the sign of (score - limit) of its
+        // 16 words into a word (first word ends at bit 15, set = below the limit); one atomic per warp
+        // reserves the slots, then each thread walks its set bits.
+        {
+            uint32_t pass[2][2];
+            int hits = 0;
 #pragma unroll
-        for (int m = 0; m < 2; ++m) {
+            for (int m = 0; m < 2; ++m) {
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int r = wr * 32 + m * 16 + half * 8 + gid;
-                const float limit = thr[r];
+                for (int half = 0; half < 2; ++half) {
+                    const float limit = thr[wr * 32 + m * 16 + half * 8 + gid];
+                    uint32_t fail = 0u;
 #pragma unroll
-                for (int n = 0; n < 8; ++n) {
+                    for (int n = 0; n < 8; ++n) {
+                        fail = __funnelshift_l(__float_as_uint(acc[m][n][2 * half] - limit), fail, 1);
+                        fail = __funnelshift_l(__float_as_uint(acc[m][n][2 * half + 1] - limit), fail, 1);
+                    }
+                    pass[m][half] = ~fail & 0xffffu;
+                    hits += __popc(pass[m][half]);
+                }
+            }
+            int before = hits;  // inclusive prefix over the warp
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        if (acc[m][n][2 * half + e] >= limit) {
-                            const int slot = atomicAdd(count, 1);
-                            if (slot < kListCap) list[slot] = (uint16_t)((r << 8) | (wq * 64 + n * 8 + 2 * q + e));
-                        }
+            for (int off = 1; off < 32; off <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, before, off);
+                if (lane >= off) before += up;
+            }
+            int base = 0;
+            if (lane == 31 && before > 0) base = atomicAdd(count, before);
+            base = __shfl_sync(0xffffffffu, base, 31);
+            int slot = base + before - hits;
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t todo = pass[m][half];
+                    const int r = wr * 32 + m * 16 + half * 8 + gid;
+                    while (todo != 0u) {
+                        const int bit = 31 - __clz(todo);
+                        todo &= ~(1u << bit);
+                        const int pos = 15 - bit;  // n * 2 + e
+                        if (slot < kListCap) list[slot] = (uint16_t)((r << 8) | (wq * 64 + (pos >> 1) * 8 + 2 * q + (pos & 1)));
+                        ++slot;
                     }
                 }
             }
@@ -286,22 +360,27 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
             }
         }
         __syncthreads();
-        // ---- update -------------------------------------------------------------------------------
-        for (int idx = tid; idx < kRows * DSUB; idx += kThreads) {
-            const int r = idx / DSUB, i = idx % DSUB;
+        // ---- update: subtract the chosen words, refresh the fp16 copy -------------------------------
+        for (int idx = tid; idx < kRows * kChunks; idx += kThreads) {
+            const int r = idx / kChunks, c8 = (idx % kChunks) * 8;
             const unsigned long long key = best[r];
             const int pick = (key == ~0ull) ? 0 : (int)(key & 0xffffffffull);
-            res[r * RS + i] = __fsub_rn(res[r * RS + i], __half2float(tab[pick * HS + i]));
+            const uint4 cw = *reinterpret_cast<const uint4 *>(tab + pick * HS + c8);
+            const __half2 *c2 = reinterpret_cast<const __half2 *>(&cw);
+            const float4 r0 = *reinterpret_cast<const float4 *>(res + r * RS + c8);
+            const float4 r1 = *reinterpret_cast<const float4 *>(res + r * RS + c8 + 4);
+            const float2 w0 = __half22float2(c2[0]), w1 = __half22float2(c2[1]);
+            const float2 w2 = __half22float2(c2[2]), w3 = __half22float2(c2[3]);
+            const float v[8] = {__fsub_rn(r0.x, w0.x), __fsub_rn(r0.y, w0.y), __fsub_rn(r0.z, w1.x), __fsub_rn(r0.w, w1.y),
+                                __fsub_rn(r1.x, w2.x), __fsub_rn(r1.y, w2.y), __fsub_rn(r1.z, w3.x), __fsub_rn(r1.w, w3.y)};
+            const float top = store_residual8(res + r * RS + c8, hi + r * HS + c8, v);
+            if (!(top < 32768.0f)) *big = 1;
         }
         if (tid < kRows) {
             const unsigned long long key = best[tid];
             const int pick = (key == ~0ull) ? 0 : (int)(key & 0xffffffffull);
-            const int64_t row = tile + tid;
             hist[tid * S + s] = (uint8_t)pick;
-            if (row < rows) {
-                const int64_t b = row / T, t = row % T;
-                codes[((((int64_t)b * H + h) * T_cap + t0 + t) * S + s) * G + g] = (uint8_t)pick;
-            }
+            if (code_at != nullptr) code_at[(int64_t)s * G] = (uint8_t)pick;
         }
     }
 
