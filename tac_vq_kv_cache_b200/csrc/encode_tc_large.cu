@@ -48,7 +48,8 @@ struct TcLargeLayout {
     static constexpr size_t kBest = kThr + kRows * 4;                              // [kRows] u64
     static constexpr size_t kList = kBest + kRows * 8;                             // [kListCap] u16
     static constexpr size_t kMisc = kList + kListCap * 2;                          // count, big flag, cc_max
-    static constexpr size_t kHist = kMisc + 16;                                    // [kRows][S] u8
+    static constexpr size_t kRowCnt = kMisc + 16;                                  // [kRows] int: listed words per row
+    static constexpr size_t kHist = kRowCnt + kRows * 4;                           // [kRows][S] u8
     static constexpr size_t bytes(int S) { return kHist + (size_t)kRows * S; }
 };
 
@@ -91,19 +92,32 @@ __device__ __forceinline__ float group8_sqnorm_ordered(Load at, int lane) {
     return total;
 }
 
-// eight consecutive residual elements -> fp32 tile and its fp16 rounding; returns max |element|
-__device__ __forceinline__ float store_residual8(float *res_at, __half *hi_at, const float (&v)[8]) {
-    *reinterpret_cast<float4 *>(res_at) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4 *>(res_at + 4) = make_float4(v[4], v[5], v[6], v[7]);
-    __half2 h[4];
-    float top = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-        top = fmaxf(top, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+// four consecutive residual elements -> fp32 tile and its fp16 rounding; returns max |element|
+__device__ __forceinline__ float store_residual4(float *res_at, __half *hi_at, const float4 v) {
+    *reinterpret_cast<float4 *>(res_at) = v;
+    __half2 h[2] = {__floats2half2_rn(v.x, v.y), __floats2half2_rn(v.z, v.w)};
+    *reinterpret_cast<uint2 *>(hi_at) = *reinterpret_cast<const uint2 *>(h);
+    return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+}
+
+template <typename XT>
+__device__ __forceinline__ float4 load4(const XT *src, bool vec);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float *src, bool vec) {
+    if (vec) return *reinterpret_cast<const float4 *>(src);
+    return make_float4(src[0], src[1], src[2], src[3]);
+}
+template <>
+__device__ __forceinline__ float4 load4<__half>(const __half *src, bool vec) {
+    __half2 h[2];
+    if (vec) {
+        *reinterpret_cast<uint2 *>(h) = *reinterpret_cast<const uint2 *>(src);
+    } else {
+        h[0] = __halves2half2(src[0], src[1]);
+        h[1] = __halves2half2(src[2], src[3]);
     }
-    *reinterpret_cast<uint4 *>(hi_at) = *reinterpret_cast<const uint4 *>(h);
-    return top;
+    const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+    return make_float4(a.x, a.y, b.x, b.y);
 }
 
 }  // namespace
@@ -112,10 +126,11 @@ template <int DSUB, typename XT>
 __global__ void __launch_bounds__(kThreads, 1)
 encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const __half *__restrict__ tables,
                        const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
-                       int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap) {
+                       int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap, int vec_ok) {
     using L = TcLargeLayout<DSUB>;
     constexpr int HS = L::kHalfStride, RS = L::kResStride;
-    constexpr int kChunks = DSUB / 8;  // 8-element pieces per row
+    constexpr int kChunks = DSUB / 8;  // threads per row: each owns elements [4c, 4c+4) and [d/2 + 4c, d/2 + 4c + 4)
+    constexpr int kPass = kThreads / kChunks;  // rows per pass over the tile
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half *tab = reinterpret_cast<__half *>(smem_raw + L::kTab);
     __half *hi = reinterpret_cast<__half *>(smem_raw + L::kHi);
@@ -130,6 +145,7 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
     int *count = reinterpret_cast<int *>(smem_raw + L::kMisc);
     int *big = count + 1;  // some residual element of the coming stage does not fit fp16
     float *cc_max = reinterpret_cast<float *>(count + 2);
+    int *rowcnt = reinterpret_cast<int *>(smem_raw + L::kRowCnt);
     uint8_t *hist = smem_raw + L::kHist;
 
     const int hg = blockIdx.y;
@@ -138,30 +154,32 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
     const int lane = tid & 31, warp = tid >> 5;
     const int gid = lane >> 2, q = lane & 3;
     const int wr = warp >> 2, wq = warp & 3;  // row block (32 rows), word quarter (64 words)
-    const int64_t rows = (int64_t)B * T;
-    const int64_t tile = (int64_t)blockIdx.x * kRows;
+    const uint32_t rows = (uint32_t)B * (uint32_t)T;  // the launcher keeps B*T below 2^31
+    const uint32_t tile = blockIdx.x * kRows;
+    const int my_c = tid % kChunks, my_r = tid / kChunks;  // this thread's piece column and first row
     const float inf = __int_as_float(0x7f800000);
 
     uint8_t *code_at = nullptr;  // this row's first code byte (threads 0..kRows-1)
     if (tid < kRows && tile + tid < rows) {
-        const int64_t row = tile + tid;
-        const int64_t b = row / T, t = row % T;
+        const uint32_t row = tile + tid;
+        const uint32_t b = row / (uint32_t)T, t = row % (uint32_t)T;
         code_at = codes + (((int64_t)b * H + h) * T_cap + t0 + t) * ((int64_t)S * G) + g;
     }
     if (tid == 0) *big = 0;
     __syncthreads();
-    for (int idx = tid; idx < kRows * kChunks; idx += kThreads) {
-        const int r = idx / kChunks, c8 = (idx % kChunks) * 8;
-        const int64_t row = tile + r;
-        float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-        if (row < rows) {
-            const int64_t b = row / T, t = row % T;
-            const XT *src = x + b * sxb + (int64_t)h * sxh + t * sxt + (int64_t)g * DSUB + c8;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = to_float<XT>(src[i]);
+    for (int r = my_r; r < kRows; r += kPass) {
+        const uint32_t row = tile + r;
+        float4 v0 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), v1 = v0;
+        if (row < rows) {
+            const uint32_t b = row / (uint32_t)T, t = row % (uint32_t)T;
+            const XT *src = x + (int64_t)b * sxb + (int64_t)h * sxh + (int64_t)t * sxt + (int64_t)g * DSUB + 4 * my_c;
+            v0 = load4<XT>(src, vec_ok != 0);
+            v1 = load4<XT>(src + DSUB / 2, vec_ok != 0);
         }
-        const float top = store_residual8(res + r * RS + c8, hi + r * HS + c8, v);
-        if (!(top < 32768.0f)) *big = 1;
+        const float top0 = store_residual4(res + r * RS + 4 * my_c, hi + r * HS + 4 * my_c, v0);
+        const float top1 = store_residual4(res + r * RS + DSUB / 2 + 4 * my_c, hi + r * HS + DSUB / 2 + 4 * my_c, v1);
+        if (!(fmaxf(top0, top1) < 32768.0f)) *big = 1;
     }
 
     for (int s = 0; s < S; ++s) {
@@ -200,6 +218,7 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
             if ((lane & 7) == 0) {
                 xxs[r] = v;
                 best[r] = ~0ull;
+                rowcnt[r] = 0;
             }
         }
         __syncthreads();
@@ -310,6 +329,7 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
                         const int pos = 15 - bit;  // n * 2 + e
                         if (slot < kListCap) list[slot] = (uint16_t)((r << 8) | (wq * 64 + (pos >> 1) * 8 + 2 * q + (pos & 1)));
                         ++slot;
+                        atomicAdd(rowcnt + r, 1);
                     }
                 }
             }
@@ -329,6 +349,10 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
                     r = entry >> 8, k = entry & 255;
                 }
                 if (k >= K) continue;
+                if (!everything && rowcnt[r] == 1) {  // the only word within the margin is the argmin
+                    best[r] = (unsigned long long)k;
+                    continue;
+                }
                 const float *rv = res + r * RS;
                 const __half *cv = tab + k * HS;
                 float dot = 0.0f;
@@ -361,19 +385,21 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
         }
         __syncthreads();
         // ---- update: subtract the chosen words, refresh the fp16 copy -------------------------------
-        for (int idx = tid; idx < kRows * kChunks; idx += kThreads) {
-            const int r = idx / kChunks, c8 = (idx % kChunks) * 8;
+#pragma unroll
+        for (int r = my_r; r < kRows; r += kPass) {
             const unsigned long long key = best[r];
             const int pick = (key == ~0ull) ? 0 : (int)(key & 0xffffffffull);
-            const uint4 cw = *reinterpret_cast<const uint4 *>(tab + pick * HS + c8);
-            const __half2 *c2 = reinterpret_cast<const __half2 *>(&cw);
-            const float4 r0 = *reinterpret_cast<const float4 *>(res + r * RS + c8);
-            const float4 r1 = *reinterpret_cast<const float4 *>(res + r * RS + c8 + 4);
-            const float2 w0 = __half22float2(c2[0]), w1 = __half22float2(c2[1]);
-            const float2 w2 = __half22float2(c2[2]), w3 = __half22float2(c2[3]);
-            const float v[8] = {__fsub_rn(r0.x, w0.x), __fsub_rn(r0.y, w0.y), __fsub_rn(r0.z, w1.x), __fsub_rn(r0.w, w1.y),
-                                __fsub_rn(r1.x, w2.x), __fsub_rn(r1.y, w2.y), __fsub_rn(r1.z, w3.x), __fsub_rn(r1.w, w3.y)};
-            const float top = store_residual8(res + r * RS + c8, hi + r * HS + c8, v);
+            float top = 0.0f;
+#pragma unroll
+            for (int piece = 0; piece < 2; ++piece) {
+                const int at = piece * (DSUB / 2) + 4 * my_c;
+                __half2 c2[2];
+                *reinterpret_cast<uint2 *>(c2) = *reinterpret_cast<const uint2 *>(tab + pick * HS + at);
+                const float4 rv = *reinterpret_cast<const float4 *>(res + r * RS + at);
+                const float2 w0 = __half22float2(c2[0]), w1 = __half22float2(c2[1]);
+                const float4 nv = make_float4(__fsub_rn(rv.x, w0.x), __fsub_rn(rv.y, w0.y), __fsub_rn(rv.z, w1.x), __fsub_rn(rv.w, w1.y));
+                top = fmaxf(top, store_residual4(res + r * RS + at, hi + r * HS + at, nv));
+            }
             if (!(top < 32768.0f)) *big = 1;
         }
         if (tid < kRows) {
@@ -386,19 +412,32 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
 
     if (recon != nullptr) {
         __syncthreads();
-        for (int idx = tid; idx < kRows * DSUB; idx += kThreads) {
-            const int r = idx / DSUB, i = idx % DSUB;
-            const int64_t row = tile + r;
+        const int64_t stage_words = (int64_t)G * K * DSUB;
+#pragma unroll
+        for (int r = my_r; r < kRows; r += kPass) {
+            const uint32_t row = tile + r;
             if (row >= rows) continue;
-            float sum = 0.0f;
-            for (int s = 0; s < S; ++s) {
-                const int code = hist[r * S + s];
-                sum = __fadd_rn(sum, __half2float(tables[((((int64_t)h * S + s) * G + g) * K + code) * DSUB + i]));
+            const uint32_t b = row / (uint32_t)T, t = row % (uint32_t)T;
+#pragma unroll
+            for (int piece = 0; piece < 2; ++piece) {
+                const int at = piece * (DSUB / 2) + 4 * my_c;
+                const __half *words = tables + ((int64_t)h * S * G + g) * (int64_t)K * DSUB + at;
+                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int s = 0; s < S; ++s) {
+                    __half2 c2[2];
+                    *reinterpret_cast<uint2 *>(c2) =
+                        *reinterpret_cast<const uint2 *>(words + s * stage_words + (int64_t)hist[r * S + s] * DSUB);
+                    const float2 w0 = __half22float2(c2[0]), w1 = __half22float2(c2[1]);
+                    sum = make_float4(__fadd_rn(sum.x, w0.x), __fadd_rn(sum.y, w0.y), __fadd_rn(sum.z, w1.x), __fadd_rn(sum.w, w1.y));
+                }
+                const int64_t o = (((int64_t)b * H + h) * T + t) * ((int64_t)G * DSUB) + (int64_t)g * DSUB + at;
+                if (recon_dtype == TACVQ_F16) {
+                    __half2 out[2] = {__floats2half2_rn(sum.x, sum.y), __floats2half2_rn(sum.z, sum.w)};
+                    *reinterpret_cast<uint2 *>((__half *)recon + o) = *reinterpret_cast<const uint2 *>(out);
+                } else {
+                    *reinterpret_cast<float4 *>((float *)recon + o) = sum;
+                }
             }
-            const int64_t b = row / T, t = row % T;
-            const int64_t o = (((int64_t)b * H + h) * T + t) * ((int64_t)G * DSUB) + (int64_t)g * DSUB + i;
-            if (recon_dtype == TACVQ_F16) store_as<__half>((__half *)recon + o, sum);
-            else store_as<float>((float *)recon + o, sum);
         }
     }
 }
@@ -408,12 +447,17 @@ static int launch_tc_large(const EncodeArgs &a) {
     const size_t smem = TcLargeLayout<DSUB>::bytes(a.S);
     if (smem > 227 * 1024) return TACVQ_ERR_UNSUPPORTED;
     const int64_t rows = (int64_t)a.B * a.T;
+    if (rows >= (int64_t)1 << 31) return TACVQ_ERR_UNSUPPORTED;
+    if (a.recon != nullptr && (reinterpret_cast<uintptr_t>(a.recon) & 15u) != 0) return TACVQ_ERR_UNSUPPORTED;
+    // 4-element vector loads of the states need an aligned base and strides that keep the alignment
+    const size_t elem = a.x_dtype == TACVQ_F16 ? 2 : 4;
+    const int vec_ok = (reinterpret_cast<uintptr_t>(a.x) % (4 * elem) == 0 && a.sxb % 4 == 0 && a.sxh % 4 == 0 && a.sxt % 4 == 0) ? 1 : 0;
     dim3 grid((unsigned)((rows + kRows - 1) / kRows), (unsigned)(a.H * a.G));
     auto launch = [&](auto kernel, auto *xp) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         kernel<<<grid, kThreads, smem, a.stream>>>(xp, a.sxb, a.sxh, a.sxt, (const __half *)a.tables, a.sqnorm, a.codes,
-                                                   a.recon, a.recon_dtype, a.B, a.H, a.T, a.G, a.S, a.K, a.t0, a.T_cap);
+                                                   a.recon, a.recon_dtype, a.B, a.H, a.T, a.G, a.S, a.K, a.t0, a.T_cap, vec_ok);
         return launch_status();
     };
     if (a.x_dtype == TACVQ_F16) return launch(encode_tc_large_kernel<DSUB, __half>, (const __half *)a.x);

@@ -78,6 +78,9 @@ def table_sqnorm(tables_f16: torch.Tensor) -> torch.Tensor:
     return out
 
 
+_word_norms = table_sqnorm  # encode() has a keyword argument of the same name
+
+
 def encode(
     states: torch.Tensor,
     tables_f16: torch.Tensor,
@@ -108,6 +111,9 @@ def encode(
         raise ValueError("codes must be contiguous uint8 [B,H,T_cap,S,G]")
     recon = torch.empty(b, h, t, dim, dtype=states.dtype, device=device) if want_recon else None
     lib = _lib.load()
+    if whitener is None and table_sqnorm is None and d >= 32 and b * t > 256:
+        # wide groups: one small launch for |c|^2 instead of every 128-row block recomputing them
+        table_sqnorm = _word_norms(tables_f16)
     with _on(device):
         if whitener is None:
             status = lib.tacvq_encode(
