@@ -80,10 +80,17 @@ TACVQ_API int tacvq_table_sqnorm(const uint16_t *tables_f16, float *out, int64_t
  *                      base and strides such that every row starts 16-byte aligned
  *   tables_f16         [H,S,G,K,d]
  *   table_sqnorm       NULL (computed inside) or [H,S,G,K] fp32 supplied by the caller
+ *                      (tacvq_table_sqnorm); for d >= 32 supplying it saves every 128-row block
+ *                      from recomputing the norms of its 256 words
  *   codes              [B,H,T_cap,S,G]; rows t0 .. t0+T-1 are written, the rest is untouched
  *   recon, recon_dtype NULL, or [B,H,T,D] contiguous receiving sum_s word_s (fp32 sum in stage
  *                      order, one final cast) - the reference's exit at depth S
  *   d = D/G must be one of 1..8, 16, 32, 64, 128.
+ *
+ * The codes are those of a full scan in the library's fp32 order (first minimum wins).  For
+ * d = 4, 8, 32, 64, 128 with 16-byte aligned tables the scan is filtered: tensor cores score every
+ * word, and only the words within a proven error margin of a row's best score are re-evaluated in
+ * that exact order, which cannot change the result.
  */
 TACVQ_API int tacvq_encode(const void *x, int x_dtype, int64_t sxb, int64_t sxh, int64_t sxt, const uint16_t *tables_f16,
                  const float *table_sqnorm, uint8_t *codes, void *recon, int recon_dtype, int B, int H, int T, int D,

@@ -450,7 +450,7 @@ static int dispatch_d(const EncodeArgs &a) {
                 default: break;
             }
         }
-        if (TACVQ_ENCODE_TC && a.D / a.G == 8) {
+        if (TACVQ_ENCODE_TC && (a.D / a.G == 8 || a.D / a.G == 4)) {
             const int st = encode_tc8_launch(a);
             if (st != TACVQ_ERR_UNSUPPORTED) return st;
         }

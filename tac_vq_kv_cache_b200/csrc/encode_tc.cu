@@ -1,4 +1,4 @@
-// Encode for 8-wide groups (d = 8, fp16 tables): tensor cores filter, exact fp32 decides.
+// Encode for 8-wide and 4-wide groups (fp16 tables): tensor cores filter, exact fp32 decides.
 //
 // The exact distance that decides a code costs about 16 instructions in the scalar kernel.  Here a
 // warp scores 16 rows against all 256 words of a stage with 32 mma.sync.m16n8k16 instructions that
@@ -92,7 +92,10 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // and after all stages {cc_max, slack} per stage.
 constexpr size_t kTcStageBytes = 4096 + 1024 + 8192 + 1024;
 
-template <typename XT>
+// DSUB = 8, or 4 run as 8 with the upper four elements of rows and words held at zero: appending zeros
+// changes neither the FMA chain of a dot product nor the left-to-right sum of squares, so the codes
+// are those of a 4-wide scan.
+template <int DSUB, typename XT>
 __global__ void __launch_bounds__(kTcThreads, TACVQ_TC_MINBLOCKS)
 encode_tc8_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const __half *__restrict__ tables,
                   const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
@@ -117,12 +120,17 @@ encode_tc8_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sx
         float cc = __int_as_float(0x7f800000);  // padding words can never be chosen
         if (k < K) {
             const int64_t word = (((int64_t)h * S + s) * G + g) * K + k;
-            w = *reinterpret_cast<const uint4 *>(tables + word * 8);
+            if constexpr (DSUB == 8) {
+                w = *reinterpret_cast<const uint4 *>(tables + word * 8);
+            } else {
+                const uint2 half_word = *reinterpret_cast<const uint2 *>(tables + word * 4);
+                w = make_uint4(half_word.x, half_word.y, 0u, 0u);
+            }
             if (sqnorm_in != nullptr) {
                 cc = sqnorm_in[word];
             } else {
                 const __half *e = reinterpret_cast<const __half *>(&w);
-                cc = sqnorm_ordered<8>([&](int i) { return __half2float(e[i]); });
+                cc = sqnorm_ordered<DSUB>([&](int i) { return __half2float(e[i]); });
             }
         }
         const int tile = k >> 3, col = k & 7;  // word k is column col of tile `tile`
@@ -159,9 +167,9 @@ encode_tc8_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sx
     // rows of this lane's quad in the current tile: `a` = gid, `b` = gid + 8; elements 2q, 2q+1
     auto fetch = [&](uint32_t row, float (&r)[2]) {
         r[0] = r[1] = 0.0f;
-        if (row < rows) {
+        if (row < rows && 2 * q < DSUB) {
             const uint32_t b = row / (uint32_t)T, t = row % (uint32_t)T;
-            const XT *src = x + (int64_t)b * sxb + (int64_t)h * sxh + (int64_t)t * sxt + g * 8 + 2 * q;
+            const XT *src = x + (int64_t)b * sxb + (int64_t)h * sxh + (int64_t)t * sxt + g * DSUB + 2 * q;
             r[0] = to_float<XT>(src[0]);
             r[1] = to_float<XT>(src[1]);
         }
@@ -314,9 +322,9 @@ encode_tc8_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sx
             }
         }
 
-        if (recon != nullptr) {
+        if (recon != nullptr && 2 * q < DSUB) {
             if (live_a) {
-                const int64_t o = (((int64_t)ba * H + h) * T + ta) * ((int64_t)G * 8) + g * 8 + 2 * q;
+                const int64_t o = (((int64_t)ba * H + h) * T + ta) * ((int64_t)G * DSUB) + g * DSUB + 2 * q;
                 if (recon_dtype == TACVQ_F16) {
                     *reinterpret_cast<uint32_t *>((__half *)recon + o) = pack_half2(da[0], da[1]);
                 } else {
@@ -324,7 +332,7 @@ encode_tc8_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sx
                 }
             }
             if (live_b) {
-                const int64_t o = (((int64_t)bb * H + h) * T + tb) * ((int64_t)G * 8) + g * 8 + 2 * q;
+                const int64_t o = (((int64_t)bb * H + h) * T + tb) * ((int64_t)G * DSUB) + g * DSUB + 2 * q;
                 if (recon_dtype == TACVQ_F16) {
                     *reinterpret_cast<uint32_t *>((__half *)recon + o) = pack_half2(db[0], db[1]);
                 } else {
@@ -339,7 +347,8 @@ encode_tc8_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sx
 // Returns TACVQ_ERR_UNSUPPORTED when the geometry is not this kernel's, so the caller can go on to
 // the scalar kernels.
 int encode_tc8_launch(const EncodeArgs &a) {
-    if (a.tables_f32 || a.D / a.G != 8 || a.K > kMaxWords) return TACVQ_ERR_UNSUPPORTED;
+    const int sub = a.D / a.G;
+    if (a.tables_f32 || (sub != 8 && sub != 4) || a.K > kMaxWords) return TACVQ_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a.tables) & 15u) != 0) return TACVQ_ERR_UNSUPPORTED;
     if (a.recon != nullptr && (reinterpret_cast<uintptr_t>(a.recon) & 7u) != 0) return TACVQ_ERR_UNSUPPORTED;
     const size_t smem = (size_t)a.S * kTcStageBytes + (size_t)a.S * 2 * sizeof(float);
@@ -360,8 +369,12 @@ int encode_tc8_launch(const EncodeArgs &a) {
                                                      a.recon, a.recon_dtype, a.B, a.H, a.T, a.G, a.S, a.K, a.t0, a.T_cap);
         return launch_status();
     };
-    if (a.x_dtype == TACVQ_F16) return launch(encode_tc8_kernel<__half>, (const __half *)a.x);
-    return launch(encode_tc8_kernel<float>, (const float *)a.x);
+    if (sub == 8) {
+        if (a.x_dtype == TACVQ_F16) return launch(encode_tc8_kernel<8, __half>, (const __half *)a.x);
+        return launch(encode_tc8_kernel<8, float>, (const float *)a.x);
+    }
+    if (a.x_dtype == TACVQ_F16) return launch(encode_tc8_kernel<4, __half>, (const __half *)a.x);
+    return launch(encode_tc8_kernel<4, float>, (const float *)a.x);
 }
 
 }  // namespace tacvq

@@ -147,15 +147,15 @@ def test_encode_is_bit_exact_with_the_c_oracle(device, name, shape, dtype, stage
         assert torch.equal(recon.cpu(), ref_recon)
 
 
-@pytest.mark.parametrize("sub", [8, 32, 128])
+@pytest.mark.parametrize("sub", [4, 8, 32, 128])
 @pytest.mark.parametrize("regime", ["ties", "midpoints", "tiny", "huge", "mixed_scale"])
 def test_filtered_search_is_exact_on_adversarial_rows(device, regime, sub):
     """8-wide and wide groups go through the tensor-core filters; the exact re-evaluation must still
     decide every tie, near tie and out-of-range row exactly like a full scan (the C oracle)."""
     ops = _ops()
     gen = torch.Generator().manual_seed(len(regime) * 131 + sub)
-    heads, groups, stages, tokens = 2, 128 // sub, 2, 700 if sub == 8 else 300
-    tables = make_tables(gen, heads, stages, groups, sub, None if sub == 8 else [0.1, 0.05])
+    heads, groups, stages, tokens = 2, 128 // sub, 2, 700 if sub <= 8 else 300
+    tables = make_tables(gen, heads, stages, groups, sub, None if sub <= 8 else [0.1, 0.05])
     dtype = torch.float32
     if regime == "ties":
         tables[:, :, :, 100:140] = tables[:, :, :, 20:60]        # duplicated words: the lower index must win
@@ -224,6 +224,31 @@ def test_strided_states_and_small_codebooks(device):
     codes, recon = ops.encode(view.contiguous().to(device), small.to(device))
     assert torch.equal(codes.cpu(), want) and torch.equal(recon.cpu(), want_recon)
     assert int(codes.max()) < 37
+
+
+@pytest.mark.parametrize("sub,groups", [(128, 1), (64, 2), (32, 4)])
+def test_wide_groups_strided_states_small_codebooks_and_in_place_rows(device, sub, groups):
+    """The block-level kernel for wide groups: strided rows, K < 256, a ragged last tile, rows written
+    at an offset of a larger code cache, fp16 and fp32 states, with and without caller-supplied norms."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(sub)
+    heads, stages, tokens = 2, 3, 333
+    raw = make_states(gen, (2, tokens, heads, 128), torch.float32)   # [B,T,H,D] viewed as [B,H,T,D]
+    view = raw.transpose(1, 2)
+    tables = make_tables(gen, heads, stages, groups, sub, [0.1, 0.05, 0.025])[:, :, :, :201].contiguous()
+    want, want_recon = C.encode(view.contiguous(), tables)
+    cache = torch.full((2, heads, tokens + 9, stages, groups), 0xCD, dtype=torch.uint8, device=device)
+    codes, recon = ops.encode(raw.to(device).transpose(1, 2), tables.to(device), codes=cache, t0=4)
+    assert torch.equal(cache[:, :, 4 : 4 + tokens].cpu(), want) and torch.equal(recon.cpu(), want_recon)
+    assert bool((cache[:, :, :4] == 0xCD).all()) and bool((cache[:, :, 4 + tokens :] == 0xCD).all())
+    assert int(cache[:, :, 4 : 4 + tokens].max()) < 201
+    norms = ops.table_sqnorm(tables.to(device))
+    half_states = view.contiguous().half()
+    want16, want16_recon = C.encode(half_states, tables)
+    a, ra = ops.encode(half_states.to(device), tables.to(device))
+    b, rb = ops.encode(half_states.to(device), tables.to(device), table_sqnorm=norms)
+    assert torch.equal(a.cpu(), want16) and torch.equal(a, b)
+    assert torch.equal(ra.cpu(), want16_recon) and torch.equal(ra, rb)
 
 
 def test_caller_supplied_table_norms_and_own_norm_kernel(device):
