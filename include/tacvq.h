@@ -225,6 +225,37 @@ TACVQ_API int tacvq_attn_decode_static(const uint16_t *q_f16, const uint8_t *kco
 TACVQ_API int tacvq_attn_combine(const float *states, int n_parts, uint16_t *out_f16, float *merged, int B, int Hq, int D,
                        tacvq_stream_t stream);
 
+/*
+ * cos/sin table of the rotary position embedding, table[t][i] = (cos, sin)((first_position + t) *
+ * theta^(-2i/D)) as fp16 pairs, i < D/2: inverse frequencies, angles and cos/sin in fp32, one rounding
+ * to fp16.  Replaces `self.rotary_emb(visible_k, all_positions)` of the reference's decode branch
+ * (experiments_followup_mistral/evaluate_mistral_longbench.py:115-117; default rope type of
+ * transformers' MistralRotaryEmbedding).  A caller that has its model's own cos/sin may fill the
+ * table itself.
+ *
+ *   table_half2        [T][D/2] pairs of fp16 (cos in the low half), 4-byte aligned;  D <= 256, D even
+ */
+TACVQ_API int tacvq_rope_table(uint32_t *table_half2, int64_t T, int D, double theta, int64_t first_position,
+                               tacvq_stream_t stream);
+
+/*
+ * tacvq_attn_decode for codes of PRE-rotary keys, as the reference stores them: every rebuilt fp16
+ * key row t is rotated with rope_table[t] ("rotate_half" pairing of channel c with c +- D/2;
+ * k*cos + rotate_half(k)*sin with fp16 products and sum, as apply_rotary_pos_emb does on the fp16
+ * window) before its dot product with q.  Replaces evaluate_mistral_longbench.py:112-122 including
+ * the rotary step (:113-118).
+ *
+ *   q_f16              [B,Hq,D] fp16, already rotated at the query's own position and multiplied by
+ *                      the softmax scale
+ *   rope_table         [T_cap][D/2] from tacvq_rope_table (row index = token index in the code buffers)
+ *   other arguments, workspace size and results as for tacvq_attn_decode; D in {64, 128, 256}.
+ */
+TACVQ_API int tacvq_attn_decode_rotary(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_t *vcodes,
+                                       const uint16_t *ktab_f16, const uint16_t *vtab_f16, const uint32_t *rope_table,
+                                       const int32_t *seq_start, const int32_t *seq_end, void *workspace,
+                                       size_t workspace_bytes, uint16_t *out_f16, float *state_out, int B, int Hq,
+                                       int Hkv, int D, int G, int S, int K, int64_t T_cap, tacvq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

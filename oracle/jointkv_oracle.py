@@ -268,6 +268,29 @@ def visible_range(length: int, window: int | None) -> tuple[int, int]:
     return max(0, length - window), length
 
 
+def rotary_table(tokens: int, dim: int, theta: float, first_position: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(cos, sin)`` fp16 ``[tokens, dim/2]`` of positions ``first_position ..``: the values the
+    reference gets from ``self.rotary_emb(visible_k, all_positions)``
+    (experiments_followup_mistral/evaluate_mistral_longbench.py:116-117; the default rope of
+    transformers' MistralRotaryEmbedding: ``inv_freq = theta ** -(arange(0, dim, 2) / dim)``,
+    angles and cos/sin in fp32, one cast to the states' dtype)."""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.int64).float() / dim))
+    angles = (first_position + torch.arange(tokens)).float()[:, None] * inv_freq[None, :]
+    return angles.cos().half(), angles.sin().half()
+
+
+def apply_rotary_fp16(rows: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """``rows [..., T, D]`` fp16 rotated by ``cos/sin [T, D/2]`` exactly as ``apply_rotary_pos_emb`` of
+    transformers' Mistral model does on an fp16 tensor: ``x*cos + rotate_half(x)*sin`` with
+    ``rotate_half(x) = cat(-x[D/2:], x[:D/2])``, every product and the sum rounded to fp16
+    (call site: evaluate_mistral_longbench.py:118)."""
+    half = rows.shape[-1] // 2
+    cos_full = torch.cat([cos, cos], dim=-1)
+    sin_full = torch.cat([sin, sin], dim=-1)
+    rotated = torch.cat([-rows[..., half:], rows[..., :half]], dim=-1)
+    return (rows * cos_full) + (rotated * sin_full)
+
+
 def attention_over_codes(
     query: torch.Tensor,
     key_codes: torch.Tensor,
@@ -276,12 +299,15 @@ def attention_over_codes(
     value_tables: torch.Tensor,
     seq_start: Iterable[int] | None = None,
     seq_end: Iterable[int] | None = None,
+    rope_theta: float | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """One decode step of attention with K and V held as codes.
 
     ``query [B,Hq,D]`` (already scaled), codes ``[B,Hkv,T,S,G]``, tables
-    ``[Hkv,S,G,K,d]``.  Semantics of the reference decode branch without the
-    rotary step: rebuild K and V as fp16 (what the reference keeps in its
+    ``[Hkv,S,G,K,d]``.  Semantics of the reference decode branch
+    (evaluate_mistral_longbench.py:112-122), by default without its rotary step; with
+    ``rope_theta`` the rebuilt fp16 key window is rotated like the reference does (``query`` is then
+    the query already rotated at its own position): rebuild K and V as fp16 (what the reference keeps in its
     decoded window), repeat each KV head for its ``Hq/Hkv`` query heads,
     ``softmax(q K^T) V`` in fp32 over ``[seq_start[b], seq_end[b])``.
 
@@ -293,7 +319,10 @@ def attention_over_codes(
     kv_heads = int(key_codes.shape[1])
     tokens = int(key_codes.shape[2])
     rep = q_heads // kv_heads
-    keys = reconstruct(key_codes, key_tables, torch.float16).float()
+    keys = reconstruct(key_codes, key_tables, torch.float16)
+    if rope_theta is not None:  # codes hold pre-rotary keys: rotate row t at absolute position t
+        keys = apply_rotary_fp16(keys, *rotary_table(tokens, dim, rope_theta))
+    keys = keys.float()
     values = reconstruct(value_codes, value_tables, torch.float16).float()
     keys = keys.repeat_interleave(rep, dim=1)
     values = values.repeat_interleave(rep, dim=1)

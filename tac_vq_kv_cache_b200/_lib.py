@@ -7,7 +7,7 @@ is not a B200-class GPU the calls raise - there is no CPU or PyTorch fallback.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_double, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
 ABI_VERSION = 1
@@ -33,6 +33,8 @@ _SIGNATURES = {
     "tacvq_attn_static_scratch_bytes": (c_size_t, []),
     "tacvq_attn_decode_static": (c_int, [c_void_p] * 7 + [c_void_p, c_void_p] + [c_int] * 7 + [c_int64, c_void_p]),
     "tacvq_attn_combine": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tacvq_rope_table": (c_int, [c_void_p, c_int64, c_int, c_double, c_int64, c_void_p]),
+    "tacvq_attn_decode_rotary": (c_int, [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p] + [c_int] * 7 + [c_int64, c_void_p]),
 }
 
 EXPORTS = tuple(_SIGNATURES)

@@ -36,8 +36,14 @@ class VQCodeCache:
         max_tokens: int,
         window: int | None = None,
         device: torch.device | str | None = None,
+        rope_theta: float | None = None,
     ) -> None:
-        """``key_tables`` / ``value_tables``: ``[H,S,G,K,d]`` masters or deployed fp16 tables."""
+        """``key_tables`` / ``value_tables``: ``[H,S,G,K,d]`` masters or deployed fp16 tables.
+
+        With ``rope_theta`` the cache holds PRE-rotary keys, like the reference's ``LayerCache``: ``attend``
+        rotates every rebuilt key row at its token index (default rope of Mistral/Llama) and expects the
+        query rotated at its own position.  Without it no rotary step is applied.
+        """
         if key_tables.ndim != 5 or key_tables.shape != value_tables.shape:
             raise ValueError("tables must be [H,S,G,K,d] with equal K and V geometry")
         if batch <= 0 or max_tokens <= 0 or (window is not None and window <= 0):
@@ -56,6 +62,7 @@ class VQCodeCache:
         self._range = torch.zeros(2, batch, dtype=torch.int32, device=self.device)  # [start; end) per row
         self._range_is = (0, 0)
         self._workspace: torch.Tensor | None = None
+        self.rope = None if rope_theta is None else ops.rope_table(self.max_tokens, self.dim, float(rope_theta), self.device)
 
     def reset(self) -> None:
         self.length = 0
@@ -101,7 +108,7 @@ class VQCodeCache:
             self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
         out, state = ops.attn_decode(
             query, self.key, self.value, self.key_tables, self.value_tables, self._range[0], self._range[1],
-            workspace=self._workspace, want_state=want_state,
+            workspace=self._workspace, want_state=want_state, rope=self.rope,
         )
         return (out, state) if want_state else out
 
@@ -112,6 +119,13 @@ class VQCodeCache:
         """
         from . import _lib
 
+        if self.rope is not None:  # the fused call has no rotary step: append, then attend
+            self.append(raw_key, raw_value)
+            result = self.attend(query)
+            if out is not None:
+                out.copy_(result)
+                return out
+            return result
         tokens = int(raw_key.shape[2])
         if raw_key.shape != raw_value.shape or tuple(raw_key.shape[:2]) != (self.batch, self.heads) or raw_key.shape[3] != self.dim:
             raise ValueError("rows must be [B,H,T,D] matching the cache geometry")

@@ -199,12 +199,16 @@ def attn_decode(
     want_state: bool = False,
     out: torch.Tensor | None = None,
     state: torch.Tensor | None = None,
+    rope: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor | None, torch.Tensor | None]:
     """Decode-step attention over codes -> ``(out fp16 [B,Hq,D] | None, state fp32 [B,Hq,2+D] | None)``.
 
     ``q [B,Hq,D]`` fp16 pre-scaled; ``seq_start/seq_end`` int32 ``[B]`` on the device (None = whole buffer).
+    With ``rope`` (from :func:`rope_table`, ``[T_cap, D/2, 2]`` fp16) the key codes are taken as
+    pre-rotary keys and every rebuilt key row is rotated at its token index, as the reference's decode
+    branch does; ``q`` is then the query already rotated at its own position.
     """
-    device = _require_cuda(q, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, workspace)
+    device = _require_cuda(q, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, workspace, rope)
     if q.dtype != torch.float16 or q.ndim != 3:
         raise ValueError("q must be fp16 [B,Hq,D]")
     q = q.contiguous()
@@ -225,6 +229,17 @@ def attn_decode(
         out = torch.empty(b, hq, dim, dtype=torch.float16, device=device)
     if want_state and state is None:
         state = torch.empty(b, hq, dim + 2, dtype=torch.float32, device=device)
+    if rope is not None:
+        if rope.dtype != torch.float16 or tuple(rope.shape) != (t_cap, dim // 2, 2) or not rope.is_contiguous():
+            raise ValueError("rope must be contiguous fp16 [T_cap, D/2, 2] (cos, sin)")
+        with _on(device):
+            status = _lib.load().tacvq_attn_decode_rotary(
+                _ptr(q), _ptr(kcodes), _ptr(vcodes), _ptr(ktab_f16.contiguous()), _ptr(vtab_f16.contiguous()), _ptr(rope),
+                _ptr(seq_start), _ptr(seq_end), _ptr(workspace), workspace.numel() * workspace.element_size(), _ptr(out),
+                _ptr(state), b, hq, hkv, dim, g, s, k, t_cap, _stream(device),
+            )
+        _lib.check("tacvq_attn_decode_rotary", status)
+        return out, state
     with _on(device):
         status = _lib.load().tacvq_attn_decode(
             _ptr(q), _ptr(kcodes), _ptr(vcodes), _ptr(ktab_f16.contiguous()), _ptr(vtab_f16.contiguous()), _ptr(seq_start),
@@ -233,6 +248,18 @@ def attn_decode(
         )
     _lib.check("tacvq_attn_decode", status)
     return out, state
+
+
+def rope_table(tokens: int, dim: int, theta: float, device, first_position: int = 0) -> torch.Tensor:
+    """``[tokens, dim/2, 2]`` fp16 ``(cos, sin)`` of positions ``first_position ..`` (default rope of Mistral/Llama)."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError("libtacvq runs on CUDA devices only")
+    table = torch.empty(int(tokens), int(dim) // 2, 2, dtype=torch.float16, device=device)
+    with _on(device):
+        status = _lib.load().tacvq_rope_table(_ptr(table), int(tokens), int(dim), float(theta), int(first_position), _stream(device))
+    _lib.check("tacvq_rope_table", status)
+    return table
 
 
 def set_ranges(seq_start: torch.Tensor, seq_end: torch.Tensor, start: int, end: int) -> None:

@@ -21,6 +21,8 @@ Cases (reference entry point -> archive):
   * ``residual_vq_ledger`` and ``pack_fixed_width`` ............................ ledger.json
   * decode-step attention: reference reconstruction -> ``repeat_interleave`` ->
     ``F.scaled_dot_product_attention`` in fp32 over the visible window ...... attention.npz
+  * the same branch with its rotary step (transformers' Mistral rotary functions on the
+    rebuilt fp16 window, fp16 SDPA) .................................... rotary.npz
 """
 
 from __future__ import annotations
@@ -245,9 +247,63 @@ def attention_cases(ref) -> dict:
     return out
 
 
+def rotary_cases(ref) -> dict:
+    """The reference's decode branch with its rotary step, restated with the library functions it calls
+    (experiments_followup_mistral/evaluate_mistral_longbench.py:112-122: rebuilt fp16 window of pre-RoPE
+    keys -> ``rotary_emb(visible_k, arange(start, length))`` -> ``apply_rotary_pos_emb`` on the fp16 window ->
+    ``repeat_kv`` -> ``F.scaled_dot_product_attention`` with its default scale), one batch row at a time
+    as the reference requires batch one."""
+    from transformers import MistralConfig
+    from transformers.models.mistral.modeling_mistral import MistralRotaryEmbedding, apply_rotary_pos_emb, repeat_kv
+
+    out = {}
+    gen = torch.Generator().manual_seed(8602)
+    for name, (b, hq, hkv, t, g, s, d, theta) in {
+        "gsrq": (2, 8, 2, 300, 16, 2, 8, 1000000.0),
+        "cq": (1, 4, 2, 160, 1, 2, 128, 10000.0),
+    }.items():
+        dim = g * d
+        cfg = MistralConfig(hidden_size=hq * dim, num_attention_heads=hq, num_key_value_heads=hkv, head_dim=dim,
+                            rope_theta=theta, num_hidden_layers=1, intermediate_size=64, vocab_size=32)
+        rotary = MistralRotaryEmbedding(cfg)
+        kstates = torch.randn(b, hkv, t, dim, generator=gen).half()
+        vstates = torch.randn(b, hkv, t, dim, generator=gen).half()
+        scale = [0.5, 0.25] if g > 1 else [0.1, 0.1]
+        ktab = torch.stack([torch.randn(hkv, g, 256, d, generator=gen) * scale[i] for i in range(s)], dim=1).half()
+        vtab = torch.stack([torch.randn(hkv, g, 256, d, generator=gen) * scale[i] for i in range(s)], dim=1).half()
+        kex, kidx = ref.hard_residual_vq_exits(_fold_states(kstates, g), _fold_tables(ktab.float()), prefixes=(s,), straight_through_states=False)
+        vex, vidx = ref.hard_residual_vq_exits(_fold_states(vstates, g), _fold_tables(vtab.float()), prefixes=(s,), straight_through_states=False)
+        kcodes, krec = _unfold(kidx, kex[s], b, hkv, g, t, s)
+        vcodes, vrec = _unfold(vidx, vex[s], b, hkv, g, t, s)
+        starts = [0, 37][:b]
+        ends = [t, t - 11][:b]
+        raw_q = torch.randn(b, hq, 1, dim, generator=gen).half()
+        q_rot = torch.zeros_like(raw_q)
+        result = torch.zeros(b, hq, dim)
+        for i in range(b):
+            length = ends[i]
+            position_ids = torch.tensor([[length - 1]])
+            visible_k, visible_v = krec[i : i + 1, :, starts[i] : length], vrec[i : i + 1, :, starts[i] : length]
+            query_cos, query_sin = rotary(visible_v, position_ids)
+            q, _ = apply_rotary_pos_emb(raw_q[i : i + 1], raw_q[i : i + 1], query_cos, query_sin)
+            all_positions = torch.arange(starts[i], length).unsqueeze(0)
+            key_cos, key_sin = rotary(visible_k, all_positions)
+            _, rotated_k = apply_rotary_pos_emb(visible_k, visible_k, key_cos, key_sin)
+            output = F.scaled_dot_product_attention(q, repeat_kv(rotated_k, hq // hkv), repeat_kv(visible_v, hq // hkv),
+                                                    attn_mask=None, dropout_p=0.0, is_causal=False)
+            q_rot[i] = q[0]
+            result[i] = output[0, :, 0].float()
+        out.update({f"{name}.q_rotated": _np(q_rot[:, :, 0]), f"{name}.kcodes": _np(kcodes), f"{name}.vcodes": _np(vcodes),
+                    f"{name}.ktab": _np(ktab), f"{name}.vtab": _np(vtab), f"{name}.seq_start": np.array(starts, np.int32),
+                    f"{name}.seq_end": np.array(ends, np.int32), f"{name}.theta": np.array(theta, np.float64),
+                    f"{name}.out": _np(result)})
+    return out
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", required=True, help="root of the reference checkout")
+    parser.add_argument("--only", default=None, help="write just this fixture (e.g. rotary)")
     args = parser.parse_args()
     sys.dont_write_bytecode = True
     sys.path.insert(0, str(Path(args.reference) / "src"))
@@ -258,6 +314,11 @@ def main() -> None:
     import jointkv.uniform_depth_tac as uni
 
     torch.set_num_threads(1)
+    if args.only == "rotary":
+        np.savez(HERE / "rotary.npz", **rotary_cases(ref))
+        print("rotary.npz", (HERE / "rotary.npz").stat().st_size)
+        return
+    np.savez(HERE / "rotary.npz", **rotary_cases(ref))
     np.savez(HERE / "reftests.npz", **reftests(ref))
     np.savez(HERE / "encode.npz", **encode_cases(ref, cq))
     np.savez(HERE / "modules.npz", **module_cases(uni, cq))

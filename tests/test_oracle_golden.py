@@ -49,6 +49,27 @@ def test_attention_matches_dequantise_then_sdpa(golden):
         assert torch.allclose(out, want, rtol=1e-5, atol=1e-6)
 
 
+def test_rotary_attention_matches_the_reference_branch_with_its_rotary_step(golden):
+    """Fixture: the reference's decode branch restated with transformers' Mistral rotary functions
+    (fp16 window, fp16 SDPA with the default scale).  The oracle keeps the fp16 rotation and sums in
+    fp32; tolerance 2e-3 of the largest output, the attention tolerance of this build."""
+    g = golden("rotary.npz")
+    for case in ("gsrq", "cq"):
+        q = g(f"{case}.q_rotated")
+        scaled = q.float() / q.shape[-1] ** 0.5
+        out, *_ = O.attention_over_codes(
+            scaled, g(f"{case}.kcodes"), g(f"{case}.vcodes"), g(f"{case}.ktab"), g(f"{case}.vtab"),
+            g(f"{case}.seq_start").tolist(), g(f"{case}.seq_end").tolist(), rope_theta=float(g(f"{case}.theta")),
+        )
+        want = g(f"{case}.out")
+        assert float((out - want).abs().max()) <= 2e-3 * float(want.abs().max())
+        plain, *_ = O.attention_over_codes(
+            scaled, g(f"{case}.kcodes"), g(f"{case}.vcodes"), g(f"{case}.ktab"), g(f"{case}.vtab"),
+            g(f"{case}.seq_start").tolist(), g(f"{case}.seq_end").tolist(),
+        )
+        assert float((plain - want).abs().max()) > 2e-2 * float(want.abs().max())  # the rotation matters
+
+
 def test_merge_of_token_ranges_equals_whole(golden):
     g = golden("attention.npz")
     args = (g("gsrq.q"), g("gsrq.kcodes"), g("gsrq.vcodes"), g("gsrq.ktab"), g("gsrq.vtab"))
