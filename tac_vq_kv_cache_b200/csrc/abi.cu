@@ -31,6 +31,7 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
                        __half *out, float *state_out, int B, int Hq, int Hkv, int64_t T_cap, int sms,
                        cudaStream_t stream);
 
+int attn_rotary_splits(int B, int Hkv, int64_t T_cap, int sms);
 int rope_table_dispatch(__half2 *table, int64_t tokens, int D, double theta, int64_t first, cudaStream_t stream);
 int attn_rotary_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
                          const __half *vtab, const __half2 *rope, const int32_t *seq_start, const int32_t *seq_end,
@@ -267,7 +268,7 @@ int tacvq_attn_decode_rotary(const uint16_t *q_f16, const uint8_t *kcodes, const
         return TACVQ_ERR_WORKSPACE;
     if (((uintptr_t)rope_table & 3) != 0) return TACVQ_ERR_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
-    const int splits = attn_generic_splits(B, Hkv, T_cap, sm_count());
+    const int splits = attn_rotary_splits(B, Hkv, T_cap, sm_count());
     int st = attn_rotary_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16, (const __half *)vtab_f16,
                                   (const __half2 *)rope_table, seq_start, seq_end, (float *)workspace, B, Hq, Hkv, D, G, S, K,
                                   T_cap, splits, s);

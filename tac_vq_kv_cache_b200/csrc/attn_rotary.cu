@@ -1,12 +1,12 @@
 // Attention over stored codes of PRE-rotary keys: the rotary embedding is applied to every rebuilt
 // key row on the fly.
 //
-// One block serves one (batch row, KV head, sequence split); a warp takes one token per step and a
-// lane owns DPL = D/32 neighbouring channels of it:
+// One block serves one (batch row, KV head, sequence split); sixteen lanes take one token and a
+// lane owns D/16 neighbouring channels of it:
 //     k_row  = fp16( sum_s word_s[kcode] )                       the reference's decoded fp16 window
 //     k_rot  = k_row*cos + rotate_half(k_row)*sin                fp16 products and sum, each rounded,
 //                                                                as apply_rotary_pos_emb does on fp16;
-//                                                                channel c pairs with c +- D/2 = lane ^ 16
+//                                                                channel c pairs with c +- D/2 = lane ^ 8
 //     score_r = q_r . k_rot                                      fp32, warp reduction
 //     online softmax, acc_r += p_r * fp16( sum_s word_s[vcode] )
 // The cos/sin pairs come from a table [T][D/2] (rope_table_kernel, positions = token index + offset),
@@ -56,17 +56,61 @@ int rope_table_dispatch(__half2 *table, int64_t tokens, int D, double theta, int
     return launch_status();
 }
 
-template <int REP, int DPL>
-__global__ void __launch_bounds__(kRotThreads)
+// ---------------------------------------------------------------------------------------------------
+// Sixteen lanes per token: a lane owns CPL = D/16 neighbouring channels, a warp works on two tokens at a
+// time and two such pairs per trip, so that the loads of one pair overlap the arithmetic of the other.
+// The rotary partner of channel c (c +- D/2) lives in lane ^ 8.
+// ---------------------------------------------------------------------------------------------------
+
+template <int N>
+__device__ __forceinline__ void load_halves(const __half *src, float *out) {
+    if constexpr (N % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < N; i += 4) {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(src + i));
+            const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+            const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+            out[i] = a.x, out[i + 1] = a.y, out[i + 2] = b.x, out[i + 3] = b.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) out[i] = __half2float(__ldg(src + i));
+    }
+}
+
+// CPL channels of one token rebuilt from its codes: fp32 sum over stages in stage order.
+// WL = channels per word piece (min(CPL, d)), CPL / WL pieces; `first_group` and `offset` locate the lane.
+template <int CPL, int WL>
+__device__ __forceinline__ void rebuild(const uint8_t *__restrict__ code_row, const __half *__restrict__ tab, int64_t head_words,
+                                        int first_group, int offset, int G, int S, int K, int d, float (&row)[CPL]) {
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) row[i] = 0.0f;
+    for (int s = 0; s < S; ++s) {
+        float piece[CPL];
+#pragma unroll
+        for (int w = 0; w < CPL / WL; ++w) {
+            const int g = first_group + w;
+            const int code = code_row[s * G + g];
+            load_halves<WL>(tab + ((head_words + (int64_t)s * G + g) * K + code) * d + offset, piece + w * WL);
+        }
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) row[i] = __fadd_rn(row[i], piece[i]);
+    }
+}
+
+template <int REP, int CPL, int WL>
+__global__ void __launch_bounds__(kRotThreads, 2)
 attn_rotary_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ kcodes, const uint8_t *__restrict__ vcodes,
                    const __half *__restrict__ ktab, const __half *__restrict__ vtab, const __half2 *__restrict__ rope,
                    const int32_t *__restrict__ seq_start, const int32_t *__restrict__ seq_end, float *__restrict__ part,
                    int B, int Hq, int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits) {
     extern __shared__ __align__(16) float smem[];
+    constexpr int kHalfWarps = 2 * kRotWarps;
     const int slots = S * G;
     const int d = D / G;
     const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = lane >> 4, l16 = lane & 15;  // which of the warp's two tokens, lane within the token
 
     const int lo_all = seq_start ? seq_start[b] : 0;
     const int hi_all = seq_end ? seq_end[b] : (int)T_cap;
@@ -75,104 +119,107 @@ attn_rotary_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ kco
     const int lo = lo_all + split * per;
     const int hi = min(lo + per, lo_all + n_all);
 
-    const int c0 = lane * DPL;             // first channel of this lane
-    const int vg = c0 / d, vi0 = c0 % d;   // its group and offset inside the group's words
+    const int c0 = l16 * CPL;              // first channel of this lane
+    const int first_group = c0 / d, offset = c0 % d;
     const int f0 = c0 % (D / 2);           // its first rotary frequency
     const bool upper = c0 >= D / 2;        // rotate_half: lower half takes -partner, upper half +partner
 
-    float qv[REP][DPL];
+    float qv[REP][CPL];
 #pragma unroll
     for (int r = 0; r < REP; ++r)
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) qv[r][i] = __half2float(q[((int64_t)b * Hq + h * REP + r) * D + c0 + i]);
+        for (int i = 0; i < CPL; ++i) qv[r][i] = __half2float(q[((int64_t)b * Hq + h * REP + r) * D + c0 + i]);
 
-    float m[REP], l[REP], acc[REP][DPL];
+    float m[REP], l[REP], acc[REP][CPL];
 #pragma unroll
     for (int r = 0; r < REP; ++r) {
         m[r] = -INFINITY;
         l[r] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) acc[r][i] = 0.0f;
+        for (int i = 0; i < CPL; ++i) acc[r][i] = 0.0f;
     }
     const int64_t code_row = ((int64_t)b * Hkv + h) * T_cap;
-    const int64_t word_row = (int64_t)h * S * G + vg;  // + s*G per stage, then * K + code
+    const int64_t head_words = (int64_t)h * S * G;
 
-    for (int t = lo + warp; t < hi; t += kRotWarps) {
-        const uint8_t *kc = kcodes + (code_row + t) * slots + vg;
-        const uint8_t *vc = vcodes + (code_row + t) * slots + vg;
-        float krow[DPL], vrow[DPL];
+    // a trip covers 4 * kRotWarps tokens: pair u of warp w holds tokens base + u*2*kRotWarps + 2*w + sub
+    for (int base = lo; base < hi; base += 4 * kRotWarps) {
+        float sc[2][REP], vrow[2][CPL];
+        bool live[2];
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) krow[i] = vrow[i] = 0.0f;
-        for (int s = 0; s < S; ++s) {
-            const __half *kw = ktab + ((word_row + (int64_t)s * G) * K + kc[s * G]) * d + vi0;
-            const __half *vw = vtab + ((word_row + (int64_t)s * G) * K + vc[s * G]) * d + vi0;
+        for (int u = 0; u < 2; ++u) {
+            const int t_raw = base + u * 2 * kRotWarps + 2 * warp + sub;
+            live[u] = t_raw < hi;
+            const int t = live[u] ? t_raw : hi - 1;  // lanes past the end redo the last token and drop it
+            float krow[CPL];
+            rebuild<CPL, WL>(kcodes + (code_row + t) * slots, ktab, head_words, first_group, offset, G, S, K, d, krow);
+            rebuild<CPL, WL>(vcodes + (code_row + t) * slots, vtab, head_words, first_group, offset, G, S, K, d, vrow[u]);
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) {
-                krow[i] = __fadd_rn(krow[i], __half2float(__ldg(kw + i)));
-                vrow[i] = __fadd_rn(vrow[i], __half2float(__ldg(vw + i)));
+            for (int r = 0; r < REP; ++r) sc[u][r] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < CPL; i += 2) {
+                const __half2 mine = __floats2half2_rn(krow[i], krow[i + 1]);
+                const __half2 other = __shfl_xor_sync(0xffffffffu, mine, 8);
+                const __half2 cs0 = rope[(int64_t)t * (D / 2) + f0 + i], cs1 = rope[(int64_t)t * (D / 2) + f0 + i + 1];
+                const __half2 cosv = __lows2half2(cs0, cs1), sinv = __highs2half2(cs0, cs1);
+                const __half2 turned = upper ? other : __hneg2(other);
+                const __half2 rotated = __hadd2(__hmul2(mine, cosv), __hmul2(turned, sinv));
+                const float2 kf = __half22float2(rotated);
+#pragma unroll
+                for (int r = 0; r < REP; ++r) sc[u][r] = fmaf(qv[r][i + 1], kf.y, fmaf(qv[r][i], kf.x, sc[u][r]));
+            }
+#pragma unroll
+            for (int r = 0; r < REP; ++r) {
+#pragma unroll
+                for (int off = 8; off >= 1; off >>= 1) sc[u][r] += __shfl_xor_sync(0xffffffffu, sc[u][r], off);
             }
         }
-        float sc[REP];
 #pragma unroll
-        for (int r = 0; r < REP; ++r) sc[r] = 0.0f;
+        for (int u = 0; u < 2; ++u) {
+            if (!live[u]) continue;
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-            const __half mine = __float2half_rn(krow[i]);
-            const __half other = __shfl_xor_sync(0xffffffffu, mine, 16);
-            const __half2 cs = rope[(int64_t)t * (D / 2) + f0 + i];
-            const __half turned = upper ? other : __hneg(other);
-            const __half rotated = __hadd(__hmul(mine, __low2half(cs)), __hmul(turned, __high2half(cs)));
-            const float kf = __half2float(rotated);
+            for (int r = 0; r < REP; ++r) {
+                if (sc[u][r] > m[r]) {
+                    const float scale = __expf(m[r] - sc[u][r]);  // exp(-inf) = 0 on the first token
+                    l[r] *= scale;
 #pragma unroll
-            for (int r = 0; r < REP; ++r) sc[r] = fmaf(qv[r][i], kf, sc[r]);
-        }
+                    for (int i = 0; i < CPL; ++i) acc[r][i] *= scale;
+                    m[r] = sc[u][r];
+                }
+                const float p = __expf(sc[u][r] - m[r]);
+                l[r] += p;
 #pragma unroll
-        for (int r = 0; r < REP; ++r) {
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) sc[r] += __shfl_xor_sync(0xffffffffu, sc[r], off);
-        }
-#pragma unroll
-        for (int r = 0; r < REP; ++r) {
-            if (sc[r] > m[r]) {
-                const float scale = __expf(m[r] - sc[r]);  // exp(-inf) = 0 on the first token
-                l[r] *= scale;
-#pragma unroll
-                for (int i = 0; i < DPL; ++i) acc[r][i] *= scale;
-                m[r] = sc[r];
+                for (int i = 0; i < CPL; ++i) acc[r][i] = fmaf(p, __half2float(__float2half_rn(vrow[u][i])), acc[r][i]);
             }
-            const float p = __expf(sc[r] - m[r]);
-            l[r] += p;
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) acc[r][i] = fmaf(p, __half2float(__float2half_rn(vrow[i])), acc[r][i]);
         }
     }
 
-    // ---- merge the warps of this block (same layout of partial states as the generic kernel) --------
-    float *wm = smem;                         // [warps][REP]
-    float *wl = wm + kRotWarps * REP;         // [warps][REP]
-    float *wacc = wl + kRotWarps * REP;       // [warps][REP][D]
-    if (lane == 0) {
+    // ---- merge the half-warps of this block (same layout of partial states as the generic kernel) ----
+    float *wm = smem;                          // [half-warps][REP]
+    float *wl = wm + kHalfWarps * REP;         // [half-warps][REP]
+    float *wacc = wl + kHalfWarps * REP;       // [half-warps][REP][D]
+    const int hw = warp * 2 + sub;
+    if (l16 == 0) {
 #pragma unroll
         for (int r = 0; r < REP; ++r) {
-            wm[warp * REP + r] = m[r];
-            wl[warp * REP + r] = l[r];
+            wm[hw * REP + r] = m[r];
+            wl[hw * REP + r] = l[r];
         }
     }
 #pragma unroll
     for (int r = 0; r < REP; ++r)
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) wacc[((size_t)warp * REP + r) * D + c0 + i] = acc[r][i];
+        for (int i = 0; i < CPL; ++i) wacc[((size_t)hw * REP + r) * D + c0 + i] = acc[r][i];
     __syncthreads();
     const int64_t rows = (int64_t)B * Hq;
     for (int idx = tid; idx < REP * (D + 2); idx += kRotThreads) {
         const int r = idx / (D + 2), col = idx % (D + 2);
         float top = -INFINITY;
-        for (int w = 0; w < kRotWarps; ++w) top = fmaxf(top, wm[w * REP + r]);
+        for (int w = 0; w < kHalfWarps; ++w) top = fmaxf(top, wm[w * REP + r]);
         float sum = 0.0f;
         if (col == 0) {
             sum = top;
         } else {
-            for (int w = 0; w < kRotWarps; ++w) {
+            for (int w = 0; w < kHalfWarps; ++w) {
                 const float mw = wm[w * REP + r];
                 if (mw == -INFINITY) continue;
                 const float scale = __expf(mw - top);
@@ -184,13 +231,13 @@ attn_rotary_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ kco
     }
 }
 
-template <int REP, int DPL>
+template <int REP, int CPL, int WL>
 static int launch_rotary(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
                          const __half *vtab, const __half2 *rope, const int32_t *seq_start, const int32_t *seq_end,
                          float *part, int B, int Hq, int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits,
                          cudaStream_t stream) {
-    const size_t smem = ((size_t)2 * kRotWarps * REP + (size_t)kRotWarps * REP * D) * sizeof(float);
-    auto kernel = attn_rotary_kernel<REP, DPL>;
+    const size_t smem = ((size_t)4 * kRotWarps * REP + (size_t)2 * kRotWarps * REP * D) * sizeof(float);
+    auto kernel = attn_rotary_kernel<REP, CPL, WL>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -201,19 +248,57 @@ static int launch_rotary(const __half *q, const uint8_t *kcodes, const uint8_t *
     return launch_status();
 }
 
+// word pieces per lane: a lane's CPL channels are either inside one word (d >= CPL) or whole words (d < CPL)
+template <int REP, int CPL>
+static int rotary_piece(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab, const __half *vtab,
+                        const __half2 *rope, const int32_t *seq_start, const int32_t *seq_end, float *part, int B, int Hq,
+                        int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits, cudaStream_t stream) {
+    const int d = D / G;
+#define TACVQ_CASE(N) \
+    return launch_rotary<REP, CPL, N>(q, kcodes, vcodes, ktab, vtab, rope, seq_start, seq_end, part, B, Hq, Hkv, D, G, S, K, T_cap, splits, stream);
+    if (d >= CPL) {
+        if (d % CPL != 0) return TACVQ_ERR_UNSUPPORTED;
+        TACVQ_CASE(CPL)
+    }
+    if (CPL % d != 0) return TACVQ_ERR_UNSUPPORTED;
+    if constexpr (CPL >= 8) {
+        if (d == 4) { TACVQ_CASE(4) }
+    }
+    if constexpr (CPL >= 4) {
+        if (d == 2) { TACVQ_CASE(2) }
+    }
+    if (d == 1) { TACVQ_CASE(1) }
+    if constexpr (CPL == 16) {
+        if (d == 8) { TACVQ_CASE(8) }
+    }
+    return TACVQ_ERR_UNSUPPORTED;
+#undef TACVQ_CASE
+}
+
 template <int REP>
 static int rotary_dpl(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab, const __half *vtab,
                       const __half2 *rope, const int32_t *seq_start, const int32_t *seq_end, float *part, int B, int Hq,
                       int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits, cudaStream_t stream) {
 #define TACVQ_CASE(N) \
-    case N: return launch_rotary<REP, N>(q, kcodes, vcodes, ktab, vtab, rope, seq_start, seq_end, part, B, Hq, Hkv, D, G, S, K, T_cap, splits, stream);
-    switch (D / 32) {
-        TACVQ_CASE(2)
+    case N: return rotary_piece<REP, N>(q, kcodes, vcodes, ktab, vtab, rope, seq_start, seq_end, part, B, Hq, Hkv, D, G, S, K, T_cap, splits, stream);
+    switch (D / 16) {
         TACVQ_CASE(4)
         TACVQ_CASE(8)
+        TACVQ_CASE(16)
         default: return TACVQ_ERR_UNSUPPORTED;
     }
 #undef TACVQ_CASE
+}
+
+// About four waves of blocks (two resident per SM), at least 256 tokens per block, at most 64 splits.
+int attn_rotary_splits(int B, int Hkv, int64_t T_cap, int sms) {
+    const int pairs = B * Hkv;
+    int splits = (8 * sms + pairs - 1) / pairs;
+    const int64_t by_len = (T_cap + 255) / 256;
+    if (splits > by_len) splits = (int)by_len;
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+    return splits;
 }
 
 int attn_rotary_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
