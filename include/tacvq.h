@@ -226,16 +226,16 @@ TACVQ_API int tacvq_attn_combine(const float *states, int n_parts, uint16_t *out
                        tacvq_stream_t stream);
 
 /*
- * cos/sin table of the rotary position embedding, table[t][i] = (cos, sin)((first_position + t) *
- * theta^(-2i/D)) as fp16 pairs, i < D/2: inverse frequencies, angles and cos/sin in fp32, one rounding
- * to fp16.  Replaces `self.rotary_emb(visible_k, all_positions)` of the reference's decode branch
+ * cos/sin table of the rotary position embedding: row t holds D/2 cosines, then D/2 sines, of the
+ * angles (first_position + t) * theta^(-2i/D), i < D/2, as fp16: inverse frequencies, angles and
+ * cos/sin in fp32, one rounding to fp16.  Replaces `self.rotary_emb(visible_k, all_positions)` of the reference's decode branch
  * (experiments_followup_mistral/evaluate_mistral_longbench.py:115-117; default rope type of
  * transformers' MistralRotaryEmbedding).  A caller that has its model's own cos/sin may fill the
  * table itself.
  *
- *   table_half2        [T][D/2] pairs of fp16 (cos in the low half), 4-byte aligned;  D <= 256, D even
+ *   table_f16          [T][2][D/2] fp16, 16-byte aligned;  D <= 256, D even
  */
-TACVQ_API int tacvq_rope_table(uint32_t *table_half2, int64_t T, int D, double theta, int64_t first_position,
+TACVQ_API int tacvq_rope_table(uint16_t *table_f16, int64_t T, int D, double theta, int64_t first_position,
                                tacvq_stream_t stream);
 
 /*
@@ -247,11 +247,11 @@ TACVQ_API int tacvq_rope_table(uint32_t *table_half2, int64_t T, int D, double t
  *
  *   q_f16              [B,Hq,D] fp16, already rotated at the query's own position and multiplied by
  *                      the softmax scale
- *   rope_table         [T_cap][D/2] from tacvq_rope_table (row index = token index in the code buffers)
+ *   rope_table         [T_cap][2][D/2] from tacvq_rope_table (row index = token index in the code buffers)
  *   other arguments, workspace size and results as for tacvq_attn_decode; D in {64, 128, 256}.
  */
 TACVQ_API int tacvq_attn_decode_rotary(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_t *vcodes,
-                                       const uint16_t *ktab_f16, const uint16_t *vtab_f16, const uint32_t *rope_table,
+                                       const uint16_t *ktab_f16, const uint16_t *vtab_f16, const uint16_t *rope_table,
                                        const int32_t *seq_start, const int32_t *seq_end, void *workspace,
                                        size_t workspace_bytes, uint16_t *out_f16, float *state_out, int B, int Hq,
                                        int Hkv, int D, int G, int S, int K, int64_t T_cap, tacvq_stream_t stream);

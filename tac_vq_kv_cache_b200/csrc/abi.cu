@@ -32,9 +32,15 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
                        cudaStream_t stream);
 
 int attn_rotary_splits(int B, int Hkv, int64_t T_cap, int sms);
-int rope_table_dispatch(__half2 *table, int64_t tokens, int D, double theta, int64_t first, cudaStream_t stream);
+bool attn_rotary_staged_supported(int Hq, int Hkv, int D, int G, int S, int K);
+int attn_rotary_staged_splits(int B, int Hkv, int64_t T_cap, int sms);
+int attn_rotary_staged_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
+                                const __half *vtab, const __half *rope, const int32_t *seq_start, const int32_t *seq_end,
+                                float *part, int B, int Hq, int Hkv, int G, int S, int64_t T_cap, int splits,
+                                cudaStream_t stream);
+int rope_table_dispatch(__half *table, int64_t tokens, int D, double theta, int64_t first, cudaStream_t stream);
 int attn_rotary_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
-                         const __half *vtab, const __half2 *rope, const int32_t *seq_start, const int32_t *seq_end,
+                         const __half *vtab, const __half *rope, const int32_t *seq_start, const int32_t *seq_end,
                          float *part, int B, int Hq, int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits,
                          cudaStream_t stream);
 
@@ -244,17 +250,17 @@ int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_
     return attn_combine_dispatch((const float *)workspace, splits, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);
 }
 
-int tacvq_rope_table(uint32_t *table_half2, int64_t T, int D, double theta, int64_t first_position, tacvq_stream_t stream) {
+int tacvq_rope_table(uint16_t *table_f16, int64_t T, int D, double theta, int64_t first_position, tacvq_stream_t stream) {
     if (T < 0 || D <= 0 || (D & 1) != 0 || !(theta > 0.0) || first_position < 0) return TACVQ_ERR_GEOMETRY;
     if (D > 256) return TACVQ_ERR_UNSUPPORTED;
     if (T == 0) return TACVQ_OK;
-    if (!table_half2) return TACVQ_ERR_NULL;
-    if (((uintptr_t)table_half2 & 3) != 0) return TACVQ_ERR_ALIGN;
-    return rope_table_dispatch((__half2 *)table_half2, T, D, theta, first_position, (cudaStream_t)stream);
+    if (!table_f16) return TACVQ_ERR_NULL;
+    if (((uintptr_t)table_f16 & 15) != 0) return TACVQ_ERR_ALIGN;
+    return rope_table_dispatch((__half *)table_f16, T, D, theta, first_position, (cudaStream_t)stream);
 }
 
 int tacvq_attn_decode_rotary(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_t *vcodes,
-                             const uint16_t *ktab_f16, const uint16_t *vtab_f16, const uint32_t *rope_table,
+                             const uint16_t *ktab_f16, const uint16_t *vtab_f16, const uint16_t *rope_table,
                              const int32_t *seq_start, const int32_t *seq_end, void *workspace, size_t workspace_bytes,
                              uint16_t *out_f16, float *state_out, int B, int Hq, int Hkv, int D, int G, int S, int K,
                              int64_t T_cap, tacvq_stream_t stream) {
@@ -266,11 +272,19 @@ int tacvq_attn_decode_rotary(const uint16_t *q_f16, const uint8_t *kcodes, const
     if (T_cap < 0 || T_cap > 0x7fffffff) return TACVQ_ERR_RANGE;
     if (!workspace || ((uintptr_t)workspace & 255) != 0 || workspace_bytes < tacvq_attn_workspace_bytes(B, Hq, Hkv, D, G, S))
         return TACVQ_ERR_WORKSPACE;
-    if (((uintptr_t)rope_table & 3) != 0) return TACVQ_ERR_ALIGN;
+    if (((uintptr_t)rope_table & 3) != 0) return TACVQ_ERR_ALIGN;  // the staged kernel wants 16 bytes and is skipped otherwise
     cudaStream_t s = (cudaStream_t)stream;
+    if (attn_rotary_staged_supported(Hq, Hkv, D, G, S, K) && (((uintptr_t)ktab_f16 | (uintptr_t)vtab_f16 | (uintptr_t)rope_table) & 15) == 0) {
+        const int staged = attn_rotary_staged_splits(B, Hkv, T_cap, sm_count());
+        int st = attn_rotary_staged_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
+                                             (const __half *)vtab_f16, (const __half *)rope_table, seq_start, seq_end,
+                                             (float *)workspace, B, Hq, Hkv, G, S, T_cap, staged, s);
+        if (st != TACVQ_OK) return st;
+        return attn_combine_dispatch((const float *)workspace, staged, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);
+    }
     const int splits = attn_rotary_splits(B, Hkv, T_cap, sm_count());
     int st = attn_rotary_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16, (const __half *)vtab_f16,
-                                  (const __half2 *)rope_table, seq_start, seq_end, (float *)workspace, B, Hq, Hkv, D, G, S, K,
+                                  (const __half *)rope_table, seq_start, seq_end, (float *)workspace, B, Hq, Hkv, D, G, S, K,
                                   T_cap, splits, s);
     if (st != TACVQ_OK) return st;
     return attn_combine_dispatch((const float *)workspace, splits, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);

@@ -34,7 +34,7 @@ struct RopeFreqs {
     float inv[128];
 };
 
-__global__ void rope_table_kernel(__half2 *__restrict__ table, int64_t tokens, int half_dim, const RopeFreqs freqs,
+__global__ void rope_table_kernel(__half *__restrict__ table, int64_t tokens, int half_dim, const RopeFreqs freqs,
                                   int64_t first) {
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= tokens * half_dim) return;
@@ -43,10 +43,11 @@ __global__ void rope_table_kernel(__half2 *__restrict__ table, int64_t tokens, i
     const float angle = (float)(first + t) * freqs.inv[i];
     float sn, cs;
     sincosf(angle, &sn, &cs);
-    table[idx] = __halves2half2(__float2half_rn(cs), __float2half_rn(sn));
+    table[t * 2 * half_dim + i] = __float2half_rn(cs);             // row t: the cosines ...
+    table[t * 2 * half_dim + half_dim + i] = __float2half_rn(sn);  // ... then the sines
 }
 
-int rope_table_dispatch(__half2 *table, int64_t tokens, int D, double theta, int64_t first, cudaStream_t stream) {
+int rope_table_dispatch(__half *table, int64_t tokens, int D, double theta, int64_t first, cudaStream_t stream) {
     const int64_t n = tokens * (D / 2);
     if (n == 0) return TACVQ_OK;
     if (D / 2 > 128) return TACVQ_ERR_UNSUPPORTED;
@@ -101,7 +102,7 @@ __device__ __forceinline__ void rebuild(const uint8_t *__restrict__ code_row, co
 template <int REP, int CPL, int WL>
 __global__ void __launch_bounds__(kRotThreads, 2)
 attn_rotary_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ kcodes, const uint8_t *__restrict__ vcodes,
-                   const __half *__restrict__ ktab, const __half *__restrict__ vtab, const __half2 *__restrict__ rope,
+                   const __half *__restrict__ ktab, const __half *__restrict__ vtab, const __half *__restrict__ rope,
                    const int32_t *__restrict__ seq_start, const int32_t *__restrict__ seq_end, float *__restrict__ part,
                    int B, int Hq, int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits) {
     extern __shared__ __align__(16) float smem[];
@@ -159,8 +160,8 @@ attn_rotary_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ kco
             for (int i = 0; i < CPL; i += 2) {
                 const __half2 mine = __floats2half2_rn(krow[i], krow[i + 1]);
                 const __half2 other = __shfl_xor_sync(0xffffffffu, mine, 8);
-                const __half2 cs0 = rope[(int64_t)t * (D / 2) + f0 + i], cs1 = rope[(int64_t)t * (D / 2) + f0 + i + 1];
-                const __half2 cosv = __lows2half2(cs0, cs1), sinv = __highs2half2(cs0, cs1);
+                const __half2 cosv = *reinterpret_cast<const __half2 *>(rope + (int64_t)t * D + f0 + i);
+                const __half2 sinv = *reinterpret_cast<const __half2 *>(rope + (int64_t)t * D + D / 2 + f0 + i);
                 const __half2 turned = upper ? other : __hneg2(other);
                 const __half2 rotated = __hadd2(__hmul2(mine, cosv), __hmul2(turned, sinv));
                 const float2 kf = __half22float2(rotated);
@@ -233,7 +234,7 @@ attn_rotary_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ kco
 
 template <int REP, int CPL, int WL>
 static int launch_rotary(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
-                         const __half *vtab, const __half2 *rope, const int32_t *seq_start, const int32_t *seq_end,
+                         const __half *vtab, const __half *rope, const int32_t *seq_start, const int32_t *seq_end,
                          float *part, int B, int Hq, int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits,
                          cudaStream_t stream) {
     const size_t smem = ((size_t)4 * kRotWarps * REP + (size_t)2 * kRotWarps * REP * D) * sizeof(float);
@@ -251,7 +252,7 @@ static int launch_rotary(const __half *q, const uint8_t *kcodes, const uint8_t *
 // word pieces per lane: a lane's CPL channels are either inside one word (d >= CPL) or whole words (d < CPL)
 template <int REP, int CPL>
 static int rotary_piece(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab, const __half *vtab,
-                        const __half2 *rope, const int32_t *seq_start, const int32_t *seq_end, float *part, int B, int Hq,
+                        const __half *rope, const int32_t *seq_start, const int32_t *seq_end, float *part, int B, int Hq,
                         int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits, cudaStream_t stream) {
     const int d = D / G;
 #define TACVQ_CASE(N) \
@@ -277,7 +278,7 @@ static int rotary_piece(const __half *q, const uint8_t *kcodes, const uint8_t *v
 
 template <int REP>
 static int rotary_dpl(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab, const __half *vtab,
-                      const __half2 *rope, const int32_t *seq_start, const int32_t *seq_end, float *part, int B, int Hq,
+                      const __half *rope, const int32_t *seq_start, const int32_t *seq_end, float *part, int B, int Hq,
                       int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits, cudaStream_t stream) {
 #define TACVQ_CASE(N) \
     case N: return rotary_piece<REP, N>(q, kcodes, vcodes, ktab, vtab, rope, seq_start, seq_end, part, B, Hq, Hkv, D, G, S, K, T_cap, splits, stream);
@@ -288,6 +289,293 @@ static int rotary_dpl(const __half *q, const uint8_t *kcodes, const uint8_t *vco
         default: return TACVQ_ERR_UNSUPPORTED;
     }
 #undef TACVQ_CASE
+}
+
+// ---------------------------------------------------------------------------------------------------
+// head_dim 128, groups of at least 8 channels, at most 2 stages, at most 4 query heads per KV head:
+// the tables of one side fit shared memory (S x 64 KB), so a block works in two passes per chunk of
+// up to 4096 tokens: pass K (key tables resident) leaves the scores in shared memory, the block takes
+// their maximum and turns them into weights, pass V (value tables loaded over the key tables)
+// accumulates.  Tables are stored by 16-byte piece, [stage][code][piece]: the sixteen lanes of a token
+// read sixteen different pieces, which is the minimum number of shared-memory wavefronts.
+// ---------------------------------------------------------------------------------------------------
+
+constexpr int kRotBigThreads = 512;
+constexpr int kRotChunk = 4096;
+
+template <int REP>
+__global__ void __launch_bounds__(kRotBigThreads, 1)
+attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ kcodes, const uint8_t *__restrict__ vcodes,
+                          const __half *__restrict__ ktab, const __half *__restrict__ vtab, const __half *__restrict__ rope,
+                          const int32_t *__restrict__ seq_start, const int32_t *__restrict__ seq_end, float *__restrict__ part,
+                          int B, int Hq, int Hkv, int G, int S, int64_t T_cap, int splits) {
+    constexpr int D = 128, K = 256, kWarps = kRotBigThreads / 32;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint4 *tab = reinterpret_cast<uint4 *>(smem_raw);                                   // [S][256][16]
+    float *score = reinterpret_cast<float *>(smem_raw + (size_t)S * K * 16 * 16);        // [kRotChunk][REP]
+    float *red = score + (size_t)kRotChunk * REP;                                       // [kWarps][REP], later merge scratch
+
+    const int slots = S * G;
+    const int d = D / G;
+    const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = lane >> 4, l16 = lane & 15;
+    const int c0 = l16 * 8;
+    const int group = c0 / d, offset = c0 % d;
+    const int f0 = c0 % (D / 2);
+    const bool upper = c0 >= D / 2;
+
+    const int lo_all = seq_start ? seq_start[b] : 0;
+    const int hi_all = seq_end ? seq_end[b] : (int)T_cap;
+    const int n_all = hi_all > lo_all ? hi_all - lo_all : 0;
+    const int per = (n_all + splits - 1) / splits;
+    const int lo = lo_all + split * per;
+    const int hi = min(lo + per, lo_all + n_all);
+
+    auto load_tables = [&](const __half *src) {
+        for (int idx = tid; idx < S * K * 16; idx += kRotBigThreads) {
+            const int p = idx & 15, code = (idx >> 4) & 255, s = idx >> 12;
+            const int g = (8 * p) / d, off = (8 * p) % d;
+            tab[idx] = __ldg(reinterpret_cast<const uint4 *>(src + ((((int64_t)h * S + s) * G + g) * K + code) * d + off));
+        }
+    };
+    // This lane's eight channels of a token from the resident tables, as the fp16 row the reference
+    // keeps: with at most two stages the fp32 sum of two fp16 words is exact, so its single rounding to
+    // fp16 is what a packed fp16 add returns.
+    // (the codes of a token are fetched one trip ahead: S <= 2 bytes per lane and side)
+    auto fetch_codes = [&](const uint8_t *code_row, int (&code)[2]) {
+        code[0] = code_row[group];
+        code[1] = S > 1 ? code_row[G + group] : 0;
+    };
+    auto rebuild8 = [&](const int (&code)[2], __half2 (&row)[4]) {
+        const uint4 first = tab[code[0] * 16 + l16];
+        const __half2 *h0 = reinterpret_cast<const __half2 *>(&first);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) row[i] = h0[i];
+        if (S > 1) {
+            const uint4 second = tab[(K + code[1]) * 16 + l16];
+            const __half2 *h1 = reinterpret_cast<const __half2 *>(&second);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) row[i] = __hadd2(row[i], h1[i]);
+        }
+    };
+
+    float qv[REP][8];
+#pragma unroll
+    for (int r = 0; r < REP; ++r)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qv[r][i] = __half2float(q[((int64_t)b * Hq + h * REP + r) * D + c0 + i]);
+    float m[REP], l[REP], acc[REP][8];
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+        m[r] = -INFINITY;
+        l[r] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[r][i] = 0.0f;
+    }
+    const int64_t code_row = ((int64_t)b * Hkv + h) * T_cap;
+
+    for (int chunk = lo; chunk < hi; chunk += kRotChunk) {
+        const int n = min(kRotChunk, hi - chunk);
+        __syncthreads();  // the previous chunk's value pass is over
+        load_tables(ktab);
+        __syncthreads();
+        // ---- pass K: scores of the chunk ------------------------------------------------------------
+        int code_next[2];
+        uint4 cos_next, sin_next;  // eight cosines and eight sines of this lane's frequencies
+        {
+            const int t = chunk + min(2 * warp + sub, n - 1);
+            fetch_codes(kcodes + (code_row + t) * slots, code_next);
+            cos_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + f0));
+            sin_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + D / 2 + f0));
+        }
+        for (int base = 0; base < n; base += 2 * kWarps) {
+            const int local = base + 2 * warp + sub;  // lanes past the end redo the last token and drop it
+            const int code_now[2] = {code_next[0], code_next[1]};
+            const uint4 cos_now = cos_next, sin_now = sin_next;
+            if (base + 2 * kWarps < n) {
+                const int t = chunk + min(local + 2 * kWarps, n - 1);
+                fetch_codes(kcodes + (code_row + t) * slots, code_next);
+                cos_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + f0));
+                sin_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + D / 2 + f0));
+            }
+            __half2 krow[4];
+            rebuild8(code_now, krow);
+            const __half2 *cosv = reinterpret_cast<const __half2 *>(&cos_now), *sinv = reinterpret_cast<const __half2 *>(&sin_now);
+            float sc[REP];
+#pragma unroll
+            for (int r = 0; r < REP; ++r) sc[r] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __half2 other = __shfl_xor_sync(0xffffffffu, krow[i], 8);
+                const __half2 turned = upper ? other : __hneg2(other);
+                const float2 kf = __half22float2(__hadd2(__hmul2(krow[i], cosv[i]), __hmul2(turned, sinv[i])));
+#pragma unroll
+                for (int r = 0; r < REP; ++r) sc[r] = fmaf(qv[r][2 * i + 1], kf.y, fmaf(qv[r][2 * i], kf.x, sc[r]));
+            }
+            // sum over the token's 16 lanes; with 4 or 2 heads the lanes first trade heads, so that fewer
+            // values travel: head (bit 3, bit 2) of the lane index ends up in the lanes with those bits
+            if constexpr (REP == 4) {
+                const bool b3 = (l16 & 8) != 0, b2 = (l16 & 4) != 0;
+                float keep0 = b3 ? sc[2] : sc[0], keep1 = b3 ? sc[3] : sc[1];
+                keep0 += __shfl_xor_sync(0xffffffffu, b3 ? sc[0] : sc[2], 8);
+                keep1 += __shfl_xor_sync(0xffffffffu, b3 ? sc[1] : sc[3], 8);
+                float one = (b2 ? keep1 : keep0) + __shfl_xor_sync(0xffffffffu, b2 ? keep0 : keep1, 4);
+                one += __shfl_xor_sync(0xffffffffu, one, 2);
+                one += __shfl_xor_sync(0xffffffffu, one, 1);
+                if ((l16 & 3) == 0 && local < n) score[local * REP + (b3 ? 2 : 0) + (b2 ? 1 : 0)] = one;
+            } else if constexpr (REP == 2) {
+                const bool b3 = (l16 & 8) != 0;
+                float one = (b3 ? sc[1] : sc[0]) + __shfl_xor_sync(0xffffffffu, b3 ? sc[0] : sc[1], 8);
+                one += __shfl_xor_sync(0xffffffffu, one, 4);
+                one += __shfl_xor_sync(0xffffffffu, one, 2);
+                one += __shfl_xor_sync(0xffffffffu, one, 1);
+                if ((l16 & 7) == 0 && local < n) score[local * REP + (b3 ? 1 : 0)] = one;
+            } else {
+                float one = sc[0];
+#pragma unroll
+                for (int off = 8; off >= 1; off >>= 1) one += __shfl_xor_sync(0xffffffffu, one, off);
+                if (l16 == 0 && local < n) score[local * REP] = one;
+            }
+        }
+        __syncthreads();
+        // ---- chunk maximum, rescale of the running sums, weights -------------------------------------
+        float top[REP];
+#pragma unroll
+        for (int r = 0; r < REP; ++r) top[r] = -INFINITY;
+        for (int i = tid; i < n; i += kRotBigThreads) {
+#pragma unroll
+            for (int r = 0; r < REP; ++r) top[r] = fmaxf(top[r], score[i * REP + r]);
+        }
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], off));
+            if (lane == 0) red[warp * REP + r] = top[r];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+            float now = m[r];
+            for (int w = 0; w < kWarps; ++w) now = fmaxf(now, red[w * REP + r]);
+            const float scale = (m[r] == -INFINITY) ? 0.0f : __expf(m[r] - now);
+            l[r] *= scale;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[r][i] *= scale;
+            m[r] = now;
+        }
+        for (int i = tid; i < n; i += kRotBigThreads) {
+#pragma unroll
+            for (int r = 0; r < REP; ++r) score[i * REP + r] = __expf(score[i * REP + r] - m[r]);
+        }
+        load_tables(vtab);  // the key tables are no longer read: every warp passed the barrier above
+        __syncthreads();
+        // ---- pass V --------------------------------------------------------------------------------
+        fetch_codes(vcodes + (code_row + chunk + min(2 * warp + sub, n - 1)) * slots, code_next);
+        for (int base = 0; base < n; base += 2 * kWarps) {
+            const int local = base + 2 * warp + sub;
+            const int code_now[2] = {code_next[0], code_next[1]};
+            if (base + 2 * kWarps < n) fetch_codes(vcodes + (code_row + chunk + min(local + 2 * kWarps, n - 1)) * slots, code_next);
+            if (local >= n) continue;  // no shuffles in this pass
+            __half2 vhalf[4];
+            rebuild8(code_now, vhalf);
+            float vrow[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(vhalf[i]);
+                vrow[2 * i] = f.x, vrow[2 * i + 1] = f.y;
+            }
+#pragma unroll
+            for (int r = 0; r < REP; ++r) {
+                const float p = score[local * REP + r];
+                l[r] += p;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[r][i] = fmaf(p, vrow[i], acc[r][i]);
+            }
+        }
+    }
+
+    // ---- sum the half-warps (they share m), write this split's partial state ------------------------
+    __syncthreads();
+    float *wl = reinterpret_cast<float *>(smem_raw);       // [2*kWarps][REP]
+    float *wacc = wl + 2 * kWarps * REP;                   // [2*kWarps][REP][D]
+    const int hw = warp * 2 + sub;
+    if (l16 == 0) {
+#pragma unroll
+        for (int r = 0; r < REP; ++r) wl[hw * REP + r] = l[r];
+    }
+#pragma unroll
+    for (int r = 0; r < REP; ++r)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wacc[((size_t)hw * REP + r) * D + c0 + i] = acc[r][i];
+    __syncthreads();
+    const int64_t rows = (int64_t)B * Hq;
+    for (int idx = tid; idx < REP * (D + 2); idx += kRotBigThreads) {
+        const int r = idx / (D + 2), col = idx % (D + 2);
+        float sum = 0.0f;
+        if (col == 0) {
+            sum = m[r];
+        } else {
+            for (int w = 0; w < 2 * kWarps; ++w) sum += (col == 1 ? wl[w * REP + r] : wacc[((size_t)w * REP + r) * D + (col - 2)]);
+        }
+        const int64_t row = (int64_t)b * Hq + h * REP + r;
+        part[((int64_t)split * rows + row) * (D + 2) + col] = sum;
+    }
+}
+
+bool attn_rotary_staged_supported(int Hq, int Hkv, int D, int G, int S, int K) {
+    const int rep = Hq / Hkv;
+    return D == 128 && K == 256 && S <= 2 && (D / G) >= 8 && (rep == 1 || rep == 2 || rep == 4);
+}
+
+template <int REP>
+static int launch_rotary_staged(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
+                                const __half *vtab, const __half *rope, const int32_t *seq_start, const int32_t *seq_end,
+                                float *part, int B, int Hq, int Hkv, int G, int S, int64_t T_cap, int splits,
+                                cudaStream_t stream) {
+    const size_t tables = (size_t)S * 256 * 16 * 16;
+    const size_t merge = ((size_t)32 * REP + (size_t)32 * REP * 128) * sizeof(float);
+    size_t smem = tables + ((size_t)kRotChunk * REP + (size_t)16 * REP) * sizeof(float);
+    if (smem < merge) smem = merge;
+    auto kernel = attn_rotary_staged_kernel<REP>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((unsigned)splits, (unsigned)Hkv, (unsigned)B);
+    kernel<<<grid, kRotBigThreads, smem, stream>>>(q, kcodes, vcodes, ktab, vtab, rope, seq_start, seq_end, part, B, Hq, Hkv, G,
+                                                   S, T_cap, splits);
+    return launch_status();
+}
+
+int attn_rotary_staged_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
+                                const __half *vtab, const __half *rope, const int32_t *seq_start, const int32_t *seq_end,
+                                float *part, int B, int Hq, int Hkv, int G, int S, int64_t T_cap, int splits,
+                                cudaStream_t stream) {
+    switch (Hq / Hkv) {
+        case 1: return launch_rotary_staged<1>(q, kcodes, vcodes, ktab, vtab, rope, seq_start, seq_end, part, B, Hq, Hkv, G, S, T_cap, splits, stream);
+        case 2: return launch_rotary_staged<2>(q, kcodes, vcodes, ktab, vtab, rope, seq_start, seq_end, part, B, Hq, Hkv, G, S, T_cap, splits, stream);
+        case 4: return launch_rotary_staged<4>(q, kcodes, vcodes, ktab, vtab, rope, seq_start, seq_end, part, B, Hq, Hkv, G, S, T_cap, splits, stream);
+        default: return TACVQ_ERR_UNSUPPORTED;
+    }
+}
+
+// One block per SM.  Among the split counts that leave at least 512 tokens per block, take the one whose
+// last wave is fullest (ties: fewer splits), looking at two to five waves.
+int attn_rotary_staged_splits(int B, int Hkv, int64_t T_cap, int sms) {
+    const int pairs = B * Hkv;
+    int64_t most = (T_cap + 511) / 512;
+    if (most > 64) most = 64;
+    if (most < 1) most = 1;
+    int best = 1;
+    double best_fill = 0.0;
+    for (int splits = 1; splits <= (int)most; ++splits) {
+        const int64_t blocks = (int64_t)pairs * splits;
+        const int64_t waves = (blocks + sms - 1) / sms;
+        if (waves > 5 && best_fill > 0.0) break;
+        double fill = (double)blocks / (double)(waves * sms);
+        if (waves < 2) fill *= 0.9;  // a single wave cannot even out unequal rows
+        if (fill > best_fill + 1e-9) best_fill = fill, best = splits;
+    }
+    return best;
 }
 
 // About four waves of blocks (two resident per SM), at least 256 tokens per block, at most 64 splits.
@@ -302,7 +590,7 @@ int attn_rotary_splits(int B, int Hkv, int64_t T_cap, int sms) {
 }
 
 int attn_rotary_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
-                         const __half *vtab, const __half2 *rope, const int32_t *seq_start, const int32_t *seq_end,
+                         const __half *vtab, const __half *rope, const int32_t *seq_start, const int32_t *seq_end,
                          float *part, int B, int Hq, int Hkv, int D, int G, int S, int K, int64_t T_cap, int splits,
                          cudaStream_t stream) {
 #define TACVQ_CASE(N) \

@@ -204,7 +204,7 @@ def attn_decode(
     """Decode-step attention over codes -> ``(out fp16 [B,Hq,D] | None, state fp32 [B,Hq,2+D] | None)``.
 
     ``q [B,Hq,D]`` fp16 pre-scaled; ``seq_start/seq_end`` int32 ``[B]`` on the device (None = whole buffer).
-    With ``rope`` (from :func:`rope_table`, ``[T_cap, D/2, 2]`` fp16) the key codes are taken as
+    With ``rope`` (from :func:`rope_table`, ``[T_cap, 2, D/2]`` fp16) the key codes are taken as
     pre-rotary keys and every rebuilt key row is rotated at its token index, as the reference's decode
     branch does; ``q`` is then the query already rotated at its own position.
     """
@@ -230,8 +230,8 @@ def attn_decode(
     if want_state and state is None:
         state = torch.empty(b, hq, dim + 2, dtype=torch.float32, device=device)
     if rope is not None:
-        if rope.dtype != torch.float16 or tuple(rope.shape) != (t_cap, dim // 2, 2) or not rope.is_contiguous():
-            raise ValueError("rope must be contiguous fp16 [T_cap, D/2, 2] (cos, sin)")
+        if rope.dtype != torch.float16 or tuple(rope.shape) != (t_cap, 2, dim // 2) or not rope.is_contiguous():
+            raise ValueError("rope must be contiguous fp16 [T_cap, 2, D/2] (cosines, sines)")
         with _on(device):
             status = _lib.load().tacvq_attn_decode_rotary(
                 _ptr(q), _ptr(kcodes), _ptr(vcodes), _ptr(ktab_f16.contiguous()), _ptr(vtab_f16.contiguous()), _ptr(rope),
@@ -251,11 +251,11 @@ def attn_decode(
 
 
 def rope_table(tokens: int, dim: int, theta: float, device, first_position: int = 0) -> torch.Tensor:
-    """``[tokens, dim/2, 2]`` fp16 ``(cos, sin)`` of positions ``first_position ..`` (default rope of Mistral/Llama)."""
+    """``[tokens, 2, dim/2]`` fp16 (cosines, then sines) of positions ``first_position ..`` (default rope of Mistral/Llama)."""
     device = torch.device(device)
     if device.type != "cuda":
         raise RuntimeError("libtacvq runs on CUDA devices only")
-    table = torch.empty(int(tokens), int(dim) // 2, 2, dtype=torch.float16, device=device)
+    table = torch.empty(int(tokens), 2, int(dim) // 2, dtype=torch.float16, device=device)
     with _on(device):
         status = _lib.load().tacvq_rope_table(_ptr(table), int(tokens), int(dim), float(theta), int(first_position), _stream(device))
     _lib.check("tacvq_rope_table", status)

@@ -37,7 +37,7 @@ def test_rope_table_matches_the_reference_arithmetic(device, theta, dim, first):
     cos, sin = O.rotary_table(tokens, dim, theta, first)
     # fp32 cos/sin of two libraries may differ in the last place; after the cast to fp16 that is at most
     # one fp16 step on a vanishing share of the entries
-    for got, want in ((table[..., 0], cos), (table[..., 1], sin)):
+    for got, want in ((table[:, 0], cos), (table[:, 1], sin)):
         differs = got != want
         assert float(differs.float().mean()) < 2e-3
         assert float((got.float() - want.float()).abs().max()) <= 2.0 ** -10
@@ -128,4 +128,4 @@ def test_rotary_argument_errors(device):
     tab = make_tables(gen, 2, 2, 16, 8).to(device)
     q = torch.zeros(1, 8, 128, dtype=torch.float16, device=device)
     with pytest.raises(ValueError):
-        ops.attn_decode(q, codes, codes, tab, tab, rope=torch.zeros(32, 64, 2, dtype=torch.float16, device=device))
+        ops.attn_decode(q, codes, codes, tab, tab, rope=torch.zeros(32, 2, 64, dtype=torch.float16, device=device))
