@@ -192,6 +192,7 @@ def run_ours(args) -> dict:
     # ---- end to end through the public API with host buffers -----------------------------------
     e2e = None
     encode = None
+    rotary = None
     cpu = None
     extras = not args.kernel_only
     if extras and (rank == 0 or world > 1):
@@ -287,6 +288,23 @@ def run_ours(args) -> dict:
             "ms_per_tensor": round(wide_ms, 4),
         }
         del k_rows, v_rows, kcodes, vcodes, wide_tab, wide_codes
+        # the timed workload once more with the rotary step inside (codes of pre-rotary keys, theta 1e6)
+        rope = ops.rope_table(CONTEXT, DIM, 1.0e6, device)
+        for i in range(3):
+            kc, vc = code_sets[i % CODE_SETS]
+            ops.attn_decode(queries[i % CODE_SETS], kc, vc, ktab, vtab, workspace=workspace, out=out, rope=rope)
+        torch.cuda.synchronize(device)
+        rot_steps = 20
+        start.record()
+        for i in range(rot_steps):
+            kc, vc = code_sets[i % CODE_SETS]
+            ops.attn_decode(queries[i % CODE_SETS], kc, vc, ktab, vtab, workspace=workspace, out=out, rope=rope)
+        end.record()
+        torch.cuda.synchronize(device)
+        rot_ms = start.elapsed_time(end) / rot_steps
+        rotary = {"value": round(BATCH / (rot_ms * 1e-3), 1), "unit": UNIT + "; keys stored pre-rotary, rotated inside the kernel",
+                  "ms_per_step": round(rot_ms, 4)}
+        del rope
         if world == 1:
             cpu = cpu_decode_baseline(sample_seconds=12.0)
 
@@ -303,7 +321,7 @@ def run_ours(args) -> dict:
             "l2": f"{CODE_SETS} code sets rotated between steps ({CODE_SETS * 2 * BATCH * KV_HEADS * CONTEXT * 32 // 2**20} MiB > 126 MB L2)",
         },
         "kv_tokens_scanned_per_s": round(BATCH * CONTEXT * world / (ms_per_step * 1e-3), 1),
-        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "encode": encode,
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "encode": encode, "rotary": rotary,
         "gpu_launches": 3 * args.steps, "clocks": clocks.summary(),
     }
     if world > 1:
