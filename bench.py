@@ -146,6 +146,23 @@ def run_ours(args) -> dict:
             ops.encode(rows, ktab, codes=codes)
         torch.cuda.synchronize(device)
         return {"encode_only": True, "rows": 2 * 8192, "steps": args.steps}
+    if args.encode_wide_only:  # profiler case: two full-width codebooks (1 group x 2 stages x 128), reduced batch
+        rows = torch.randn(2, KV_HEADS, 8192, DIM, generator=gen).half().to(device)
+        wide = (torch.randn(KV_HEADS, 2, 1, 256, DIM, generator=gen) * 0.1).half().to(device)
+        codes = torch.empty(2, KV_HEADS, 8192, 2, 1, dtype=torch.uint8, device=device)
+        for _ in range(args.warmup + args.steps):
+            ops.encode(rows, wide, codes=codes)
+        torch.cuda.synchronize(device)
+        return {"encode_wide_only": True, "rows": 2 * 8192, "steps": args.steps}
+    if args.rotary_only:  # profiler case: rotary attention at batch 8 x 8192 tokens (benchmark geometry, shorter context)
+        pgen = torch.Generator(device=device).manual_seed(8601)
+        kc, vc = (torch.randint(0, 256, (BATCH, KV_HEADS, 8192, STAGES, GROUPS), dtype=torch.uint8, device=device, generator=pgen) for _ in range(2))
+        query = (torch.randn(BATCH, Q_HEADS, DIM, device=device, generator=pgen) / DIM**0.5).half()
+        rope = ops.rope_table(8192, DIM, 1.0e6, device)
+        for _ in range(args.warmup + args.steps):
+            ops.attn_decode(query, kc, vc, ktab, vtab, rope=rope)
+        torch.cuda.synchronize(device)
+        return {"rotary_only": True, "tokens": 8192, "steps": args.steps}
     dgen = torch.Generator(device=device).manual_seed(8601 + rank)
     code_sets = [
         tuple(torch.randint(0, 256, (BATCH, KV_HEADS, CONTEXT, STAGES, GROUPS), dtype=torch.uint8, device=device, generator=dgen) for _ in range(2))
@@ -515,6 +532,8 @@ def main() -> None:
     parser.add_argument("--workload", choices=("decode32k", "seqsplit131k"), default="decode32k",
                         help="decode32k: the headline configuration; seqsplit131k: one sequence split across the ranks (extra)")
     parser.add_argument("--encode-only", action="store_true", help="run only the layer encode (used for profiler captures)")
+    parser.add_argument("--encode-wide-only", action="store_true", help="run only a full-width (d = 128) encode (profiler captures)")
+    parser.add_argument("--rotary-only", action="store_true", help="run only rotary attention at 8192 tokens (profiler captures)")
     parser.add_argument("--kernel-only", action="store_true", help="time the decode-attention launches only (used for profiler captures)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)

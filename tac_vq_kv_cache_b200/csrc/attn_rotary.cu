@@ -300,7 +300,13 @@ static int rotary_dpl(const __half *q, const uint8_t *kcodes, const uint8_t *vco
 // read sixteen different pieces, which is the minimum number of shared-memory wavefronts.
 // ---------------------------------------------------------------------------------------------------
 
-constexpr int kRotBigThreads = 512;
+#ifndef TACVQ_ROT_THREADS
+#define TACVQ_ROT_THREADS 512
+#endif
+#ifndef TACVQ_ROT_PREFETCH_ROPE
+#define TACVQ_ROT_PREFETCH_ROPE 1
+#endif
+constexpr int kRotBigThreads = TACVQ_ROT_THREADS;
 constexpr int kRotChunk = 4096;
 
 template <int REP>
@@ -392,12 +398,20 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
         for (int base = 0; base < n; base += 2 * kWarps) {
             const int local = base + 2 * warp + sub;  // lanes past the end redo the last token and drop it
             const int code_now[2] = {code_next[0], code_next[1]};
+#if TACVQ_ROT_PREFETCH_ROPE
             const uint4 cos_now = cos_next, sin_now = sin_next;
+#else
+            const int t_now = chunk + min(local, n - 1);
+            const uint4 cos_now = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t_now * D + f0));
+            const uint4 sin_now = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t_now * D + D / 2 + f0));
+#endif
             if (base + 2 * kWarps < n) {
                 const int t = chunk + min(local + 2 * kWarps, n - 1);
                 fetch_codes(kcodes + (code_row + t) * slots, code_next);
+#if TACVQ_ROT_PREFETCH_ROPE
                 cos_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + f0));
                 sin_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + D / 2 + f0));
+#endif
             }
             __half2 krow[4];
             rebuild8(code_now, krow);
@@ -534,8 +548,8 @@ static int launch_rotary_staged(const __half *q, const uint8_t *kcodes, const ui
                                 float *part, int B, int Hq, int Hkv, int G, int S, int64_t T_cap, int splits,
                                 cudaStream_t stream) {
     const size_t tables = (size_t)S * 256 * 16 * 16;
-    const size_t merge = ((size_t)32 * REP + (size_t)32 * REP * 128) * sizeof(float);
-    size_t smem = tables + ((size_t)kRotChunk * REP + (size_t)16 * REP) * sizeof(float);
+    const size_t merge = ((size_t)(kRotBigThreads / 16) * REP + (size_t)(kRotBigThreads / 16) * REP * 128) * sizeof(float);
+    size_t smem = tables + ((size_t)kRotChunk * REP + (size_t)(kRotBigThreads / 32) * REP) * sizeof(float);
     if (smem < merge) smem = merge;
     auto kernel = attn_rotary_staged_kernel<REP>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
