@@ -276,11 +276,13 @@ int tacvq_attn_decode_rotary(const uint16_t *q_f16, const uint8_t *kcodes, const
     cudaStream_t s = (cudaStream_t)stream;
     if (attn_rotary_staged_supported(Hq, Hkv, D, G, S, K) && (((uintptr_t)ktab_f16 | (uintptr_t)vtab_f16 | (uintptr_t)rope_table) & 15) == 0) {
         const int staged = attn_rotary_staged_splits(B, Hkv, T_cap, sm_count());
+        if (staged > 0) {
         int st = attn_rotary_staged_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
                                              (const __half *)vtab_f16, (const __half *)rope_table, seq_start, seq_end,
                                              (float *)workspace, B, Hq, Hkv, G, S, T_cap, staged, s);
         if (st != TACVQ_OK) return st;
         return attn_combine_dispatch((const float *)workspace, staged, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);
+        }
     }
     const int splits = attn_rotary_splits(B, Hkv, T_cap, sm_count());
     int st = attn_rotary_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16, (const __half *)vtab_f16,

@@ -301,7 +301,7 @@ static int rotary_dpl(const __half *q, const uint8_t *kcodes, const uint8_t *vco
 // ---------------------------------------------------------------------------------------------------
 
 #ifndef TACVQ_ROT_THREADS
-#define TACVQ_ROT_THREADS 512
+#define TACVQ_ROT_THREADS 1024
 #endif
 #ifndef TACVQ_ROT_PREFETCH_ROPE
 #define TACVQ_ROT_PREFETCH_ROPE 1
@@ -371,19 +371,14 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
     for (int r = 0; r < REP; ++r)
 #pragma unroll
         for (int i = 0; i < 8; ++i) qv[r][i] = __half2float(q[((int64_t)b * Hq + h * REP + r) * D + c0 + i]);
-    float m[REP], l[REP], acc[REP][8];
+    float m[REP], l[REP], acc[REP][8];  // the sums are only live in the value pass: registers for the key pass
 #pragma unroll
-    for (int r = 0; r < REP; ++r) {
-        m[r] = -INFINITY;
-        l[r] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[r][i] = 0.0f;
-    }
+    for (int r = 0; r < REP; ++r) m[r] = -INFINITY;
     const int64_t code_row = ((int64_t)b * Hkv + h) * T_cap;
+    const int chunk = lo;
+    const int n = hi - lo;  // at most kRotChunk: the launcher picks the split count for that
 
-    for (int chunk = lo; chunk < hi; chunk += kRotChunk) {
-        const int n = min(kRotChunk, hi - chunk);
-        __syncthreads();  // the previous chunk's value pass is over
+    if (n > 0) {
         load_tables(ktab);
         __syncthreads();
         // ---- pass K: scores of the chunk ------------------------------------------------------------
@@ -470,13 +465,7 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
         __syncthreads();
 #pragma unroll
         for (int r = 0; r < REP; ++r) {
-            float now = m[r];
-            for (int w = 0; w < kWarps; ++w) now = fmaxf(now, red[w * REP + r]);
-            const float scale = (m[r] == -INFINITY) ? 0.0f : __expf(m[r] - now);
-            l[r] *= scale;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[r][i] *= scale;
-            m[r] = now;
+            for (int w = 0; w < kWarps; ++w) m[r] = fmaxf(m[r], red[w * REP + r]);
         }
         for (int i = tid; i < n; i += kRotBigThreads) {
 #pragma unroll
@@ -485,6 +474,12 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
         load_tables(vtab);  // the key tables are no longer read: every warp passed the barrier above
         __syncthreads();
         // ---- pass V --------------------------------------------------------------------------------
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+            l[r] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[r][i] = 0.0f;
+        }
         fetch_codes(vcodes + (code_row + chunk + min(2 * warp + sub, n - 1)) * slots, code_next);
         for (int base = 0; base < n; base += 2 * kWarps) {
             const int local = base + 2 * warp + sub;
@@ -509,6 +504,14 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
         }
     }
 
+    if (n <= 0) {
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+            l[r] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[r][i] = 0.0f;
+        }
+    }
     // ---- sum the half-warps (they share m), write this split's partial state ------------------------
     __syncthreads();
     float *wl = reinterpret_cast<float *>(smem_raw);       // [2*kWarps][REP]
@@ -579,9 +582,12 @@ int attn_rotary_staged_splits(int B, int Hkv, int64_t T_cap, int sms) {
     int64_t most = (T_cap + 511) / 512;
     if (most > 64) most = 64;
     if (most < 1) most = 1;
-    int best = 1;
+    const int least = (int)((T_cap + kRotChunk - 1) / kRotChunk);  // a block holds at most kRotChunk scores
+    if (least > 64) return 0;                                      // too long for this kernel
+    if (most < least) most = least;
+    int best = least > 1 ? least : 1;
     double best_fill = 0.0;
-    for (int splits = 1; splits <= (int)most; ++splits) {
+    for (int splits = best; splits <= (int)most; ++splits) {
         const int64_t blocks = (int64_t)pairs * splits;
         const int64_t waves = (blocks + sms - 1) / sms;
         if (waves > 5 && best_fill > 0.0) break;
