@@ -29,7 +29,11 @@ size_t attn_gsrq_workspace_bytes(int B, int Hq, int Hkv, int D, int sms);
 int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
                        const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, void *workspace,
                        __half *out, float *state_out, int B, int Hq, int Hkv, int64_t T_cap, int sms,
-                       cudaStream_t stream);
+                       cudaStream_t stream, bool after_prologue = false);
+int decode_prologue_dispatch(const void *k_rows, const void *v_rows, int rows_dtype, int64_t sxb, int64_t sxh, int64_t sxt,
+                             const __half *ktab, const __half *vtab, uint8_t *kcodes, uint8_t *vcodes, int32_t *seq_start,
+                             int32_t *seq_end, int start, int end, int B, int H, int T, int D, int G, int S, int K, int64_t t0,
+                             int64_t T_cap, cudaStream_t stream);
 
 int attn_rotary_splits(int B, int Hkv, int64_t T_cap, int sms);
 bool attn_rotary_staged_supported(int Hq, int Hkv, int D, int G, int S, int K);
@@ -307,6 +311,33 @@ int tacvq_decode_step(const uint16_t *q_f16, const void *k_rows, const void *v_r
     if (!k_rows || !v_rows || !seq_start || !seq_end) return TACVQ_ERR_NULL;
     if (length < 0 || window < 0 || T_new <= 0 || length + T_new > T_cap) return TACVQ_ERR_RANGE;
     const int64_t row = (int64_t)T_new * D;
+    {
+        // Fast path: one launch encodes both sides and sets the ranges, and the attention kernels that do
+        // not read its results start while it runs.  Every argument check of the separate calls is made first.
+        const int64_t new_end = length + T_new;
+        const int64_t new_start = (window > 0 && new_end > window) ? new_end - window : 0;
+        const bool plain = dtype_ok(rows_dtype) && q_f16 && ktab_f16 && vtab_f16 && kcodes && vcodes && (out_f16 || state_out) &&
+                           check_code_geometry(B, Hkv, T_new, D, G, S, K, length, T_cap) == TACVQ_OK &&
+                           check_attn_geometry(B, Hq, Hkv, D, G, S, K) == TACVQ_OK && T_cap <= 0x7fffffff && workspace &&
+                           ((uintptr_t)workspace & 255) == 0 && workspace_bytes >= tacvq_attn_workspace_bytes(B, Hq, Hkv, D, G, S) &&
+                           (((uintptr_t)kcodes | (uintptr_t)vcodes) & 15) == 0;
+        if (plain) {
+            cudaStream_t s = (cudaStream_t)stream;
+            const int pro = decode_prologue_dispatch(k_rows, v_rows, rows_dtype, (int64_t)Hkv * row, row, D, (const __half *)ktab_f16,
+                                                     (const __half *)vtab_f16, kcodes, vcodes, seq_start, seq_end, (int)new_start,
+                                                     (int)new_end, B, Hkv, T_new, D, G, S, K, length, T_cap, s);
+            if (pro == TACVQ_OK) {
+                if (attn_gsrq_supported(Hq, Hkv, D, G, S, K) && gsrq_batch_ok(B, Hkv)) {
+                    return attn_gsrq_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
+                                              (const __half *)vtab_f16, seq_start, seq_end, workspace, (__half *)out_f16,
+                                              state_out, B, Hq, Hkv, T_cap, sm_count(), s, true);
+                }
+                return tacvq_attn_decode(q_f16, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, workspace,
+                                         workspace_bytes, out_f16, state_out, B, Hq, Hkv, D, G, S, K, T_cap, stream);
+            }
+            if (pro != TACVQ_ERR_UNSUPPORTED) return pro;
+        }
+    }
     int st = tacvq_encode(k_rows, rows_dtype, (int64_t)Hkv * row, row, D, ktab_f16, nullptr, kcodes, nullptr, TACVQ_F16, B,
                           Hkv, T_new, D, G, S, K, length, T_cap, stream);
     if (st != TACVQ_OK) return st;

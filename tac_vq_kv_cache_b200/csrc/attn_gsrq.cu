@@ -183,7 +183,11 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
                          const __half *__restrict__ vtab, uint2 *__restrict__ lut_g, uint4 *__restrict__ vperm_g,
                          float *__restrict__ scale_g, int *__restrict__ tickets, const int32_t *__restrict__ seq_start,
                          const int32_t *__restrict__ seq_end, __half *__restrict__ out, float *__restrict__ state_out,
-                         int B, int Hkv, int T_cap) {
+                         int B, int Hkv, int T_cap, int chained) {
+    // chained != 0: launched as a programmatic dependent of a kernel that is still writing the visible
+    // ranges and the newest codes (one decode step).  Nothing here reads those (the ranges of a decode step
+    // are never empty, so the empty-row case below is skipped); before it ends, every thread waits for
+    // that kernel, so that the scan, which waits for this grid, also sees that kernel's results.
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int pairs = B * Hkv;
     if ((int)blockIdx.x >= 2 * pairs) {
@@ -198,6 +202,7 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
             const __half *src = vtab + ((((size_t)h * kStages + s) * kGroups + g) * kWords + code) * kSub;
             vperm_g[(size_t)h * (kWords * kSlots) + j] = __ldg(reinterpret_cast<const uint4 *>(src));
         }
+        if (chained) wait_for_previous_kernel();
         return;
     }
     extern __shared__ __align__(128) unsigned char psm[];
@@ -209,7 +214,7 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
     const int Hq = Hkv * kRep;
     if (stage == 0) {
         if (tid == 0) tickets[pair] = 0;  // the scan counts finished blocks per pair from zero
-        if (row_tokens(seq_start, seq_end, b, T_cap) == 0) {
+        if (!chained && row_tokens(seq_start, seq_end, b, T_cap) == 0) {
             // an empty range never reaches the scan: its result is defined here (out 0, m -inf, l 0, acc 0)
             for (int o = tid; o < kRep * kDim; o += kPrepThreads) {
                 const size_t row = (size_t)b * Hq + h * kRep + (o >> 7);
@@ -314,6 +319,7 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
         packed.y = e[2] | (e[3] << 16);
         lut_g[((size_t)pair * kWords + code) * kSlots + stage * kGroups + g] = packed;
     }
+    if (chained) wait_for_previous_kernel();
 }
 
 // Scan blocks whose share of work units [start_c, start_{c+1}) gives them at least one tile of the pair
@@ -850,7 +856,7 @@ size_t attn_gsrq_workspace_bytes(int B, int Hq, int Hkv, int D, int sms) {
 int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
                        const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, void *workspace,
                        __half *out, float *state_out, int B, int Hq, int Hkv, int64_t T_cap, int sms,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, bool after_prologue) {
     (void)Hq;
     if (B > gsrq::kMaxBatch || sms > gsrq::kMaxScanBlocks) return TACVQ_ERR_UNSUPPORTED;
     if (((T_cap + gsrq::kTile - 1) / gsrq::kTile + gsrq::kItemCost) * B * Hkv > 0x7fffffffLL) return TACVQ_ERR_UNSUPPORTED;
@@ -881,9 +887,18 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
     uint4 *vperm = (uint4 *)(base + ws.vperm);
     float *scale = (float *)(base + ws.scale);
     int *tickets = (int *)(base + ws.tickets);
-    gsrq::attn_gsrq_prepare_kernel<<<2 * B * Hkv + gsrq::kPrepVBlocks * Hkv, gsrq::kPrepThreads, gsrq::kPrepSmemBytes, stream>>>(
-        q, ktab, vtab, lut, vperm, scale, tickets, seq_start, seq_end, out, state_out, B, Hkv, (int)T_cap);
-    int st = launch_status();
+    int st;
+    if (after_prologue && TACVQ_PDL) {
+        // the previous launch on this stream is the decode-step prologue, which lets this grid start at once
+        cudaError_t e = launch_dependent(gsrq::attn_gsrq_prepare_kernel, dim3(2 * B * Hkv + gsrq::kPrepVBlocks * Hkv),
+                                         dim3(gsrq::kPrepThreads), gsrq::kPrepSmemBytes, stream, q, ktab, vtab, lut, vperm, scale,
+                                         tickets, seq_start, seq_end, out, state_out, B, Hkv, (int)T_cap, 1);
+        st = e == cudaSuccess ? launch_status() : (int)e;
+    } else {
+        gsrq::attn_gsrq_prepare_kernel<<<2 * B * Hkv + gsrq::kPrepVBlocks * Hkv, gsrq::kPrepThreads, gsrq::kPrepSmemBytes, stream>>>(
+            q, ktab, vtab, lut, vperm, scale, tickets, seq_start, seq_end, out, state_out, B, Hkv, (int)T_cap, 0);
+        st = launch_status();
+    }
     if (st != TACVQ_OK) return st;
 #if TACVQ_PDL
     {

@@ -162,13 +162,10 @@ encode_small_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t 
 // above, so the codes are too.
 
 template <int DSUB, typename XT>
-__global__ void __launch_bounds__(256)
-encode_rows_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const __half *__restrict__ tables,
-                   const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
-                   int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap) {
-    const int lane = threadIdx.x & 31;
-    const int64_t unit = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (unit >= (int64_t)B * T * H * G) return;
+__device__ __forceinline__ void encode_row_unit(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt,
+                                                const __half *__restrict__ tables, const float *__restrict__ sqnorm_in,
+                                                uint8_t *__restrict__ codes, void *__restrict__ recon, int recon_dtype, int H,
+                                                int T, int G, int S, int K, int64_t t0, int64_t T_cap, int64_t unit, int lane) {
     const int g = (int)(unit % G);
     const int h = (int)((unit / G) % H);
     const int64_t row = unit / ((int64_t)G * H);
@@ -225,6 +222,56 @@ encode_rows_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t s
             else store_as<float>((float *)recon + o + i, dec[i]);
         }
     }
+}
+
+template <int DSUB, typename XT>
+__global__ void __launch_bounds__(256)
+encode_rows_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const __half *__restrict__ tables,
+                   const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
+                   int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap) {
+    const int lane = threadIdx.x & 31;
+    const int64_t unit = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (unit >= (int64_t)B * T * H * G) return;
+    encode_row_unit<DSUB, XT>(x, sxb, sxh, sxt, tables, sqnorm_in, codes, recon, recon_dtype, H, T, G, S, K, t0, T_cap, unit, lane);
+}
+
+// One decode step's bookkeeping in a single launch: the new rows of K and of V are encoded in place (a
+// warp per (row, head, group) and side, as above) and every row's visible range is set.  The kernel lets
+// its successor start at once (programmatic dependent launch): a successor that needs these outputs
+// waits for this grid by itself.
+template <int DSUB, typename XT>
+__global__ void __launch_bounds__(256)
+decode_prologue_kernel(const XT *__restrict__ k_rows, const XT *__restrict__ v_rows, int64_t sxb, int64_t sxh, int64_t sxt,
+                       const __half *__restrict__ ktab, const __half *__restrict__ vtab, uint8_t *__restrict__ kcodes,
+                       uint8_t *__restrict__ vcodes, int32_t *__restrict__ seq_start, int32_t *__restrict__ seq_end, int start,
+                       int end, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (blockIdx.x == 0) {
+        for (int b = threadIdx.x; b < B; b += blockDim.x) {
+            seq_start[b] = start;
+            seq_end[b] = end;
+        }
+    }
+    const int lane = threadIdx.x & 31;
+    const int64_t units = (int64_t)B * T * H * G;
+    int64_t unit = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const bool value_side = unit >= units;
+    if (value_side) unit -= units;
+    if (unit >= units) return;
+    encode_row_unit<DSUB, XT>(value_side ? v_rows : k_rows, sxb, sxh, sxt, value_side ? vtab : ktab, nullptr,
+                              value_side ? vcodes : kcodes, nullptr, TACVQ_F16, H, T, G, S, K, t0, T_cap, unit, lane);
+}
+
+template <int DSUB, typename XT>
+static int launch_prologue(const void *k_rows, const void *v_rows, int64_t sxb, int64_t sxh, int64_t sxt, const __half *ktab,
+                           const __half *vtab, uint8_t *kcodes, uint8_t *vcodes, int32_t *seq_start, int32_t *seq_end,
+                           int start, int end, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap,
+                           cudaStream_t stream) {
+    const int64_t units = (int64_t)B * T * H * G;
+    decode_prologue_kernel<DSUB, XT><<<(unsigned)((2 * units + 7) / 8), 256, 0, stream>>>(
+        (const XT *)k_rows, (const XT *)v_rows, sxb, sxh, sxt, ktab, vtab, kcodes, vcodes, seq_start, seq_end, start, end, B, H,
+        T, G, S, K, t0, T_cap);
+    return launch_status();
 }
 
 template <int DSUB, typename XT>
@@ -474,6 +521,29 @@ static int dispatch_d(const EncodeArgs &a) {
         case 128: return launch_large<128, XT, TT>(a);
         default: return TACVQ_ERR_UNSUPPORTED;
     }
+}
+
+// Returns TACVQ_ERR_UNSUPPORTED when the step is not a handful of rows of narrow groups; the caller then
+// makes the three separate launches.
+int decode_prologue_dispatch(const void *k_rows, const void *v_rows, int rows_dtype, int64_t sxb, int64_t sxh, int64_t sxt,
+                             const __half *ktab, const __half *vtab, uint8_t *kcodes, uint8_t *vcodes, int32_t *seq_start,
+                             int32_t *seq_end, int start, int end, int B, int H, int T, int D, int G, int S, int K, int64_t t0,
+                             int64_t T_cap, cudaStream_t stream) {
+    if ((int64_t)B * T > kFewRows) return TACVQ_ERR_UNSUPPORTED;
+#define TACVQ_CASE(N)                                                                                                          \
+    case N:                                                                                                                    \
+        return rows_dtype == TACVQ_F16                                                                                         \
+                   ? launch_prologue<N, __half>(k_rows, v_rows, sxb, sxh, sxt, ktab, vtab, kcodes, vcodes, seq_start, seq_end, \
+                                                start, end, B, H, T, G, S, K, t0, T_cap, stream)                               \
+                   : launch_prologue<N, float>(k_rows, v_rows, sxb, sxh, sxt, ktab, vtab, kcodes, vcodes, seq_start, seq_end,  \
+                                               start, end, B, H, T, G, S, K, t0, T_cap, stream);
+    switch (D / G) {
+        TACVQ_CASE(4)
+        TACVQ_CASE(8)
+        TACVQ_CASE(16)
+        default: return TACVQ_ERR_UNSUPPORTED;
+    }
+#undef TACVQ_CASE
 }
 
 int encode_dispatch(const EncodeArgs &a) {
