@@ -283,8 +283,37 @@ table_sqnorm_kernel(const __half *__restrict__ tables, float *__restrict__ out, 
     }
 }
 
+// d a multiple of 32: eight neighbouring lanes per word.  Lane j owns running sum j of each of the four
+// sets (element i goes to set (i/8)%4, sum i%8), adds its sets ((0+1)+2)+3, and the eight sums are added
+// 0..7 - the library's order for such d.
+__global__ void __launch_bounds__(256)
+table_sqnorm_wide_kernel(const __half *__restrict__ tables, float *__restrict__ out, int64_t words, int d) {
+    const int64_t slot = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31, j = lane & 7;
+    const int64_t word = slot >> 3;
+    const __half *src = tables + (word < words ? word : words - 1) * d;  // spare lanes redo the last word
+    float set[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int i = 0; i < d; i += 32) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float v = __half2float(src[i + 8 * u + j]);
+            set[u] = __fadd_rn(set[u], __fmul_rn(v, v));
+        }
+    }
+    const float mine = __fadd_rn(__fadd_rn(__fadd_rn(set[0], set[1]), set[2]), set[3]);
+    const int first = lane & 24;
+    float total = __shfl_sync(0xffffffffu, mine, first);
+#pragma unroll
+    for (int k = 1; k < 8; ++k) total = __fadd_rn(total, __shfl_sync(0xffffffffu, mine, first + k));
+    if (j == 0 && word < words) out[word] = total;
+}
+
 int table_sqnorm_dispatch(const __half *tables, float *out, int64_t words, int d, cudaStream_t stream) {
     if (words == 0) return TACVQ_OK;
+    if (d % 32 == 0) {
+        table_sqnorm_wide_kernel<<<(unsigned)((words * 8 + 255) / 256), 256, 0, stream>>>(tables, out, words, d);
+        return launch_status();
+    }
     table_sqnorm_kernel<<<(unsigned)((words + 255) / 256), 256, 0, stream>>>(tables, out, words, d);
     return launch_status();
 }
