@@ -191,6 +191,40 @@ def test_filtered_search_is_exact_on_adversarial_rows(device, regime, sub):
         assert not bool(((codes[:, :, :, 0] >= 100) & (codes[:, :, :, 0] < 140)).any())
 
 
+@pytest.mark.parametrize(
+    "name,shape,stages,groups,outliers",
+    [
+        ("gsrq2_layer_full", (4, 8, 8192, 128), 2, 16, 4),        # the benchmark's encode configuration
+        ("cq_fullwidth_full", (16, 8, 16384, 128), 2, 1, 0),      # two full-width codebooks, full batch
+    ],
+)
+def test_full_size_encode_agrees_with_the_oracle_on_sampled_rows(device, name, shape, stages, groups, outliers):
+    """Rows are independent, so the full-size launch (grid loops, tile tails, every block) is checked by
+    running the oracle on a random sample of its rows; plus determinism and decode(codes) == recon."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(8601)
+    sub = shape[-1] // groups
+    tables = make_tables(gen, shape[1], stages, groups, sub, [0.1] * stages if sub == 128 else None)
+    dgen = torch.Generator(device=device).manual_seed(8601)
+    states = torch.randn(*shape, device=device, generator=dgen)
+    if outliers:
+        for h in range(shape[1]):
+            states[:, h, :, torch.randperm(shape[-1], generator=gen)[:outliers].to(device)] *= 8.0
+    states = states.half()
+    codes, recon = ops.encode(states, tables.to(device))
+    again, _ = ops.encode(states, tables.to(device), want_recon=False)
+    assert torch.equal(codes, again)
+    assert torch.equal(ops.decode(codes, tables.to(device), torch.float16), recon)
+    pick = torch.randperm(shape[2], generator=gen)[:512].sort().values
+    sample = states[:, :, pick.to(device)].cpu().contiguous()
+    want_codes, want_recon = C.encode(sample, tables)
+    assert torch.equal(codes[:, :, pick.to(device)].cpu(), want_codes)
+    assert torch.equal(recon[:, :, pick.to(device)].cpu(), want_recon)
+    ends = torch.tensor([0, 1, shape[2] - 2, shape[2] - 1])   # first and last rows of every (batch, head)
+    edge_codes, _ = C.encode(states[:, :, ends.to(device)].cpu().contiguous(), tables, want_recon=False)
+    assert torch.equal(codes[:, :, ends.to(device)].cpu(), edge_codes)
+
+
 @pytest.mark.parametrize("tokens", [0, 1, 31, 33, 127, 129, 513])
 def test_ragged_token_counts_and_in_place_append(device, tokens):
     ops = _ops()
