@@ -62,6 +62,7 @@ class VQCodeCache:
         self._range = torch.zeros(2, batch, dtype=torch.int32, device=self.device)  # [start; end) per row
         self._range_is = (0, 0)
         self._workspace: torch.Tensor | None = None
+        self._step_key, self._step_args = None, None  # decode_step's checked and marshalled arguments
         self.rope = None if rope_theta is None else ops.rope_table(self.max_tokens, self.dim, float(rope_theta), self.device)
 
     def reset(self) -> None:
@@ -126,29 +127,44 @@ class VQCodeCache:
                 out.copy_(result)
                 return out
             return result
-        tokens = int(raw_key.shape[2])
-        if raw_key.shape != raw_value.shape or tuple(raw_key.shape[:2]) != (self.batch, self.heads) or raw_key.shape[3] != self.dim:
-            raise ValueError("rows must be [B,H,T,D] matching the cache geometry")
-        if raw_key.dtype != raw_value.dtype or not (raw_key.is_contiguous() and raw_value.is_contiguous() and query.is_contiguous()):
-            raise ValueError("query and rows must be contiguous, rows of one dtype")
+        # A decoding loop calls this with the same buffers every step: the argument checks and the
+        # marshalling of everything but `length` are done once per set of buffers.
+        if not (raw_key.is_contiguous() and raw_value.is_contiguous() and query.is_contiguous()):
+            raise ValueError("query and rows must be contiguous")
+        key = (query.data_ptr(), raw_key.data_ptr(), raw_value.data_ptr(), 0 if out is None else out.data_ptr(),
+               raw_key.dtype, raw_value.dtype, query.dtype, tuple(raw_key.shape), tuple(raw_value.shape), tuple(query.shape))
+        if key != self._step_key:
+            tokens = int(raw_key.shape[2])
+            if raw_key.shape != raw_value.shape or tuple(raw_key.shape[:2]) != (self.batch, self.heads) or raw_key.shape[3] != self.dim:
+                raise ValueError("rows must be [B,H,T,D] matching the cache geometry")
+            if raw_key.dtype != raw_value.dtype:
+                raise ValueError("rows must be of one dtype")
+            ops._require_cuda(query, raw_key, raw_value, out)
+            hq = int(query.shape[1])
+            if tuple(query.shape) != (self.batch, hq, self.dim) or query.dtype != torch.float16:
+                raise ValueError("query must be fp16 [B,Hq,D]")
+            if out is not None and (tuple(out.shape) != (self.batch, hq, self.dim) or out.dtype != torch.float16 or not out.is_contiguous()):
+                raise ValueError("out must be contiguous fp16 [B,Hq,D]")
+            if self._workspace is None:
+                need = ops.attn_workspace_bytes(self.batch, hq, self.heads, self.dim, self.groups, self.stages)
+                if need == 0:
+                    raise ValueError("attention geometry not supported")
+                self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+            head = (query.data_ptr(), raw_key.data_ptr(), raw_value.data_ptr(), ops._DTYPE_TAG[raw_key.dtype],
+                    self.key_tables.data_ptr(), self.value_tables.data_ptr(), self.key.data_ptr(), self.value.data_ptr(),
+                    self._range[0].data_ptr(), self._range[1].data_ptr())
+            tail = (self.batch, hq, self.heads, self.dim, self.groups, self.stages, int(self.key_tables.shape[-2]), tokens,
+                    self.max_tokens)
+            self._step_key, self._step_args = (key if out is not None else None), (head, tail, tokens, hq)
+        head, tail, tokens, hq = self._step_args
         if self.length + tokens > self.max_tokens:
             raise ValueError("code cache is full")
-        ops._require_cuda(query, raw_key, raw_value)
-        hq = int(query.shape[1])
-        if self._workspace is None:
-            need = ops.attn_workspace_bytes(self.batch, hq, self.heads, self.dim, self.groups, self.stages)
-            if need == 0:
-                raise ValueError("attention geometry not supported")
-            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
         if out is None:
             out = torch.empty(self.batch, hq, self.dim, dtype=torch.float16, device=self.device)
         with ops._on(self.device):
             status = _lib.load().tacvq_decode_step(
-                query.data_ptr(), raw_key.data_ptr(), raw_value.data_ptr(), ops._DTYPE_TAG[raw_key.dtype],
-                self.key_tables.data_ptr(), self.value_tables.data_ptr(), self.key.data_ptr(), self.value.data_ptr(),
-                self._range[0].data_ptr(), self._range[1].data_ptr(), self.length, 0 if self.window is None else self.window,
-                self._workspace.data_ptr(), self._workspace.numel(), out.data_ptr(), 0, self.batch, hq, self.heads, self.dim,
-                self.groups, self.stages, int(self.key_tables.shape[-2]), tokens, self.max_tokens, ops._stream(self.device),
+                *head, self.length, 0 if self.window is None else self.window, self._workspace.data_ptr(),
+                self._workspace.numel(), out.data_ptr(), 0, *tail, ops._stream(self.device),
             )
         _lib.check("tacvq_decode_step", status)
         self.length += tokens
