@@ -247,6 +247,18 @@ int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_
         if (fw != TACVQ_OK) return fw;
         return attn_combine_dispatch((const float *)workspace, splits, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);
     }
+    if (attn_rotary_staged_supported(Hq, Hkv, D, G, S, K) && (((uintptr_t)ktab_f16 | (uintptr_t)vtab_f16) & 15) == 0) {
+        // head_dim 128 in pieces of 8 channels, at most two stages (e.g. one-stage grouped CQ): score table and
+        // value tables in shared memory, two passes (the staged kernel of attn_rotary.cu without its rotary step)
+        const int staged = attn_rotary_staged_splits(B, Hkv, T_cap, sm_count());
+        if (staged > 0) {
+            int st = attn_rotary_staged_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
+                                                 (const __half *)vtab_f16, nullptr, seq_start, seq_end, (float *)workspace,
+                                                 B, Hq, Hkv, G, S, T_cap, staged, s);
+            if (st != TACVQ_OK) return st;
+            return attn_combine_dispatch((const float *)workspace, staged, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);
+        }
+    }
     int st = attn_generic_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
                                    (const __half *)vtab_f16, seq_start, seq_end, (float *)workspace, B, Hq, Hkv, D, G,
                                    S, K, T_cap, splits, s);

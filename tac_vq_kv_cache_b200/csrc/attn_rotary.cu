@@ -303,13 +303,13 @@ static int rotary_dpl(const __half *q, const uint8_t *kcodes, const uint8_t *vco
 #ifndef TACVQ_ROT_THREADS
 #define TACVQ_ROT_THREADS 1024
 #endif
-#ifndef TACVQ_ROT_PREFETCH_ROPE
-#define TACVQ_ROT_PREFETCH_ROPE 1
-#endif
 constexpr int kRotBigThreads = TACVQ_ROT_THREADS;
 constexpr int kRotChunk = 4096;
 
-template <int REP>
+// ROTARY = false: the same two passes without the rotary step.  The key pass then needs no key rows at
+// all: the block first fills the table area with scores, lut[stage][code][piece] = q_r . (8 channels of the
+// word), r < REP, and a token's score is the sum of its S x 16 entries.
+template <int REP, bool ROTARY>
 __global__ void __launch_bounds__(kRotBigThreads, 1)
 attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ kcodes, const uint8_t *__restrict__ vcodes,
                           const __half *__restrict__ ktab, const __half *__restrict__ vtab, const __half *__restrict__ rope,
@@ -345,6 +345,28 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
             tab[idx] = __ldg(reinterpret_cast<const uint4 *>(src + ((((int64_t)h * S + s) * G + g) * K + code) * d + off));
         }
     };
+    auto build_score_table = [&]() {  // ROTARY = false only; the query rows sit at the start of the score area
+        float *q_s = score;
+        for (int i = tid; i < REP * D; i += kRotBigThreads)
+            q_s[i] = __half2float(q[((int64_t)b * Hq + h * REP + i / D) * D + i % D]);
+        __syncthreads();
+        float4 *lut = reinterpret_cast<float4 *>(tab);
+        for (int idx = tid; idx < S * K * 16; idx += kRotBigThreads) {
+            const int p = idx & 15, code = (idx >> 4) & 255, s = idx >> 12;
+            const int g = (8 * p) / d, off = (8 * p) % d;
+            const uint4 w = __ldg(reinterpret_cast<const uint4 *>(ktab + ((((int64_t)h * S + s) * G + g) * K + code) * d + off));
+            const __half2 *hp = reinterpret_cast<const __half2 *>(&w);
+            float dot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(hp[i]);
+#pragma unroll
+                for (int r = 0; r < REP; ++r)
+                    dot[r] = fmaf(q_s[r * D + 8 * p + 2 * i + 1], f.y, fmaf(q_s[r * D + 8 * p + 2 * i], f.x, dot[r]));
+            }
+            lut[idx] = make_float4(dot[0], dot[1], dot[2], dot[3]);
+        }
+    };
     // This lane's eight channels of a token from the resident tables, as the fp16 row the reference
     // keeps: with at most two stages the fp32 sum of two fp16 words is exact, so its single rounding to
     // fp16 is what a packed fp16 add returns.
@@ -367,10 +389,12 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
     };
 
     float qv[REP][8];
+    if constexpr (ROTARY) {
 #pragma unroll
-    for (int r = 0; r < REP; ++r)
+        for (int r = 0; r < REP; ++r)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) qv[r][i] = __half2float(q[((int64_t)b * Hq + h * REP + r) * D + c0 + i]);
+            for (int i = 0; i < 8; ++i) qv[r][i] = __half2float(q[((int64_t)b * Hq + h * REP + r) * D + c0 + i]);
+    }
     float m[REP], l[REP], acc[REP][8];  // the sums are only live in the value pass: registers for the key pass
 #pragma unroll
     for (int r = 0; r < REP; ++r) m[r] = -INFINITY;
@@ -379,48 +403,57 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
     const int n = hi - lo;  // at most kRotChunk: the launcher picks the split count for that
 
     if (n > 0) {
-        load_tables(ktab);
+        if constexpr (ROTARY) load_tables(ktab);
+        else build_score_table();
         __syncthreads();
         // ---- pass K: scores of the chunk ------------------------------------------------------------
         int code_next[2];
-        uint4 cos_next, sin_next;  // eight cosines and eight sines of this lane's frequencies
+        uint4 cos_next = make_uint4(0u, 0u, 0u, 0u), sin_next = cos_next;  // eight cosines and sines of this lane's frequencies
         {
             const int t = chunk + min(2 * warp + sub, n - 1);
             fetch_codes(kcodes + (code_row + t) * slots, code_next);
-            cos_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + f0));
-            sin_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + D / 2 + f0));
+            if constexpr (ROTARY) {
+                cos_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + f0));
+                sin_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + D / 2 + f0));
+            }
         }
         for (int base = 0; base < n; base += 2 * kWarps) {
             const int local = base + 2 * warp + sub;  // lanes past the end redo the last token and drop it
             const int code_now[2] = {code_next[0], code_next[1]};
-#if TACVQ_ROT_PREFETCH_ROPE
             const uint4 cos_now = cos_next, sin_now = sin_next;
-#else
-            const int t_now = chunk + min(local, n - 1);
-            const uint4 cos_now = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t_now * D + f0));
-            const uint4 sin_now = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t_now * D + D / 2 + f0));
-#endif
             if (base + 2 * kWarps < n) {
                 const int t = chunk + min(local + 2 * kWarps, n - 1);
                 fetch_codes(kcodes + (code_row + t) * slots, code_next);
-#if TACVQ_ROT_PREFETCH_ROPE
-                cos_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + f0));
-                sin_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + D / 2 + f0));
-#endif
+                if constexpr (ROTARY) {
+                    cos_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + f0));
+                    sin_next = __ldg(reinterpret_cast<const uint4 *>(rope + (int64_t)t * D + D / 2 + f0));
+                }
             }
-            __half2 krow[4];
-            rebuild8(code_now, krow);
-            const __half2 *cosv = reinterpret_cast<const __half2 *>(&cos_now), *sinv = reinterpret_cast<const __half2 *>(&sin_now);
             float sc[REP];
+            if constexpr (ROTARY) {
+                __half2 krow[4];
+                rebuild8(code_now, krow);
+                const __half2 *cosv = reinterpret_cast<const __half2 *>(&cos_now), *sinv = reinterpret_cast<const __half2 *>(&sin_now);
 #pragma unroll
-            for (int r = 0; r < REP; ++r) sc[r] = 0.0f;
+                for (int r = 0; r < REP; ++r) sc[r] = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const __half2 other = __shfl_xor_sync(0xffffffffu, krow[i], 8);
-                const __half2 turned = upper ? other : __hneg2(other);
-                const float2 kf = __half22float2(__hadd2(__hmul2(krow[i], cosv[i]), __hmul2(turned, sinv[i])));
+                for (int i = 0; i < 4; ++i) {
+                    const __half2 other = __shfl_xor_sync(0xffffffffu, krow[i], 8);
+                    const __half2 turned = upper ? other : __hneg2(other);
+                    const float2 kf = __half22float2(__hadd2(__hmul2(krow[i], cosv[i]), __hmul2(turned, sinv[i])));
 #pragma unroll
-                for (int r = 0; r < REP; ++r) sc[r] = fmaf(qv[r][2 * i + 1], kf.y, fmaf(qv[r][2 * i], kf.x, sc[r]));
+                    for (int r = 0; r < REP; ++r) sc[r] = fmaf(qv[r][2 * i + 1], kf.y, fmaf(qv[r][2 * i], kf.x, sc[r]));
+                }
+            } else {
+                const float4 *lut = reinterpret_cast<const float4 *>(tab);
+                float4 e = lut[code_now[0] * 16 + l16];
+                if (S > 1) {
+                    const float4 e1 = lut[(K + code_now[1]) * 16 + l16];
+                    e = make_float4(e.x + e1.x, e.y + e1.y, e.z + e1.z, e.w + e1.w);
+                }
+                const float ev[4] = {e.x, e.y, e.z, e.w};
+#pragma unroll
+                for (int r = 0; r < REP; ++r) sc[r] = ev[r];
             }
             // sum over the token's 16 lanes; with 4 or 2 heads the lanes first trade heads, so that fewer
             // values travel: head (bit 3, bit 2) of the lane index ends up in the lanes with those bits
@@ -554,7 +587,7 @@ static int launch_rotary_staged(const __half *q, const uint8_t *kcodes, const ui
     const size_t merge = ((size_t)(kRotBigThreads / 16) * REP + (size_t)(kRotBigThreads / 16) * REP * 128) * sizeof(float);
     size_t smem = tables + ((size_t)kRotChunk * REP + (size_t)(kRotBigThreads / 32) * REP) * sizeof(float);
     if (smem < merge) smem = merge;
-    auto kernel = attn_rotary_staged_kernel<REP>;
+    auto kernel = rope != nullptr ? attn_rotary_staged_kernel<REP, true> : attn_rotary_staged_kernel<REP, false>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((unsigned)splits, (unsigned)Hkv, (unsigned)B);

@@ -103,6 +103,34 @@ def test_other_geometries(device, b, hq, hkv, t, groups, stages, sub):
     _check(out, want)
 
 
+@pytest.mark.parametrize(
+    "b,hq,hkv,t,groups,stages,sub",
+    [
+        (8, 32, 8, 5000, 16, 1, 8),   # one-stage grouped CQ at the benchmark's head layout
+        (2, 8, 2, 9000, 16, 1, 8),    # more than one block's worth of tokens per row
+        (2, 8, 4, 1200, 8, 2, 16),    # 16-wide groups, two stages, 2 query heads per KV head
+        (1, 4, 4, 800, 2, 2, 64),     # two 64-wide groups, no head sharing
+        (3, 12, 3, 257, 4, 1, 32),    # odd batch, 32-wide groups
+    ],
+)
+def test_two_pass_kernel_for_head_dim_128_geometries(device, b, hq, hkv, t, groups, stages, sub):
+    """head_dim 128, groups at least 8 wide, at most two stages, at most 4 query heads per KV head, other than
+    the two specialised layouts: score table and value tables in shared memory, two passes."""
+    work = _workload(31 + t, b, hq, hkv, t, groups, stages, sub, [0.2] * stages if sub >= 32 else None)
+    start = [(7 * i) % 50 for i in range(b)]
+    end = [t - (11 * i) % 40 for i in range(b)]
+    if b > 2:
+        end[1] = start[1]  # an empty row
+    out, state = _run(device, work, start, end, want_state=True)
+    want, want_state = C.attention(*work, start, end)
+    _check(out, want)
+    live = [i for i in range(b) if end[i] > start[i]]
+    _check_state(state.cpu()[live], want_state[live])
+    if len(live) < b:
+        dead = [i for i in range(b) if i not in live]
+        assert bool((out.cpu()[dead] == 0).all()) and bool((state.cpu()[dead][..., 1:] == 0).all())
+
+
 def test_partial_states_merge_to_the_whole(device):
     """Sequence split as ranks would do it: per-range states, then the log-sum-exp merge."""
     ops = _ops()
