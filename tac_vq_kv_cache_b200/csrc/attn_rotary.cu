@@ -309,7 +309,10 @@ constexpr int kRotChunk = 4096;
 // ROTARY = false: the same two passes without the rotary step.  The key pass then needs no key rows at
 // all: the block first fills the table area with scores, lut[stage][code][piece] = q_r . (8 channels of the
 // word), r < REP, and a token's score is the sum of its S x 16 entries.
-template <int REP, bool ROTARY>
+// NARROW = true: one stage of 32 groups of 4 channels.  A lane's eight channels are then two whole words of
+// neighbouring groups; tables and score table are stored [code][group] (8-byte words, 16-byte scores) and the
+// lane's two codes take the place of the two stage codes.
+template <int REP, bool ROTARY, bool NARROW>
 __global__ void __launch_bounds__(kRotBigThreads, 1)
 attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ kcodes, const uint8_t *__restrict__ vcodes,
                           const __half *__restrict__ ktab, const __half *__restrict__ vtab, const __half *__restrict__ rope,
@@ -318,7 +321,8 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
     constexpr int D = 128, K = 256, kWarps = kRotBigThreads / 32;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint4 *tab = reinterpret_cast<uint4 *>(smem_raw);                                   // [S][256][16]
-    float *score = reinterpret_cast<float *>(smem_raw + (size_t)S * K * 16 * 16);        // [kRotChunk][REP]
+    const size_t table_bytes = NARROW ? (ROTARY ? (size_t)K * 32 * 8 : (size_t)K * 32 * 16) : (size_t)S * K * 16 * 16;
+    float *score = reinterpret_cast<float *>(smem_raw + table_bytes);                   // [kRotChunk][REP]
     float *red = score + (size_t)kRotChunk * REP;                                       // [kWarps][REP], later merge scratch
 
     const int slots = S * G;
@@ -339,6 +343,14 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
     const int hi = min(lo + per, lo_all + n_all);
 
     auto load_tables = [&](const __half *src) {
+        if constexpr (NARROW) {
+            uint2 *tab8 = reinterpret_cast<uint2 *>(tab);  // [256][32 groups] words of 4 channels
+            for (int idx = tid; idx < K * 32; idx += kRotBigThreads) {
+                const int g = idx & 31, code = idx >> 5;
+                tab8[idx] = __ldg(reinterpret_cast<const uint2 *>(src + (((int64_t)h * G + g) * K + code) * 4));
+            }
+            return;
+        }
         for (int idx = tid; idx < S * K * 16; idx += kRotBigThreads) {
             const int p = idx & 15, code = (idx >> 4) & 255, s = idx >> 12;
             const int g = (8 * p) / d, off = (8 * p) % d;
@@ -351,6 +363,23 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
             q_s[i] = __half2float(q[((int64_t)b * Hq + h * REP + i / D) * D + i % D]);
         __syncthreads();
         float4 *lut = reinterpret_cast<float4 *>(tab);
+        if constexpr (NARROW) {
+            for (int idx = tid; idx < K * 32; idx += kRotBigThreads) {
+                const int g = idx & 31, code = idx >> 5;
+                const uint2 w = __ldg(reinterpret_cast<const uint2 *>(ktab + (((int64_t)h * G + g) * K + code) * 4));
+                const __half2 *hp = reinterpret_cast<const __half2 *>(&w);
+                float dot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const float2 f = __half22float2(hp[i]);
+#pragma unroll
+                    for (int r = 0; r < REP; ++r)
+                        dot[r] = fmaf(q_s[r * D + 4 * g + 2 * i + 1], f.y, fmaf(q_s[r * D + 4 * g + 2 * i], f.x, dot[r]));
+                }
+                lut[idx] = make_float4(dot[0], dot[1], dot[2], dot[3]);
+            }
+            return;
+        }
         for (int idx = tid; idx < S * K * 16; idx += kRotBigThreads) {
             const int p = idx & 15, code = (idx >> 4) & 255, s = idx >> 12;
             const int g = (8 * p) / d, off = (8 * p) % d;
@@ -372,10 +401,24 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
     // fp16 is what a packed fp16 add returns.
     // (the codes of a token are fetched one trip ahead: S <= 2 bytes per lane and side)
     auto fetch_codes = [&](const uint8_t *code_row, int (&code)[2]) {
-        code[0] = code_row[group];
-        code[1] = S > 1 ? code_row[G + group] : 0;
+        if constexpr (NARROW) {
+            code[0] = code_row[2 * l16];
+            code[1] = code_row[2 * l16 + 1];
+        } else {
+            code[0] = code_row[group];
+            code[1] = S > 1 ? code_row[G + group] : 0;
+        }
     };
     auto rebuild8 = [&](const int (&code)[2], __half2 (&row)[4]) {
+        if constexpr (NARROW) {
+            const uint2 *tab8 = reinterpret_cast<const uint2 *>(tab);
+            const uint2 low = tab8[code[0] * 32 + 2 * l16], high = tab8[code[1] * 32 + 2 * l16 + 1];
+            row[0] = *reinterpret_cast<const __half2 *>(&low.x);
+            row[1] = *reinterpret_cast<const __half2 *>(&low.y);
+            row[2] = *reinterpret_cast<const __half2 *>(&high.x);
+            row[3] = *reinterpret_cast<const __half2 *>(&high.y);
+            return;
+        }
         const uint4 first = tab[code[0] * 16 + l16];
         const __half2 *h0 = reinterpret_cast<const __half2 *>(&first);
 #pragma unroll
@@ -446,10 +489,17 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
                 }
             } else {
                 const float4 *lut = reinterpret_cast<const float4 *>(tab);
-                float4 e = lut[code_now[0] * 16 + l16];
-                if (S > 1) {
-                    const float4 e1 = lut[(K + code_now[1]) * 16 + l16];
+                float4 e;
+                if constexpr (NARROW) {
+                    e = lut[code_now[0] * 32 + 2 * l16];
+                    const float4 e1 = lut[code_now[1] * 32 + 2 * l16 + 1];
                     e = make_float4(e.x + e1.x, e.y + e1.y, e.z + e1.z, e.w + e1.w);
+                } else {
+                    e = lut[code_now[0] * 16 + l16];
+                    if (S > 1) {
+                        const float4 e1 = lut[(K + code_now[1]) * 16 + l16];
+                        e = make_float4(e.x + e1.x, e.y + e1.y, e.z + e1.z, e.w + e1.w);
+                    }
                 }
                 const float ev[4] = {e.x, e.y, e.z, e.w};
 #pragma unroll
@@ -575,7 +625,9 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
 
 bool attn_rotary_staged_supported(int Hq, int Hkv, int D, int G, int S, int K) {
     const int rep = Hq / Hkv;
-    return D == 128 && K == 256 && S <= 2 && (D / G) >= 8 && (rep == 1 || rep == 2 || rep == 4);
+    const bool pieces = (D / G) >= 8 && S <= 2;   // a lane's eight channels lie inside one word
+    const bool narrow = (D / G) == 4 && S == 1;   // ... or are two whole words
+    return D == 128 && K == 256 && (pieces || narrow) && (rep == 1 || rep == 2 || rep == 4);
 }
 
 template <int REP>
@@ -583,11 +635,13 @@ static int launch_rotary_staged(const __half *q, const uint8_t *kcodes, const ui
                                 const __half *vtab, const __half *rope, const int32_t *seq_start, const int32_t *seq_end,
                                 float *part, int B, int Hq, int Hkv, int G, int S, int64_t T_cap, int splits,
                                 cudaStream_t stream) {
-    const size_t tables = (size_t)S * 256 * 16 * 16;
+    const bool narrow = G == 32;
+    const size_t tables = narrow ? (rope != nullptr ? (size_t)256 * 32 * 8 : (size_t)256 * 32 * 16) : (size_t)S * 256 * 16 * 16;
     const size_t merge = ((size_t)(kRotBigThreads / 16) * REP + (size_t)(kRotBigThreads / 16) * REP * 128) * sizeof(float);
     size_t smem = tables + ((size_t)kRotChunk * REP + (size_t)(kRotBigThreads / 32) * REP) * sizeof(float);
     if (smem < merge) smem = merge;
-    auto kernel = rope != nullptr ? attn_rotary_staged_kernel<REP, true> : attn_rotary_staged_kernel<REP, false>;
+    auto kernel = narrow ? (rope != nullptr ? attn_rotary_staged_kernel<REP, true, true> : attn_rotary_staged_kernel<REP, false, true>)
+                         : (rope != nullptr ? attn_rotary_staged_kernel<REP, true, false> : attn_rotary_staged_kernel<REP, false, false>);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((unsigned)splits, (unsigned)Hkv, (unsigned)B);

@@ -111,6 +111,8 @@ def test_other_geometries(device, b, hq, hkv, t, groups, stages, sub):
         (2, 8, 4, 1200, 8, 2, 16),    # 16-wide groups, two stages, 2 query heads per KV head
         (1, 4, 4, 800, 2, 2, 64),     # two 64-wide groups, no head sharing
         (3, 12, 3, 257, 4, 1, 32),    # odd batch, 32-wide groups
+        (2, 16, 4, 6000, 32, 1, 4),   # 32 groups of 4 (a lane's eight channels are two whole words)
+        (1, 2, 2, 300, 32, 1, 4),     # ... without head sharing
     ],
 )
 def test_two_pass_kernel_for_head_dim_128_geometries(device, b, hq, hkv, t, groups, stages, sub):

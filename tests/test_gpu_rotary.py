@@ -66,6 +66,8 @@ def test_rotary_attention_matches_the_reference_golden(golden, device, case):
         (1, 8, 8, 1500, 1, 2, 128, 10000.0),     # two full-width codebooks, no head sharing
         (2, 16, 2, 700, 32, 1, 4, 1000000.0),    # 8 query heads per KV head
         (1, 4, 2, 900, 8, 3, 8, 10000.0),        # head_dim 64
+        (2, 8, 2, 5000, 32, 1, 4, 1000000.0),    # 32 groups of 4 in the two-pass kernel
+        (2, 8, 4, 4500, 16, 1, 8, 10000.0),      # one-stage grouped CQ in the two-pass kernel
     ],
 )
 def test_rotary_attention_matches_the_oracle(device, b, hq, hkv, t, groups, stages, sub, theta):
