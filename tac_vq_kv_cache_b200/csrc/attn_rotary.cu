@@ -380,9 +380,17 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
             }
             return;
         }
+        // the block size is a multiple of 16, so a thread meets the same piece p on every trip: its query
+        // channels are read once
+        const int p = tid & 15;
+        const int g = (8 * p) / d, off = (8 * p) % d;
+        float qp[REP][8];
+#pragma unroll
+        for (int r = 0; r < REP; ++r)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qp[r][i] = q_s[r * D + 8 * p + i];
         for (int idx = tid; idx < S * K * 16; idx += kRotBigThreads) {
-            const int p = idx & 15, code = (idx >> 4) & 255, s = idx >> 12;
-            const int g = (8 * p) / d, off = (8 * p) % d;
+            const int code = (idx >> 4) & 255, s = idx >> 12;
             const uint4 w = __ldg(reinterpret_cast<const uint4 *>(ktab + ((((int64_t)h * S + s) * G + g) * K + code) * d + off));
             const __half2 *hp = reinterpret_cast<const __half2 *>(&w);
             float dot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -390,8 +398,7 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
             for (int i = 0; i < 4; ++i) {
                 const float2 f = __half22float2(hp[i]);
 #pragma unroll
-                for (int r = 0; r < REP; ++r)
-                    dot[r] = fmaf(q_s[r * D + 8 * p + 2 * i + 1], f.y, fmaf(q_s[r * D + 8 * p + 2 * i], f.x, dot[r]));
+                for (int r = 0; r < REP; ++r) dot[r] = fmaf(qp[r][2 * i + 1], f.y, fmaf(qp[r][2 * i], f.x, dot[r]));
             }
             lut[idx] = make_float4(dot[0], dot[1], dot[2], dot[3]);
         }
