@@ -146,6 +146,13 @@ def run_ours(args) -> dict:
             ops.encode(rows, ktab, codes=codes)
         torch.cuda.synchronize(device)
         return {"encode_only": True, "rows": 2 * 8192, "steps": args.steps}
+    if args.decode_only:  # profiler case: rebuild fp16 rows from the 2-stage codes of one layer (batch 8 x 8192 tokens)
+        pgen = torch.Generator(device=device).manual_seed(8601)
+        codes = torch.randint(0, 256, (BATCH, KV_HEADS, 8192, STAGES, GROUPS), dtype=torch.uint8, device=device, generator=pgen)
+        for _ in range(args.warmup + args.steps):
+            ops.decode(codes, ktab, torch.float16)
+        torch.cuda.synchronize(device)
+        return {"decode_only": True, "tokens": 8192, "steps": args.steps}
     if args.encode_wide_only:  # profiler case: two full-width codebooks (1 group x 2 stages x 128), reduced batch
         rows = torch.randn(2, KV_HEADS, 8192, DIM, generator=gen).half().to(device)
         wide = (torch.randn(KV_HEADS, 2, 1, 256, DIM, generator=gen) * 0.1).half().to(device)
@@ -211,6 +218,7 @@ def run_ours(args) -> dict:
     encode = None
     rotary = None
     window = None
+    reconstruct = None
     cpu = None
     extras = not args.kernel_only
     if extras and (rank == 0 or world > 1):
@@ -334,6 +342,19 @@ def run_ours(args) -> dict:
         end.record()
         torch.cuda.synchronize(device)
         win_ms = start.elapsed_time(end) / rot_steps
+        # reconstruction of the whole 32768-token window as fp16 rows (what the reference keeps per layer): output-bound
+        for i in range(3):
+            ops.decode(code_sets[i % CODE_SETS][0], ktab, torch.float16)
+        torch.cuda.synchronize(device)
+        start.record()
+        for i in range(rot_steps):
+            ops.decode(code_sets[i % CODE_SETS][0], ktab, torch.float16)
+        end.record()
+        torch.cuda.synchronize(device)
+        rec_ms = start.elapsed_time(end) / rot_steps
+        rec_bytes = BATCH * KV_HEADS * CONTEXT * (DIM * 2 + STAGES * GROUPS)
+        reconstruct = {"value": round(BATCH * KV_HEADS * CONTEXT / (rec_ms * 1e-3), 1), "unit": "rows/s (fp16 [8,8,32768,128] rebuilt from 2 x 16 code bytes per row)",
+                       "ms": round(rec_ms, 4), "achieved_gbs": round(rec_bytes / (rec_ms * 1e-3) / 1e9, 1), "frac_of_hbm_peak": round(rec_bytes / (rec_ms * 1e-3) / 1e9 / peak, 4)}
         window = {"value": round(BATCH / (win_ms * 1e-3), 1), "unit": "decode tokens/s (per layer; batch 8, sliding window of 4096 over a 32768-token code cache)",
                   "ms_per_step": round(win_ms, 4)}
         rotary = {"value": round(BATCH / (rot_ms * 1e-3), 1), "unit": UNIT + "; keys stored pre-rotary, rotated inside the kernel",
@@ -355,7 +376,7 @@ def run_ours(args) -> dict:
             "l2": f"{CODE_SETS} code sets rotated between steps ({CODE_SETS * 2 * BATCH * KV_HEADS * CONTEXT * 32 // 2**20} MiB > 126 MB L2)",
         },
         "kv_tokens_scanned_per_s": round(BATCH * CONTEXT * world / (ms_per_step * 1e-3), 1),
-        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "encode": encode, "rotary": rotary, "window4096": window,
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "encode": encode, "rotary": rotary, "window4096": window, "reconstruct": reconstruct,
         "gpu_launches": 3 * args.steps, "clocks": clocks.summary(),
     }
     if world > 1:
@@ -549,6 +570,7 @@ def main() -> None:
     parser.add_argument("--workload", choices=("decode32k", "seqsplit131k"), default="decode32k",
                         help="decode32k: the headline configuration; seqsplit131k: one sequence split across the ranks (extra)")
     parser.add_argument("--encode-only", action="store_true", help="run only the layer encode (used for profiler captures)")
+    parser.add_argument("--decode-only", action="store_true", help="run only the reconstruction of rows from codes (profiler captures)")
     parser.add_argument("--encode-wide-only", action="store_true", help="run only a full-width (d = 128) encode (profiler captures)")
     parser.add_argument("--rotary-only", action="store_true", help="run only rotary attention at 8192 tokens (profiler captures)")
     parser.add_argument("--kernel-only", action="store_true", help="time the decode-attention launches only (used for profiler captures)")

@@ -141,18 +141,61 @@ decode_staged_kernel(const uint8_t *__restrict__ codes, const __half *__restrict
     const int per_block = (rows + gridDim.x - 1) / gridDim.x;
     const int r_begin = blockIdx.x * per_block, r_end = min(rows, r_begin + per_block);
     const __half *tab_g = tab + (size_t)g * K * d + i0;   // + (s*G*K + code) * d
-    const size_t stage_stride = (size_t)G * K * d;
+    const int stage_stride = G * K * d;                   // halves; a head's tables are at most 160 KB
+    const int slots = S * G;
     int row = r_begin + row_lane;
     int b = row / T, t = row - b * T;
+    // byte offset of this thread's first code and element offset of its output chunk; both advance by a
+    // constant per pass and are recomputed only when the walk enters the next batch row
+    auto code_offset = [&](int bb, int tt) { return (((size_t)bb * H + h) * T_cap + t0 + tt) * slots + g; };
+    auto out_offset = [&](int bb, int tt) { return (((size_t)bb * H + h) * T + tt) * (size_t)D + c0; };
+    size_t code_at = code_offset(b, t), out_at = out_offset(b, t);
+    // codes of the first row (at most two stages are fetched ahead; deeper stacks read the rest in the loop)
+    int ahead0 = 0, ahead1 = 0;
+    if (row < r_end) {
+        ahead0 = codes[code_at];
+        if (S_use > 1) ahead1 = codes[code_at + G];
+    }
     for (; row < r_end; row += rows_per_pass) {
-        const size_t rid = ((size_t)b * H + h);
-        const uint8_t *cd = codes + ((rid * T_cap + t0 + t) * S) * G + g;
+        const int c_first = ahead0, c_second = ahead1;
+        const size_t code_now = code_at, out_now = out_at;
+        t += rows_per_pass;
+        if (t >= T) {
+            while (t >= T) {
+                t -= T;
+                ++b;
+            }
+            code_at = code_offset(b, t);
+            out_at = out_offset(b, t);
+        } else {
+            code_at += (size_t)rows_per_pass * slots;
+            out_at += (size_t)rows_per_pass * D;
+        }
+        if (row + rows_per_pass < r_end) {  // the next row's codes travel while this row is rebuilt
+            ahead0 = codes[code_at];
+            if (S_use > 1) ahead1 = codes[code_at + G];
+        }
+        OT *dst = out + out_now;
+        if (S_use <= 2 && sizeof(OT) == 2) {
+            // one or two fp16 words: their fp32 sum is exact, so its single rounding to fp16 is a packed fp16 add
+            uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+            if (S_use >= 1) packed = *reinterpret_cast<const uint4 *>(tab_g + c_first * d);
+            if (S_use == 2) {
+                const uint4 second = *reinterpret_cast<const uint4 *>(tab_g + stage_stride + c_second * d);
+                __half2 *pv = reinterpret_cast<__half2 *>(&packed);
+                const __half2 *sv = reinterpret_cast<const __half2 *>(&second);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) pv[i] = __hadd2(pv[i], sv[i]);
+            }
+            *reinterpret_cast<uint4 *>(dst) = packed;
+            continue;
+        }
         float sum[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
         for (int s = 0; s < S_use; ++s) {
-            const int c = cd[s * G];
-            const uint4 raw = *reinterpret_cast<const uint4 *>(tab_g + s * stage_stride + (size_t)c * d);
+            const int c = s == 0 ? c_first : (s == 1 ? c_second : (int)codes[code_now + (size_t)s * G]);
+            const uint4 raw = *reinterpret_cast<const uint4 *>(tab_g + s * stage_stride + c * d);
             const __half2 *hv = reinterpret_cast<const __half2 *>(&raw);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -161,7 +204,6 @@ decode_staged_kernel(const uint8_t *__restrict__ codes, const __half *__restrict
                 sum[2 * i + 1] = __fadd_rn(sum[2 * i + 1], f.y);
             }
         }
-        OT *dst = out + (rid * T + t) * (size_t)D + c0;
         if constexpr (sizeof(OT) == 2) {
             uint4 packed;
             __half2 *pv = reinterpret_cast<__half2 *>(&packed);
@@ -171,11 +213,6 @@ decode_staged_kernel(const uint8_t *__restrict__ codes, const __half *__restrict
         } else {
             *reinterpret_cast<float4 *>(dst) = make_float4(sum[0], sum[1], sum[2], sum[3]);
             *reinterpret_cast<float4 *>(dst + 4) = make_float4(sum[4], sum[5], sum[6], sum[7]);
-        }
-        t += rows_per_pass;
-        while (t >= T) {
-            t -= T;
-            ++b;
         }
     }
     if (threadIdx.x == 0 && !ready_s) {
