@@ -151,10 +151,14 @@ decode_staged_kernel(const uint8_t *__restrict__ codes, const __half *__restrict
     auto out_offset = [&](int bb, int tt) { return (((size_t)bb * H + h) * T + tt) * (size_t)D + c0; };
     size_t code_at = code_offset(b, t), out_at = out_offset(b, t);
     // codes of the first row (at most two stages are fetched ahead; deeper stacks read the rest in the loop)
+    // (groups of 4 channels: the chunk is two whole words of neighbouring groups, and the two codes fetched
+    // ahead are those of the first stage)
+    const bool narrow = d == 4;
     int ahead0 = 0, ahead1 = 0;
     if (row < r_end) {
         ahead0 = codes[code_at];
-        if (S_use > 1) ahead1 = codes[code_at + G];
+        if (narrow) ahead1 = codes[code_at + 1];
+        else if (S_use > 1) ahead1 = codes[code_at + G];
     }
     for (; row < r_end; row += rows_per_pass) {
         const int c_first = ahead0, c_second = ahead1;
@@ -173,9 +177,40 @@ decode_staged_kernel(const uint8_t *__restrict__ codes, const __half *__restrict
         }
         if (row + rows_per_pass < r_end) {  // the next row's codes travel while this row is rebuilt
             ahead0 = codes[code_at];
-            if (S_use > 1) ahead1 = codes[code_at + G];
+            if (narrow) ahead1 = codes[code_at + 1];
+            else if (S_use > 1) ahead1 = codes[code_at + G];
         }
         OT *dst = out + out_now;
+        if (narrow) {
+            float sum[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
+            for (int s = 0; s < S_use; ++s) {
+                const int ca = s == 0 ? c_first : (int)codes[code_now + (size_t)s * G];
+                const int cb = s == 0 ? c_second : (int)codes[code_now + (size_t)s * G + 1];
+                const uint2 wa = *reinterpret_cast<const uint2 *>(tab_g + s * stage_stride + ca * 4);
+                const uint2 wb = *reinterpret_cast<const uint2 *>(tab_g + s * stage_stride + K * 4 + cb * 4);
+                const __half2 hv[4] = {*reinterpret_cast<const __half2 *>(&wa.x), *reinterpret_cast<const __half2 *>(&wa.y),
+                                       *reinterpret_cast<const __half2 *>(&wb.x), *reinterpret_cast<const __half2 *>(&wb.y)};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(hv[i]);
+                    sum[2 * i] = __fadd_rn(sum[2 * i], f.x);
+                    sum[2 * i + 1] = __fadd_rn(sum[2 * i + 1], f.y);
+                }
+            }
+            if constexpr (sizeof(OT) == 2) {
+                uint4 packed;
+                __half2 *pv = reinterpret_cast<__half2 *>(&packed);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) pv[i] = __floats2half2_rn(sum[2 * i], sum[2 * i + 1]);
+                *reinterpret_cast<uint4 *>(dst) = packed;
+            } else {
+                *reinterpret_cast<float4 *>(dst) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+                *reinterpret_cast<float4 *>(dst + 4) = make_float4(sum[4], sum[5], sum[6], sum[7]);
+            }
+            continue;
+        }
         if (S_use <= 2 && sizeof(OT) == 2) {
             // one or two fp16 words: their fp32 sum is exact, so its single rounding to fp16 is a packed fp16 add
             uint4 packed = make_uint4(0u, 0u, 0u, 0u);
@@ -259,7 +294,7 @@ int decode_dispatch(const uint8_t *codes, const __half *tables, void *out, int o
                     int G, int S, int S_use, int K, int64_t t0, int64_t T_cap, cudaStream_t stream) {
     const int d = D / G;
     const size_t head_bytes = (size_t)S * G * K * d * 2;
-    const bool staged = d % 8 == 0 && kStagedThreads % (D / 8) == 0 && (int64_t)B * T < 0x7fffffff &&
+    const bool staged = (d % 8 == 0 || d == 4) && D % 8 == 0 && kStagedThreads % (D / 8) == 0 && (int64_t)B * T < 0x7fffffff &&
                         head_bytes <= (size_t)kStagedMaxBytes && head_bytes % 16 == 0 &&
                         ((uintptr_t)tables & 15) == 0 && ((uintptr_t)out & 15) == 0 && (int64_t)B * T >= 1024;
     if (staged) {

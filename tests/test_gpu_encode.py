@@ -331,7 +331,7 @@ def test_argument_errors_are_reported_before_any_launch(device):
         hard_grouped_cq(x.cpu(), torch.zeros(1, 16, 256, 8))
 
 
-@pytest.mark.parametrize("groups,stages,sub,dtype", [(16, 2, 8, torch.float16), (1, 2, 128, torch.float32), (16, 1, 8, torch.float16), (1, 16, 128, torch.float16)])
+@pytest.mark.parametrize("groups,stages,sub,dtype", [(16, 2, 8, torch.float16), (1, 2, 128, torch.float32), (16, 1, 8, torch.float16), (1, 16, 128, torch.float16), (32, 1, 4, torch.float16), (32, 2, 4, torch.float32), (8, 3, 16, torch.float16)])
 def test_decode_of_long_rows_matches_the_oracle(device, groups, stages, sub, dtype):
     """Row counts large enough for the kernel that stages a head's tables in shared memory (when they fit)."""
     ops = _ops()
