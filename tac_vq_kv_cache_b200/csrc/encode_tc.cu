@@ -164,33 +164,43 @@ encode_tc8_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sx
     const uint32_t stride = gridDim.x * kTcRows;
     const float inf = __int_as_float(0x7f800000);
 
-    // rows of this lane's quad in the current tile: `a` = gid, `b` = gid + 8; elements 2q, 2q+1
-    auto fetch = [&](uint32_t row, float (&r)[2]) {
+    // rows of this lane's quad in the current tile: `a` = gid, `b` = gid + 8; elements 2q, 2q+1.
+    // (batch row, token) of a row is divided out once and then advanced by the tile stride.
+    auto fetch = [&](bool live, uint32_t b, uint32_t t, float (&r)[2]) {
         r[0] = r[1] = 0.0f;
-        if (row < rows && 2 * q < DSUB) {
-            const uint32_t b = row / (uint32_t)T, t = row % (uint32_t)T;
+        if (live && 2 * q < DSUB) {
             const XT *src = x + (int64_t)b * sxb + (int64_t)h * sxh + (int64_t)t * sxt + g * DSUB + 2 * q;
             r[0] = to_float<XT>(src[0]);
             r[1] = to_float<XT>(src[1]);
         }
     };
+    const uint32_t step_b = stride / (uint32_t)T, step_t = stride % (uint32_t)T;
+    auto advance = [&](uint32_t &b, uint32_t &t) {
+        b += step_b;
+        t += step_t;
+        if (t >= (uint32_t)T) {
+            t -= (uint32_t)T;
+            ++b;
+        }
+    };
     uint32_t tile = blockIdx.x * kTcRows;
+    uint32_t ba = (tile + warp * 16 + gid) / (uint32_t)T, ta = (tile + warp * 16 + gid) % (uint32_t)T;
+    uint32_t bb = (tile + warp * 16 + gid + 8) / (uint32_t)T, tb = (tile + warp * 16 + gid + 8) % (uint32_t)T;
     float ra[2], rb[2];
-    if (tile < rows) {
-        fetch(tile + warp * 16 + gid, ra);
-        fetch(tile + warp * 16 + gid + 8, rb);
-    }
+    fetch(tile + warp * 16 + gid < rows, ba, ta, ra);
+    fetch(tile + warp * 16 + gid + 8 < rows, bb, tb, rb);
     for (; tile < rows; tile += stride) {
         const uint32_t row_a = tile + warp * 16 + gid, row_b = row_a + 8;
         // next tile's elements travel while this one is searched
+        uint32_t nba = ba, nta = ta, nbb = bb, ntb = tb;
+        advance(nba, nta);
+        advance(nbb, ntb);
         float na[2] = {0.0f, 0.0f}, nb[2] = {0.0f, 0.0f};
         if (tile + stride < rows && tile + stride > tile) {
-            fetch(row_a + stride, na);
-            fetch(row_b + stride, nb);
+            fetch(row_a + stride < rows, nba, nta, na);
+            fetch(row_b + stride < rows, nbb, ntb, nb);
         }
         const bool live_a = row_a < rows, live_b = row_b < rows;
-        const uint32_t ba = row_a / (uint32_t)T, ta = row_a % (uint32_t)T;
-        const uint32_t bb = row_b / (uint32_t)T, tb = row_b % (uint32_t)T;
         uint8_t *code_a = codes + (((int64_t)ba * H + h) * T_cap + t0 + ta) * ((int64_t)S * G) + g;
         uint8_t *code_b = codes + (((int64_t)bb * H + h) * T_cap + t0 + tb) * ((int64_t)S * G) + g;
         float da[2] = {0.0f, 0.0f}, db[2] = {0.0f, 0.0f};
@@ -341,6 +351,7 @@ encode_tc8_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sx
             }
         }
         ra[0] = na[0], ra[1] = na[1], rb[0] = nb[0], rb[1] = nb[1];
+        ba = nba, ta = nta, bb = nbb, tb = ntb;
     }
 }
 
