@@ -29,7 +29,7 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kDim = 128, kRep = 4, kWords = 256;
 constexpr int kMaxStages = 16;
 constexpr int kStageBytes = 16384;           // code bytes of one side staged in shared memory at a time
-constexpr int kSplitTokens = 8192;          // a block's range: 8192 weights of at most 2^18 fit 32 bits
+[[maybe_unused]] constexpr int kSplitTokens = 8192;          // a block's range: 8192 weights of at most 2^18 fit 32 bits
 constexpr float kWeightOne = 262144.0f;     // fixed-point one (2^18); the largest weight of a range is exactly 1
 
 __global__ void __launch_bounds__(kThreads)

@@ -49,7 +49,7 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kDim = 128, kGroups = 16, kStages = 2, kSub = 8, kRep = 4, kSlots = 32, kWords = 256;
 constexpr int kTile = 32;          // tokens per warp tile
 constexpr int kMaxBatch = 512;
-constexpr int kBulkPiece = 16384;     // bytes per bulk copy instruction
+[[maybe_unused]] constexpr int kBulkPiece = 16384;     // bytes per bulk copy instruction
 #ifndef TACVQ_FUSED_MERGE
 #define TACVQ_FUSED_MERGE 0  // 1: the last scan block of a pair merges it (no merge launch); measured slower
 #endif

@@ -331,7 +331,7 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int sub = lane >> 4, l16 = lane & 15;
     const int c0 = l16 * 8;
-    const int group = c0 / d, offset = c0 % d;
+    const int group = c0 / d;
     const int f0 = c0 % (D / 2);
     const bool upper = c0 >= D / 2;
 
@@ -349,12 +349,12 @@ attn_rotary_staged_kernel(const __half *__restrict__ q, const uint8_t *__restric
                 const int g = idx & 31, code = idx >> 5;
                 tab8[idx] = __ldg(reinterpret_cast<const uint2 *>(src + (((int64_t)h * G + g) * K + code) * 4));
             }
-            return;
-        }
-        for (int idx = tid; idx < S * K * 16; idx += kRotBigThreads) {
-            const int p = idx & 15, code = (idx >> 4) & 255, s = idx >> 12;
-            const int g = (8 * p) / d, off = (8 * p) % d;
-            tab[idx] = __ldg(reinterpret_cast<const uint4 *>(src + ((((int64_t)h * S + s) * G + g) * K + code) * d + off));
+        } else {
+            for (int idx = tid; idx < S * K * 16; idx += kRotBigThreads) {
+                const int p = idx & 15, code = (idx >> 4) & 255, s = idx >> 12;
+                const int g = (8 * p) / d, off = (8 * p) % d;
+                tab[idx] = __ldg(reinterpret_cast<const uint4 *>(src + ((((int64_t)h * S + s) * G + g) * K + code) * d + off));
+            }
         }
     };
     auto build_score_table = [&]() {  // ROTARY = false only; the query rows sit at the start of the score area
