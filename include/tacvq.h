@@ -72,6 +72,15 @@ TACVQ_API const char *tacvq_status_string(int status);
 TACVQ_API int tacvq_table_sqnorm(const uint16_t *tables_f16, float *out, int64_t words, int d, tacvq_stream_t stream);
 
 /*
+ * Diagnostic of the wide-group encode (d = 64, 128), whose approximate scores are tensor-core products
+ * (tcgen05) kept in tensor memory: *count = how many times, on the current device since the library was
+ * loaded, a block stopped waiting for those products and re-evaluated every pair of the stage instead
+ * (codes stay exact either way).  Synchronises the device.  Expected value: 0.  No counterpart in the
+ * reference.
+ */
+TACVQ_API int tacvq_encode_tensor_memory_timeouts(unsigned int *count);
+
+/*
  * Encode: greedy residual nearest-codeword search, all S stages fused, groups independent.
  * Replaces the forward of hard_residual_vq_exits (closed_loop_vq.py:235-410, G=1) and of
  * hard_grouped_cq (cq_tac.py:33-114, S=1), including _nearest_indices (closed_loop_vq.py:52-76).

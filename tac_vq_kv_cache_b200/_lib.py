@@ -19,6 +19,7 @@ _SIGNATURES = {
     "tacvq_version": (c_int, []),
     "tacvq_status_string": (c_char_p, [c_int]),
     "tacvq_table_sqnorm": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "tacvq_encode_tensor_memory_timeouts": (c_int, [c_void_p]),
     "tacvq_encode": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int]
                      + [c_int] * 7 + [c_int64, c_int64, c_void_p]),
     "tacvq_encode_whitened": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -11,6 +11,7 @@ int decode_dispatch(const uint8_t *codes, const __half *tables, void *out, int o
 int codeword_grad_dispatch(const uint8_t *codes, const float *grad_out, float *grad_tables, int B, int H, int T, int D,
                            int G, int S, int S_use, int K, int64_t t0, int64_t T_cap, cudaStream_t stream);
 int table_sqnorm_dispatch(const __half *tables, float *out, int64_t words, int d, cudaStream_t stream);
+int tensor_memory_timeouts(unsigned int *out);
 int whiten_dispatch(const void *x, int x_dtype, int64_t sxb, int64_t sxh, int64_t sxt, const __half *tables,
                     const float *whitener, float *search_tables, float *search_rows, int B, int H, int T, int D, int G,
                     int S, int K, cudaStream_t stream);
@@ -135,6 +136,11 @@ int tacvq_table_sqnorm(const uint16_t *tables_f16, float *out, int64_t words, in
     if (!tables_f16 || !out) return TACVQ_ERR_NULL;
     if (words < 0 || d <= 0 || d > 128) return TACVQ_ERR_GEOMETRY;
     return table_sqnorm_dispatch((const __half *)tables_f16, out, words, d, (cudaStream_t)stream);
+}
+
+int tacvq_encode_tensor_memory_timeouts(unsigned int *count) {
+    if (!count) return TACVQ_ERR_NULL;
+    return tensor_memory_timeouts(count);
 }
 
 int tacvq_encode(const void *x, int x_dtype, int64_t sxb, int64_t sxh, int64_t sxt, const uint16_t *tables_f16,

@@ -33,13 +33,17 @@ constexpr int kRows = 128;     // rows per block
 constexpr int kThreads = 512;  // 16 warps = 4 row blocks of 32 x 4 word quarters of 64
 constexpr int kListCap = 2048;
 
-template <int DSUB>
+// TM = true: the two fp16 operands are stored the way the 5th-generation tensor core reads them from
+// shared memory (K-major, 128-byte rows, 128-byte swizzle: within every 1024-byte group of 8 rows the
+// 16-byte piece p of row r sits at piece p ^ (r & 7); 64 elements per row, so d = 128 takes two such
+// panels).  Both operands then start on 1024-byte boundaries.
+template <int DSUB, bool TM>
 struct TcLargeLayout {
     static constexpr int kHalfStride = DSUB + 8;  // halves: 16-byte rows that land on distinct banks for ldmatrix
     static constexpr int kResStride = DSUB + 4;   // floats
     static constexpr size_t kTab = 0;                                              // [256][kHalfStride] half
-    static constexpr size_t kHi = kTab + (size_t)kMaxWords * kHalfStride * 2;      // [kRows][kHalfStride] half
-    static constexpr size_t kRes = kHi + (size_t)kRows * kHalfStride * 2;          // [kRows][kResStride] float
+    static constexpr size_t kHi = kTab + (size_t)kMaxWords * (TM ? DSUB : kHalfStride) * 2;      // [kRows][kHalfStride] half
+    static constexpr size_t kRes = kHi + (size_t)kRows * (TM ? DSUB : kHalfStride) * 2;          // [kRows][kResStride] float
     static constexpr size_t kNrm = kRes + (size_t)kRows * kResStride * 4;          // [256] float
     static constexpr size_t kSeed = kNrm + kMaxWords * 4;                          // [256] float: -|c|^2/2
     static constexpr size_t kXx = kSeed + kMaxWords * 4;                           // [kRows] float
@@ -47,10 +51,19 @@ struct TcLargeLayout {
     static constexpr size_t kThr = kRowMax + 4 * kRows * 4;                        // [kRows] float
     static constexpr size_t kBest = kThr + kRows * 4;                              // [kRows] u64
     static constexpr size_t kList = kBest + kRows * 8;                             // [kListCap] u16
-    static constexpr size_t kMisc = kList + kListCap * 2;                          // count, big flag, cc_max
-    static constexpr size_t kRowCnt = kMisc + 16;                                  // [kRows] int: listed words per row
+    static constexpr size_t kMisc = kList + kListCap * 2;                          // count, big flag, cc_max, tensor-memory slot; +16: mbarrier
+    static constexpr size_t kRowCnt = kMisc + 32;                                  // [kRows] int: listed words per row
     static constexpr size_t kHist = kRowCnt + kRows * 4;                           // [kRows][S] u8
-    static constexpr size_t bytes(int S) { return kHist + (size_t)kRows * S; }
+    static constexpr size_t bytes(int S) { return kHist + (size_t)kRows * S + (TM ? 1024 : 0); }  // TM: room to align the base
+    // half index of element e of word k / of row r
+    __device__ static __forceinline__ int tab_at(int k, int e) {
+        if constexpr (TM) return (e >> 6) * (kMaxWords * 64) + k * 64 + ((((e >> 3) & 7) ^ (k & 7)) << 3) + (e & 7);
+        else return k * kHalfStride + e;
+    }
+    __device__ static __forceinline__ int hi_at(int r, int e) {
+        if constexpr (TM) return (e >> 6) * (kRows * 64) + r * 64 + ((((e >> 3) & 7) ^ (r & 7)) << 3) + (e & 7);
+        else return r * kHalfStride + e;
+    }
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *smem_ptr) {
@@ -65,6 +78,33 @@ __device__ __forceinline__ void mma_acc_16816(float (&c)[4], const uint32_t (&a)
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+
+// 32 consecutive fp32 columns of this warp's 32 tensor-memory lanes (lane = thread)
+__device__ __forceinline__ void tmem_load32(uint32_t *v, uint32_t taddr) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// Shared-memory operand descriptor of tcgen05.mma for a K-major panel with 128-byte rows and the
+// 128-byte swizzle: start address / 16 in bits 0-13, leading offset (one 16-byte unit, not used by this
+// layout) in bits 16-29, 1024 bytes between groups of 8 rows in bits 32-45, descriptor version 1 in
+// bits 46-47, swizzle mode 2 (128 bytes) in bits 61-63.
+__device__ __forceinline__ uint64_t panel_descriptor(uint32_t smem_addr) {
+    const uint32_t lo = ((smem_addr & 0x3ffffu) >> 4) | (1u << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+// Instruction descriptor: fp32 accumulator (bits 4-5 = 1), fp16 A and B (bits 7-12 = 0), both K-major
+// (bits 15, 16 = 0), N / 8 in bits 17-22, M / 16 in bits 24-28.
+constexpr uint32_t kMmaShape = (1u << 4) | ((uint32_t)(kMaxWords >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
 
 // monotone map float -> uint32 (total order of the values, -0 below +0)
 __device__ __forceinline__ uint32_t ordered_bits(float v) {
@@ -122,16 +162,23 @@ __device__ __forceinline__ float4 load4<__half>(const __half *src, bool vec) {
 
 }  // namespace
 
-template <int DSUB, typename XT>
+// Times a block gave up waiting for its tensor-core products (the stage then re-evaluates every pair,
+// so the codes are still exact); read by tacvq_debug_tensor_memory_timeouts.  Expected to stay 0.
+__device__ unsigned int g_tensor_memory_timeouts = 0;
+
+template <int DSUB, typename XT, bool TM>
 __global__ void __launch_bounds__(kThreads, 1)
 encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const __half *__restrict__ tables,
                        const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
                        int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap, int vec_ok) {
-    using L = TcLargeLayout<DSUB>;
-    constexpr int HS = L::kHalfStride, RS = L::kResStride;
+    using L = TcLargeLayout<DSUB, TM>;
+    constexpr int RS = L::kResStride;
     constexpr int kChunks = DSUB / 8;  // threads per row: each owns elements [4c, 4c+4) and [d/2 + 4c, d/2 + 4c + 4)
     constexpr int kPass = kThreads / kChunks;  // rows per pass over the tile
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(16) unsigned char smem_dyn[];
+    // the tensor-core operands of the TM path start on a 1024-byte boundary of the shared window
+    unsigned char *smem_raw = smem_dyn;
+    if constexpr (TM) smem_raw += (1024u - ((uint32_t)__cvta_generic_to_shared(smem_dyn) & 1023u)) & 1023u;
     __half *tab = reinterpret_cast<__half *>(smem_raw + L::kTab);
     __half *hi = reinterpret_cast<__half *>(smem_raw + L::kHi);
     float *res = reinterpret_cast<float *>(smem_raw + L::kRes);
@@ -153,7 +200,8 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int gid = lane >> 2, q = lane & 3;
-    const int wr = warp >> 2, wq = warp & 3;  // row block (32 rows), word quarter (64 words)
+    // row block (32 rows), word quarter (64 words); a warp reads the tensor-memory lanes 32 * (warp % 4)..+31
+    const int wr = TM ? (warp & 3) : (warp >> 2), wq = TM ? (warp >> 2) : (warp & 3);
     const uint32_t rows = (uint32_t)B * (uint32_t)T;  // the launcher keeps B*T below 2^31
     const uint32_t tile = blockIdx.x * kRows;
     const int my_c = tid % kChunks, my_r = tid / kChunks;  // this thread's piece column and first row
@@ -166,7 +214,29 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
         code_at = codes + (((int64_t)b * H + h) * T_cap + t0 + t) * ((int64_t)S * G) + g;
     }
     if (tid == 0) *big = 0;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(count + 3);
+    int *tm_fail = count + 6;
+    const uint32_t mbar_a = (uint32_t)__cvta_generic_to_shared(smem_raw + L::kMisc + 16);
+    uint32_t tmem_base = 0;
+    if constexpr (TM) {
+        // 256 fp32 columns x 128 lanes of tensor memory hold the block's 128 x 256 score tile
+        if (warp == 0) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             (uint32_t)__cvta_generic_to_shared(tmem_slot)), "r"((uint32_t)kMaxWords) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+        if (tid == 0) {
+            *tm_fail = 0;
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_a) : "memory");
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
     __syncthreads();
+    if constexpr (TM) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    }
 #pragma unroll
     for (int r = my_r; r < kRows; r += kPass) {
         const uint32_t row = tile + r;
@@ -177,8 +247,8 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
             v0 = load4<XT>(src, vec_ok != 0);
             v1 = load4<XT>(src + DSUB / 2, vec_ok != 0);
         }
-        const float top0 = store_residual4(res + r * RS + 4 * my_c, hi + r * HS + 4 * my_c, v0);
-        const float top1 = store_residual4(res + r * RS + DSUB / 2 + 4 * my_c, hi + r * HS + DSUB / 2 + 4 * my_c, v1);
+        const float top0 = store_residual4(res + r * RS + 4 * my_c, hi + L::hi_at(r, 4 * my_c), v0);
+        const float top1 = store_residual4(res + r * RS + DSUB / 2 + 4 * my_c, hi + L::hi_at(r, DSUB / 2 + 4 * my_c), v1);
         if (!(fmaxf(top0, top1) < 32768.0f)) *big = 1;
     }
 
@@ -189,17 +259,36 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
             const int k = idx / kChunks, c = idx % kChunks;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (k < K) v = *reinterpret_cast<const uint4 *>(src + (int64_t)k * DSUB + c * 8);
-            *reinterpret_cast<uint4 *>(tab + k * HS + c * 8) = v;
+            *reinterpret_cast<uint4 *>(tab + L::tab_at(k, c * 8)) = v;
         }
         if (tid == 0) *count = 0;
+        if constexpr (TM) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what was stored above
         __syncthreads();
+        if constexpr (TM) {
+            // One thread issues the whole 128 x 256 x d product (d / 16 instructions); it runs while the
+            // block computes the norms below and reports to the mbarrier when the last one has finished.
+            if (tid == 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a0 = (uint32_t)__cvta_generic_to_shared(hi), b0 = (uint32_t)__cvta_generic_to_shared(tab);
+#pragma unroll
+                for (int ks = 0; ks < DSUB / 16; ++ks) {
+                    const uint64_t da = panel_descriptor(a0 + (ks >> 2) * (kRows * 128) + (ks & 3) * 32);
+                    const uint64_t db = panel_descriptor(b0 + (ks >> 2) * (kMaxWords * 128) + (ks & 3) * 32);
+                    asm volatile(
+                        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                        ::"r"(tmem_base), "l"(da), "l"(db), "r"(kMmaShape), "r"(ks) : "memory");
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_a) : "memory");
+            }
+        }
         // |c|^2 per word and |r|^2 per row, one warp per vector
         // (eight lanes per vector, four vectors per warp and trip, placed so that their loads miss each other's banks)
         if (sqnorm_in == nullptr) {
 #pragma unroll
             for (int it = 0; it < 4; ++it) {
                 const int k = warp * 16 + it * 4 + (lane >> 3);
-                float v = group8_sqnorm_ordered<DSUB>([&](int i) { return __half2float(tab[k * HS + i]); }, lane);
+                float v = group8_sqnorm_ordered<DSUB>([&](int i) { return __half2float(tab[L::tab_at(k, i)]); }, lane);
                 if (k >= K) v = inf;  // padding words can never be chosen
                 if ((lane & 7) == 0) {
                     nrm[k] = v;
@@ -230,106 +319,181 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
             if (lane == 0) *cc_max = top;
         }
 
-        // ---- approximate scores: 32 rows x 64 words per warp --------------------------------------
-        float acc[2][8][4];
-#pragma unroll
-        for (int n = 0; n < 8; ++n) {
-            const float2 sv = *reinterpret_cast<const float2 *>(seed + wq * 64 + n * 8 + 2 * q);
-#pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                acc[m][n][0] = sv.x;
-                acc[m][n][1] = sv.y;
-                acc[m][n][2] = sv.x;
-                acc[m][n][3] = sv.y;
+        if constexpr (TM) {
+            // ---- approximate scores from tensor memory: thread = row, 64 words of quarter wq per thread ------
+            {
+                int done = 0;
+                for (int spin = 0; spin < (1 << 22) && !done; ++spin)  // bounded wait for the products issued above
+                    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.s32 %0, 1, 0, p;\n}"
+                                 : "=r"(done) : "r"(mbar_a), "r"((uint32_t)(s & 1)) : "memory");
+                if (!done) {  // never seen; the stage then re-evaluates every pair, so the codes stay exact
+                    *tm_fail = 1;
+                    atomicAdd(&g_tensor_memory_timeouts, 1u);
+                }
+                __syncwarp();
             }
-        }
-        {
-            // ldmatrix lane addresses: A tiles are [16 rows][16 k], B tiles [16 words][16 k] (two n-tiles)
-            const int a_row = wr * 32 + (lane & 15), a_col = (lane >> 4) * 8;
-            const int b_row = wq * 64 + (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
-#pragma unroll 2
-            for (int ks = 0; ks < DSUB / 16; ++ks) {
-                uint32_t a[2][4];
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float sc[64];
+            {
+                uint32_t v[64];
+                const uint32_t taddr = tmem_base + ((uint32_t)(wr * 32) << 16) + (uint32_t)(wq * 64);
+                tmem_load32(v, taddr);
+                tmem_load32(v + 32, taddr + 32);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                float top = -inf;
 #pragma unroll
-                for (int m = 0; m < 2; ++m) ldmatrix_x4(a[m], hi + (a_row + m * 16) * HS + ks * 16 + a_col);
+                for (int j = 0; j < 64; j += 4) {
+                    const float4 sv = *reinterpret_cast<const float4 *>(seed + wq * 64 + j);
+                    sc[j] = __uint_as_float(v[j]) + sv.x;
+                    sc[j + 1] = __uint_as_float(v[j + 1]) + sv.y;
+                    sc[j + 2] = __uint_as_float(v[j + 2]) + sv.z;
+                    sc[j + 3] = __uint_as_float(v[j + 3]) + sv.w;
+                    top = fmaxf(fmaxf(top, fmaxf(sc[j], sc[j + 1])), fmaxf(sc[j + 2], sc[j + 3]));
+                }
+                rowmax[wq * kRows + wr * 32 + lane] = top;
+            }
+            __syncthreads();
+            if (tid < kRows) {
+                const float top = fmaxf(fmaxf(rowmax[tid], rowmax[kRows + tid]), fmaxf(rowmax[2 * kRows + tid], rowmax[3 * kRows + tid]));
+                const float cm = *cc_max, xx = xxs[tid];
+                const float margin = 1.220703125e-03f * sqrtf(xx * cm) + 6.103515625e-05f * (xx + cm) + 3.814697265625e-06f * sqrtf(cm);
+                thr[tid] = (*big != 0 || *tm_fail != 0) ? -inf : top - margin;
+            }
+            __syncthreads();
+            if (tid == 0) *big = 0;  // read above; the update below raises it for the next stage
+            // List the pairs within the margin: a thread holds one row's 64 scores, so its hits are a 64-bit mask.
+            {
+                const int r = wr * 32 + lane;
+                const float limit = thr[r];
+                uint32_t lo = 0u, hi32 = 0u;
 #pragma unroll
-                for (int np = 0; np < 4; ++np) {
-                    uint32_t bw[4];
-                    ldmatrix_x4(bw, tab + (b_row + np * 16) * HS + ks * 16 + b_col);
+                for (int j = 31; j >= 0; --j) {
+                    lo = __funnelshift_l(__float_as_uint(sc[j] - limit), lo, 1);
+                    hi32 = __funnelshift_l(__float_as_uint(sc[32 + j] - limit), hi32, 1);
+                }
+                unsigned long long todo = ~(((unsigned long long)hi32 << 32) | lo);  // set = not below the limit
+                const int hits = __popcll(todo);
+                int before = hits;  // inclusive prefix over the warp
 #pragma unroll
-                    for (int m = 0; m < 2; ++m) {
-                        mma_acc_16816(acc[m][2 * np], a[m], bw[0], bw[1]);
-                        mma_acc_16816(acc[m][2 * np + 1], a[m], bw[2], bw[3]);
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, before, off);
+                    if (lane >= off) before += up;
+                }
+                int base = 0;
+                if (lane == 31 && before > 0) base = atomicAdd(count, before);
+                base = __shfl_sync(0xffffffffu, base, 31);
+                int slot = base + before - hits;
+                if (hits > 0) atomicAdd(rowcnt + r, hits);
+                while (todo != 0ull) {
+                    const int j = __ffsll((long long)todo) - 1;
+                    todo &= todo - 1ull;
+                    if (slot < kListCap) list[slot] = (uint16_t)((r << 8) | (wq * 64 + j));
+                    ++slot;
+                }
+            }
+        } else {
+            // ---- approximate scores: 32 rows x 64 words per warp --------------------------------------
+            float acc[2][8][4];
+    #pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const float2 sv = *reinterpret_cast<const float2 *>(seed + wq * 64 + n * 8 + 2 * q);
+    #pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    acc[m][n][0] = sv.x;
+                    acc[m][n][1] = sv.y;
+                    acc[m][n][2] = sv.x;
+                    acc[m][n][3] = sv.y;
+                }
+            }
+            {
+                // ldmatrix lane addresses: A tiles are [16 rows][16 k], B tiles [16 words][16 k] (two n-tiles)
+                const int a_row = wr * 32 + (lane & 15), a_col = (lane >> 4) * 8;
+                const int b_row = wq * 64 + (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+    #pragma unroll 2
+                for (int ks = 0; ks < DSUB / 16; ++ks) {
+                    uint32_t a[2][4];
+    #pragma unroll
+                    for (int m = 0; m < 2; ++m) ldmatrix_x4(a[m], hi + L::hi_at(a_row + m * 16, ks * 16 + a_col));
+    #pragma unroll
+                    for (int np = 0; np < 4; ++np) {
+                        uint32_t bw[4];
+                        ldmatrix_x4(bw, tab + L::tab_at(b_row + np * 16, ks * 16 + b_col));
+    #pragma unroll
+                        for (int m = 0; m < 2; ++m) {
+                            mma_acc_16816(acc[m][2 * np], a[m], bw[0], bw[1]);
+                            mma_acc_16816(acc[m][2 * np + 1], a[m], bw[2], bw[3]);
+                        }
                     }
                 }
             }
-        }
-        // row maxima over this warp's 64 words
-#pragma unroll
-        for (int m = 0; m < 2; ++m) {
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                float top = fmaxf(acc[m][0][2 * half], acc[m][0][2 * half + 1]);
-#pragma unroll
-                for (int n = 1; n < 8; ++n) top = fmaxf(top, fmaxf(acc[m][n][2 * half], acc[m][n][2 * half + 1]));
-                top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
-                top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
-                if (q == 0) rowmax[wq * kRows + wr * 32 + m * 16 + half * 8 + gid] = top;
-            }
-        }
-        __syncthreads();
-        if (tid < kRows) {
-            const float top = fmaxf(fmaxf(rowmax[tid], rowmax[kRows + tid]), fmaxf(rowmax[2 * kRows + tid], rowmax[3 * kRows + tid]));
-            const float cm = *cc_max, xx = xxs[tid];
-            const float margin = 1.220703125e-03f * sqrtf(xx * cm) + 6.103515625e-05f * (xx + cm) + 3.814697265625e-06f * sqrtf(cm);
-            thr[tid] = (*big != 0) ? -inf : top - margin;
-        }
-        __syncthreads();
-        if (tid == 0) *big = 0;  // read above; the update below raises it for the next stage
-        // List the pairs within the margin.  Per row a thread shifts the sign of (score - limit) of its
-        // 16 words into a word (first word ends at bit 15, set = below the limit); one atomic per warp
-        // reserves the slots, then each thread walks its set bits.
-        {
-            uint32_t pass[2][2];
-            int hits = 0;
-#pragma unroll
+            // row maxima over this warp's 64 words
+    #pragma unroll
             for (int m = 0; m < 2; ++m) {
-#pragma unroll
+    #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    const float limit = thr[wr * 32 + m * 16 + half * 8 + gid];
-                    uint32_t fail = 0u;
-#pragma unroll
-                    for (int n = 0; n < 8; ++n) {
-                        fail = __funnelshift_l(__float_as_uint(acc[m][n][2 * half] - limit), fail, 1);
-                        fail = __funnelshift_l(__float_as_uint(acc[m][n][2 * half + 1] - limit), fail, 1);
-                    }
-                    pass[m][half] = ~fail & 0xffffu;
-                    hits += __popc(pass[m][half]);
+                    float top = fmaxf(acc[m][0][2 * half], acc[m][0][2 * half + 1]);
+    #pragma unroll
+                    for (int n = 1; n < 8; ++n) top = fmaxf(top, fmaxf(acc[m][n][2 * half], acc[m][n][2 * half + 1]));
+                    top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
+                    top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
+                    if (q == 0) rowmax[wq * kRows + wr * 32 + m * 16 + half * 8 + gid] = top;
                 }
             }
-            int before = hits;  // inclusive prefix over the warp
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int up = __shfl_up_sync(0xffffffffu, before, off);
-                if (lane >= off) before += up;
+            __syncthreads();
+            if (tid < kRows) {
+                const float top = fmaxf(fmaxf(rowmax[tid], rowmax[kRows + tid]), fmaxf(rowmax[2 * kRows + tid], rowmax[3 * kRows + tid]));
+                const float cm = *cc_max, xx = xxs[tid];
+                const float margin = 1.220703125e-03f * sqrtf(xx * cm) + 6.103515625e-05f * (xx + cm) + 3.814697265625e-06f * sqrtf(cm);
+                thr[tid] = (*big != 0) ? -inf : top - margin;
             }
-            int base = 0;
-            if (lane == 31 && before > 0) base = atomicAdd(count, before);
-            base = __shfl_sync(0xffffffffu, base, 31);
-            int slot = base + before - hits;
-#pragma unroll
-            for (int m = 0; m < 2; ++m) {
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t todo = pass[m][half];
-                    const int r = wr * 32 + m * 16 + half * 8 + gid;
-                    while (todo != 0u) {
-                        const int bit = 31 - __clz(todo);
-                        todo &= ~(1u << bit);
-                        const int pos = 15 - bit;  // n * 2 + e
-                        if (slot < kListCap) list[slot] = (uint16_t)((r << 8) | (wq * 64 + (pos >> 1) * 8 + 2 * q + (pos & 1)));
-                        ++slot;
-                        atomicAdd(rowcnt + r, 1);
+            __syncthreads();
+            if (tid == 0) *big = 0;  // read above; the update below raises it for the next stage
+            // List the pairs within the margin.  Per row a thread shifts the sign of (score - limit) of its
+            // 16 words into a word (first word ends at bit 15, set = below the limit); one atomic per warp
+            // reserves the slots, then each thread walks its set bits.
+            {
+                uint32_t pass[2][2];
+                int hits = 0;
+    #pragma unroll
+                for (int m = 0; m < 2; ++m) {
+    #pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const float limit = thr[wr * 32 + m * 16 + half * 8 + gid];
+                        uint32_t fail = 0u;
+    #pragma unroll
+                        for (int n = 0; n < 8; ++n) {
+                            fail = __funnelshift_l(__float_as_uint(acc[m][n][2 * half] - limit), fail, 1);
+                            fail = __funnelshift_l(__float_as_uint(acc[m][n][2 * half + 1] - limit), fail, 1);
+                        }
+                        pass[m][half] = ~fail & 0xffffu;
+                        hits += __popc(pass[m][half]);
+                    }
+                }
+                int before = hits;  // inclusive prefix over the warp
+    #pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, before, off);
+                    if (lane >= off) before += up;
+                }
+                int base = 0;
+                if (lane == 31 && before > 0) base = atomicAdd(count, before);
+                base = __shfl_sync(0xffffffffu, base, 31);
+                int slot = base + before - hits;
+    #pragma unroll
+                for (int m = 0; m < 2; ++m) {
+    #pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t todo = pass[m][half];
+                        const int r = wr * 32 + m * 16 + half * 8 + gid;
+                        while (todo != 0u) {
+                            const int bit = 31 - __clz(todo);
+                            todo &= ~(1u << bit);
+                            const int pos = 15 - bit;  // n * 2 + e
+                            if (slot < kListCap) list[slot] = (uint16_t)((r << 8) | (wq * 64 + (pos >> 1) * 8 + 2 * q + (pos & 1)));
+                            ++slot;
+                            atomicAdd(rowcnt + r, 1);
+                        }
                     }
                 }
             }
@@ -354,11 +518,10 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
                     continue;
                 }
                 const float *rv = res + r * RS;
-                const __half *cv = tab + k * HS;
                 float dot = 0.0f;
 #pragma unroll 4
                 for (int i8 = 0; i8 < DSUB; i8 += 8) {
-                    const uint4 cw = *reinterpret_cast<const uint4 *>(cv + i8);
+                    const uint4 cw = *reinterpret_cast<const uint4 *>(tab + L::tab_at(k, i8));
                     const __half2 *c2 = reinterpret_cast<const __half2 *>(&cw);
                     const float4 r0 = *reinterpret_cast<const float4 *>(rv + i8);
                     const float4 r1 = *reinterpret_cast<const float4 *>(rv + i8 + 4);
@@ -394,11 +557,11 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
             for (int piece = 0; piece < 2; ++piece) {
                 const int at = piece * (DSUB / 2) + 4 * my_c;
                 __half2 c2[2];
-                *reinterpret_cast<uint2 *>(c2) = *reinterpret_cast<const uint2 *>(tab + pick * HS + at);
+                *reinterpret_cast<uint2 *>(c2) = *reinterpret_cast<const uint2 *>(tab + L::tab_at(pick, at));
                 const float4 rv = *reinterpret_cast<const float4 *>(res + r * RS + at);
                 const float2 w0 = __half22float2(c2[0]), w1 = __half22float2(c2[1]);
                 const float4 nv = make_float4(__fsub_rn(rv.x, w0.x), __fsub_rn(rv.y, w0.y), __fsub_rn(rv.z, w1.x), __fsub_rn(rv.w, w1.y));
-                top = fmaxf(top, store_residual4(res + r * RS + at, hi + r * HS + at, nv));
+                top = fmaxf(top, store_residual4(res + r * RS + at, hi + L::hi_at(r, at), nv));
             }
             if (!(top < 32768.0f)) *big = 1;
         }
@@ -440,11 +603,23 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
             }
         }
     }
+    if constexpr (TM) {
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (warp == 0)
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kMaxWords) : "memory");
+    }
 }
+
+#ifndef TACVQ_ENCODE_TENSOR_MEMORY
+#define TACVQ_ENCODE_TENSOR_MEMORY 1  // 0: d = 64 and 128 also score with mma.sync from registers
+#endif
 
 template <int DSUB>
 static int launch_tc_large(const EncodeArgs &a) {
-    const size_t smem = TcLargeLayout<DSUB>::bytes(a.S);
+    // tcgen05 panels have 64-element rows, so the tensor-memory path carries d = 64 and 128
+    constexpr bool TM = TACVQ_ENCODE_TENSOR_MEMORY != 0 && DSUB >= 64;
+    const size_t smem = TcLargeLayout<DSUB, TM>::bytes(a.S);
     if (smem > 227 * 1024) return TACVQ_ERR_UNSUPPORTED;
     const int64_t rows = (int64_t)a.B * a.T;
     if (rows >= (int64_t)1 << 31) return TACVQ_ERR_UNSUPPORTED;
@@ -460,8 +635,8 @@ static int launch_tc_large(const EncodeArgs &a) {
                                                    a.recon, a.recon_dtype, a.B, a.H, a.T, a.G, a.S, a.K, a.t0, a.T_cap, vec_ok);
         return launch_status();
     };
-    if (a.x_dtype == TACVQ_F16) return launch(encode_tc_large_kernel<DSUB, __half>, (const __half *)a.x);
-    return launch(encode_tc_large_kernel<DSUB, float>, (const float *)a.x);
+    if (a.x_dtype == TACVQ_F16) return launch(encode_tc_large_kernel<DSUB, __half, TM>, (const __half *)a.x);
+    return launch(encode_tc_large_kernel<DSUB, float, TM>, (const float *)a.x);
 }
 
 // Returns TACVQ_ERR_UNSUPPORTED when the geometry is not this kernel's, so the caller can go on to
@@ -475,6 +650,10 @@ int encode_tc_large_launch(const EncodeArgs &a) {
         case 128: return launch_tc_large<128>(a);
         default: return TACVQ_ERR_UNSUPPORTED;
     }
+}
+
+int tensor_memory_timeouts(unsigned int *out) {
+    return (int)cudaMemcpyFromSymbol(out, g_tensor_memory_timeouts, sizeof(unsigned int));
 }
 
 }  // namespace tacvq

@@ -78,6 +78,18 @@ def table_sqnorm(tables_f16: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def encode_tensor_memory_timeouts(device=None) -> int:
+    """How often a wide-group encode block gave up waiting for its tensor-core products (expected 0)."""
+    import ctypes
+
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    count = ctypes.c_uint(0)
+    with _on(device):
+        status = _lib.load().tacvq_encode_tensor_memory_timeouts(ctypes.addressof(count))
+    _lib.check("tacvq_encode_tensor_memory_timeouts", status)
+    return int(count.value)
+
+
 _word_norms = table_sqnorm  # encode() has a keyword argument of the same name
 
 

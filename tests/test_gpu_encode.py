@@ -283,6 +283,8 @@ def test_wide_groups_strided_states_small_codebooks_and_in_place_rows(device, su
     b, rb = ops.encode(half_states.to(device), tables.to(device), table_sqnorm=norms)
     assert torch.equal(a.cpu(), want16) and torch.equal(a, b)
     assert torch.equal(ra.cpu(), want16_recon) and torch.equal(ra, rb)
+    # d = 64 and 128 take their approximate scores from tensor memory; no block may have given up waiting for them
+    assert ops.encode_tensor_memory_timeouts(device) == 0
 
 
 def test_caller_supplied_table_norms_and_own_norm_kernel(device):
