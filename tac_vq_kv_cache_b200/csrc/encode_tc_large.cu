@@ -3,9 +3,14 @@
 // Same idea as the 8-wide kernel in encode_tc.cu, shaped as a block-level GEMM.  A block owns 128
 // rows of one (head, group).  Per stage it
 //   1. keeps, next to the fp32 residual tile, its fp16 rounding in shared memory,
-//   2. scores all 128 x 256 (row, word) pairs with mma.sync.m16n8k16 (fragments by ldmatrix; each of
-//      16 warps owns 32 rows x 64 words; the accumulators start at -|c|^2/2, so a score is
-//      t = r.c - |c|^2/2 and the distance is |r|^2 - 2t),
+//   2. scores all 128 x 256 (row, word) pairs on the tensor cores; a score is t = r.c - |c|^2/2 and the
+//      distance is |r|^2 - 2t.
+//      d = 64, 128: both operands lie in shared memory as K-major panels with the 128-byte swizzle; one
+//      thread issues d/16 tcgen05.mma (M 128, N 256, K 16, fp16 x fp16 -> fp32) into 256 columns of tensor
+//      memory and commits them to an mbarrier, the other warps compute the row norms meanwhile, and every
+//      warp then reads its 32 rows x 64 words with tcgen05.ld (thread = row) and adds -|c|^2/2.
+//      d = 32: mma.sync.m16n8k16 with ldmatrix fragments, accumulators seeded with -|c|^2/2, each of
+//      16 warps owning 32 rows x 64 words,
 //   3. takes the row maxima over the four word quarters and lists every pair whose score lies within
 //      a margin of its row's maximum,
 //   4. re-evaluates the listed pairs in the library's exact fp32 order (one d-step FMA chain each,
@@ -255,13 +260,20 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
     for (int s = 0; s < S; ++s) {
         __syncthreads();  // residual tiles settled; the previous stage's table is no longer read
         const __half *src = tables + (((int64_t)h * S + s) * G + g) * (int64_t)K * DSUB;
+        // caller-supplied word norms: fetched by the upper half of the block while the table is copied
+        const int norm_k = tid - (kThreads - kMaxWords);
+        float norm_v = inf;
+        if (sqnorm_in != nullptr && norm_k >= 0 && norm_k < K) norm_v = sqnorm_in[(((int64_t)h * S + s) * G + g) * K + norm_k];
+        if (tid == 0) {
+            *count = 0;
+            *cc_max = 0.0f;
+        }
         for (int idx = tid; idx < kMaxWords * kChunks; idx += kThreads) {
             const int k = idx / kChunks, c = idx % kChunks;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (k < K) v = *reinterpret_cast<const uint4 *>(src + (int64_t)k * DSUB + c * 8);
             *reinterpret_cast<uint4 *>(tab + L::tab_at(k, c * 8)) = v;
         }
-        if (tid == 0) *count = 0;
         if constexpr (TM) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what was stored above
         __syncthreads();
         if constexpr (TM) {
@@ -282,27 +294,38 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_a) : "memory");
             }
         }
-        // |c|^2 per word and |r|^2 per row, one warp per vector
-        // (eight lanes per vector, four vectors per warp and trip, placed so that their loads miss each other's banks)
-        if (sqnorm_in == nullptr) {
+        // |c|^2 per word and |r|^2 per row, eight lanes per vector (four vectors per warp and trip, placed so
+        // that their loads miss each other's banks).  The largest |c|^2 is gathered with an integer atomic
+        // maximum (non-negative floats order like their bit patterns).
+        {
+            float top = 0.0f;
+            if (sqnorm_in == nullptr) {
 #pragma unroll
-            for (int it = 0; it < 4; ++it) {
-                const int k = warp * 16 + it * 4 + (lane >> 3);
-                float v = group8_sqnorm_ordered<DSUB>([&](int i) { return __half2float(tab[L::tab_at(k, i)]); }, lane);
-                if (k >= K) v = inf;  // padding words can never be chosen
-                if ((lane & 7) == 0) {
-                    nrm[k] = v;
-                    seed[k] = -0.5f * v;
+                for (int it = 0; it < 4; ++it) {
+                    const int k = warp * 16 + it * 4 + (lane >> 3);
+                    float v = group8_sqnorm_ordered<DSUB>([&](int i) { return __half2float(tab[L::tab_at(k, i)]); }, lane);
+                    if (k >= K) v = inf;  // padding words can never be chosen
+                    else if (v == v) top = fmaxf(top, v);
+                    if ((lane & 7) == 0) {
+                        nrm[k] = v;
+                        seed[k] = -0.5f * v;
+                    }
                 }
+            } else if (norm_k >= 0) {
+                nrm[norm_k] = norm_v;
+                seed[norm_k] = -0.5f * norm_v;
+                if (norm_k < K && norm_v == norm_v) top = norm_v;
             }
-        } else if (tid < kMaxWords) {
-            const float v = tid < K ? sqnorm_in[(((int64_t)h * S + s) * G + g) * K + tid] : inf;
-            nrm[tid] = v;
-            seed[tid] = -0.5f * v;
-        }
+            if (sqnorm_in == nullptr || norm_k >= 0) {  // warp-uniform
 #pragma unroll
-        for (int it = 0; it < 2; ++it) {
-            const int r = warp * 8 + it + 2 * (lane >> 3);
+                for (int off = 16; off >= 1; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+                if (lane == 0) atomicMax(reinterpret_cast<int *>(cc_max), __float_as_int(top));
+            }
+        }
+        // Row norms in 32 trips of 4 rows; on the tensor-memory path warp 0 takes none (its first thread is
+        // busy issuing the products), the other 15 warps share them.
+        for (int trip = TM ? (warp == 0 ? 32 : warp - 1) : warp; trip < 32; trip += TM ? 15 : 16) {
+            const int r = (trip >> 1) * 8 + (trip & 1) + 2 * (lane >> 3);
             const float v = group8_sqnorm_ordered<DSUB>([&](int i) { return res[r * RS + i]; }, lane);
             if ((lane & 7) == 0) {
                 xxs[r] = v;
@@ -311,13 +334,6 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
             }
         }
         __syncthreads();
-        if (warp == 0) {
-            float top = 0.0f;
-            for (int k = lane; k < K; k += 32) top = fmaxf(top, nrm[k]);
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
-            if (lane == 0) *cc_max = top;
-        }
 
         if constexpr (TM) {
             // ---- approximate scores from tensor memory: thread = row, 64 words of quarter wq per thread ------
