@@ -535,7 +535,7 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
                 }
                 const float *rv = res + r * RS;
                 float dot = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
                 for (int i8 = 0; i8 < DSUB; i8 += 8) {
                     const uint4 cw = *reinterpret_cast<const uint4 *>(tab + L::tab_at(k, i8));
                     const __half2 *c2 = reinterpret_cast<const __half2 *>(&cw);
