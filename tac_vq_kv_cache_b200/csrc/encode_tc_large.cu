@@ -591,30 +591,47 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
 
     if (recon != nullptr) {
         __syncthreads();
-        const int64_t stage_words = (int64_t)G * K * DSUB;
+        // stage loop outermost: the gathers of a stage (this thread's rows and pieces) travel together
+        constexpr int kMine = kRows / kPass;
+        float4 sum[kMine][2];
 #pragma unroll
-        for (int r = my_r; r < kRows; r += kPass) {
-            const uint32_t row = tile + r;
+        for (int i = 0; i < kMine; ++i) sum[i][0] = sum[i][1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const __half *words = tables + ((int64_t)h * S * G + g) * (int64_t)K * DSUB + 4 * my_c;
+        const int64_t stage_words = (int64_t)G * K * DSUB;
+#pragma unroll 1
+        for (int s = 0; s < S; ++s) {
+            uint2 raw[kMine][2];
+#pragma unroll
+            for (int i = 0; i < kMine; ++i) {
+                const __half *word = words + s * stage_words + (int64_t)hist[(my_r + i * kPass) * S + s] * DSUB;
+                raw[i][0] = *reinterpret_cast<const uint2 *>(word);
+                raw[i][1] = *reinterpret_cast<const uint2 *>(word + DSUB / 2);
+            }
+#pragma unroll
+            for (int i = 0; i < kMine; ++i) {
+#pragma unroll
+                for (int piece = 0; piece < 2; ++piece) {
+                    const __half2 *c2 = reinterpret_cast<const __half2 *>(&raw[i][piece]);
+                    const float2 w0 = __half22float2(c2[0]), w1 = __half22float2(c2[1]);
+                    float4 &acc = sum[i][piece];
+                    acc = make_float4(__fadd_rn(acc.x, w0.x), __fadd_rn(acc.y, w0.y), __fadd_rn(acc.z, w1.x), __fadd_rn(acc.w, w1.y));
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kMine; ++i) {
+            const uint32_t row = tile + my_r + i * kPass;
             if (row >= rows) continue;
             const uint32_t b = row / (uint32_t)T, t = row % (uint32_t)T;
 #pragma unroll
             for (int piece = 0; piece < 2; ++piece) {
                 const int at = piece * (DSUB / 2) + 4 * my_c;
-                const __half *words = tables + ((int64_t)h * S * G + g) * (int64_t)K * DSUB + at;
-                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                for (int s = 0; s < S; ++s) {
-                    __half2 c2[2];
-                    *reinterpret_cast<uint2 *>(c2) =
-                        *reinterpret_cast<const uint2 *>(words + s * stage_words + (int64_t)hist[r * S + s] * DSUB);
-                    const float2 w0 = __half22float2(c2[0]), w1 = __half22float2(c2[1]);
-                    sum = make_float4(__fadd_rn(sum.x, w0.x), __fadd_rn(sum.y, w0.y), __fadd_rn(sum.z, w1.x), __fadd_rn(sum.w, w1.y));
-                }
                 const int64_t o = (((int64_t)b * H + h) * T + t) * ((int64_t)G * DSUB) + (int64_t)g * DSUB + at;
                 if (recon_dtype == TACVQ_F16) {
-                    __half2 out[2] = {__floats2half2_rn(sum.x, sum.y), __floats2half2_rn(sum.z, sum.w)};
+                    __half2 out[2] = {__floats2half2_rn(sum[i][piece].x, sum[i][piece].y), __floats2half2_rn(sum[i][piece].z, sum[i][piece].w)};
                     *reinterpret_cast<uint2 *>((__half *)recon + o) = *reinterpret_cast<const uint2 *>(out);
                 } else {
-                    *reinterpret_cast<float4 *>((float *)recon + o) = sum;
+                    *reinterpret_cast<float4 *>((float *)recon + o) = sum[i][piece];
                 }
             }
         }
@@ -627,15 +644,440 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// d = 64, 128 with the residual tile in tensor memory
+// ------------------------------------------------------------------------------------------------
+// Same search, organised around tensor memory.  Thread (row, q) = (32 * (warp % 4) + lane, warp / 4):
+// a warp can reach the 32 tensor-memory lanes 32 * (warp % 4)..+31, and a lane is a row.
+//   * The fp32 residual tile lives in tensor-memory columns [256, 256 + d) (the scores use [0, 256)); only
+//     its fp16 rounding, the A operand of the product, is in shared memory.  Thread (row, q) owns the
+//     8-element pieces q, q + 4, q + 8, ... of its row: exactly the elements of one of the four partial sums
+//     the library's |r|^2 order is made of, so the residual update also yields the next stage's partial
+//     sums, and a 16 KB exchange through shared memory finishes the norm.
+//   * With the residual out of shared memory there is room for two table buffers: the next stage's table
+//     arrives by cp.async while the current stage is searched.
+//   * A thread keeps the candidate mask of its 64 words; there is no list.  Rows with a single candidate
+//     take it; otherwise every thread runs the exact chain for its own candidates, reading its row from
+//     tensor memory 32 columns at a time (warp-wide loads, so the loop is warp-uniform).
+
+template <int DSUB>
+struct TmLargeLayout {
+    static constexpr size_t kTabBytes = (size_t)kMaxWords * DSUB * 2;
+    static constexpr size_t kTab = 0;                                   // two buffers, swizzled K-major panels
+    static constexpr size_t kHi = 2 * kTabBytes;                        // [kRows][DSUB] half, swizzled K-major panels
+    static constexpr size_t kExch = kHi + (size_t)kRows * DSUB * 2;     // [kRows][36] float: four partial-sum sets of 8
+    static constexpr size_t kNrm = kExch + (size_t)kRows * 36 * 4;      // [256] float
+    static constexpr size_t kSeed = kNrm + kMaxWords * 4;               // [256] float: -|c|^2/2
+    static constexpr size_t kXx = kSeed + kMaxWords * 4;                // [kRows] float
+    static constexpr size_t kRowMax = kXx + kRows * 4;                  // [4][kRows] float
+    static constexpr size_t kCnt = kRowMax + 4 * kRows * 4;             // [4][kRows] int: candidates per quarter
+    static constexpr size_t kBest = kCnt + 4 * kRows * 4;               // [kRows] u64
+    static constexpr size_t kMisc = kBest + kRows * 8;                  // mbarrier, tensor-memory slot, flags, cc_max
+    static constexpr size_t kHist = kMisc + 64;                         // [kRows][S] u8
+    static constexpr size_t bytes(int S) { return kHist + (size_t)kRows * S + 1024; }  // + room to align the base
+    __device__ static __forceinline__ int tab_at(int k, int e) {
+        return (e >> 6) * (kMaxWords * 64) + k * 64 + ((((e >> 3) & 7) ^ (k & 7)) << 3) + (e & 7);
+    }
+    __device__ static __forceinline__ int hi_at(int r, int e) {
+        return (e >> 6) * (kRows * 64) + r * 64 + ((((e >> 3) & 7) ^ (r & 7)) << 3) + (e & 7);
+    }
+};
+
+__device__ __forceinline__ void tmem_load8(uint32_t *v, uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_store8(uint32_t taddr, const float *v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "f"(v[0]), "f"(v[1]),
+                 "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+                 : "memory");
+}
+__device__ __forceinline__ uint4 pack8_half(const float *v) {
+    const __half2 h[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]), __floats2half2_rn(v[4], v[5]),
+                          __floats2half2_rn(v[6], v[7])};
+    return *reinterpret_cast<const uint4 *>(h);
+}
+__device__ __forceinline__ void unpack8_half(const uint4 raw, float *v) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
+template <int DSUB, typename XT>
+__global__ void __launch_bounds__(kThreads, 1)
+encode_tm_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const __half *__restrict__ tables,
+                       const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
+                       int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap, int vec_ok) {
+    using L = TmLargeLayout<DSUB>;
+    constexpr int kChunks = DSUB / 8;   // 16-byte pieces per row
+    constexpr int kOwn = DSUB / 32;     // pieces a thread owns per row: q, q + 4, ...
+    constexpr uint32_t kTmemCols = 512; // scores [0, 256), residual [256, 256 + DSUB)
+    extern __shared__ __align__(16) unsigned char smem_dyn[];
+    unsigned char *smem_raw = smem_dyn + ((1024u - ((uint32_t)__cvta_generic_to_shared(smem_dyn) & 1023u)) & 1023u);
+    __half *tab_buf = reinterpret_cast<__half *>(smem_raw + L::kTab);
+    __half *hi = reinterpret_cast<__half *>(smem_raw + L::kHi);
+    float *exch = reinterpret_cast<float *>(smem_raw + L::kExch);
+    float *nrm = reinterpret_cast<float *>(smem_raw + L::kNrm);
+    float *seed = reinterpret_cast<float *>(smem_raw + L::kSeed);
+    float *xxs = reinterpret_cast<float *>(smem_raw + L::kXx);
+    float *rowmax = reinterpret_cast<float *>(smem_raw + L::kRowMax);
+    int *cnt = reinterpret_cast<int *>(smem_raw + L::kCnt);
+    unsigned long long *best = reinterpret_cast<unsigned long long *>(smem_raw + L::kBest);
+    const uint32_t mbar_a = (uint32_t)__cvta_generic_to_shared(smem_raw + L::kMisc);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + L::kMisc + 8);
+    int *big = reinterpret_cast<int *>(smem_raw + L::kMisc + 12);      // [2]: some residual element of stage parity p does not fit fp16
+    int *tm_fail = reinterpret_cast<int *>(smem_raw + L::kMisc + 20);
+    float *cc_max = reinterpret_cast<float *>(smem_raw + L::kMisc + 24);
+    uint8_t *hist = smem_raw + L::kHist;
+
+    const int hg = blockIdx.y;
+    const int h = hg / G, g = hg % G;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int row = (warp & 3) * 32 + lane, q = warp >> 2;
+    const uint32_t rows = (uint32_t)B * (uint32_t)T;  // the launcher keeps B*T below 2^31
+    const uint32_t tile = blockIdx.x * kRows;
+    const float inf = __int_as_float(0x7f800000);
+
+    // table of stage s -> buffer s & 1, zero rows past K
+    auto fetch_table = [&](int s) {
+        const __half *src = tables + (((int64_t)h * S + s) * G + g) * (int64_t)K * DSUB;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(tab_buf) + (uint32_t)(s & 1) * (uint32_t)L::kTabBytes;
+#pragma unroll
+        for (int idx = tid; idx < kMaxWords * kChunks; idx += kThreads) {
+            const int k = idx / kChunks, c = idx % kChunks;
+            const bool real = k < K;
+            const __half *from = real ? src + (int64_t)k * DSUB + c * 8 : src;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + (uint32_t)L::tab_at(k, c * 8) * 2), "l"(from),
+                         "r"(real ? 16 : 0) : "memory");
+        }
+    };
+    fetch_table(0);
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         (uint32_t)__cvta_generic_to_shared(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid == 0) {
+        big[0] = 0;
+        big[1] = 0;
+        *tm_fail = 0;
+        *cc_max = 0.0f;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_a) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const uint32_t score_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(q * 64);
+    const uint32_t res_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)kMaxWords;
+
+    uint8_t *code_at = nullptr;  // this row's first code byte (threads with q == 0)
+    const bool live = tile + row < rows;
+    const uint32_t rb = live ? (tile + row) / (uint32_t)T : 0u, rt = live ? (tile + row) % (uint32_t)T : 0u;
+    if (q == 0 && live) code_at = codes + (((int64_t)rb * H + h) * T_cap + t0 + rt) * ((int64_t)S * G) + g;
+
+    // ---- the block's rows: fp32 into tensor memory, fp16 rounding into shared memory, partial sums of |r|^2 ----
+    {
+        float part[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f}, top = 0.0f;
+        float4 in[kOwn][2];  // every piece is requested before the first one is used
+#pragma unroll
+        for (int m = 0; m < kOwn; ++m) {
+            in[m][0] = in[m][1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (live) {
+                const XT *src = x + (int64_t)rb * sxb + (int64_t)h * sxh + (int64_t)rt * sxt + (int64_t)g * DSUB + 8 * (q + 4 * m);
+                in[m][0] = load4<XT>(src, vec_ok != 0);
+                in[m][1] = load4<XT>(src + 4, vec_ok != 0);
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < kOwn; ++m) {
+            const int e0 = 8 * (q + 4 * m);
+            const float v[8] = {in[m][0].x, in[m][0].y, in[m][0].z, in[m][0].w, in[m][1].x, in[m][1].y, in[m][1].z, in[m][1].w};
+            tmem_store8(res_addr + e0, v);
+            *reinterpret_cast<uint4 *>(hi + L::hi_at(row, e0)) = pack8_half(v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                part[j] = __fadd_rn(part[j], __fmul_rn(v[j], v[j]));
+                top = fmaxf(top, fabsf(v[j]));
+            }
+        }
+        *reinterpret_cast<float4 *>(exch + row * 36 + q * 8) = make_float4(part[0], part[1], part[2], part[3]);
+        *reinterpret_cast<float4 *>(exch + row * 36 + q * 8 + 4) = make_float4(part[4], part[5], part[6], part[7]);
+        if (!(top < 32768.0f)) big[0] = 1;
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+
+    uint64_t todo = 0ull;
+    for (int s = 0; s < S; ++s) {
+        const __half *tab = tab_buf + (size_t)(s & 1) * (L::kTabBytes / 2);
+        // caller-supplied word norms: fetched by the upper half of the block
+        const int norm_k = tid - (kThreads - kMaxWords);
+        float norm_v = inf;
+        if (sqnorm_in != nullptr && norm_k >= 0 && norm_k < K) norm_v = sqnorm_in[(((int64_t)h * S + s) * G + g) * K + norm_k];
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads the table and the fp16 rows
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();  // table s, fp16 rows, residual and partial sums settled
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a0 = (uint32_t)__cvta_generic_to_shared(hi), b0 = (uint32_t)__cvta_generic_to_shared(tab);
+#pragma unroll
+            for (int ks = 0; ks < DSUB / 16; ++ks) {
+                const uint64_t da = panel_descriptor(a0 + (ks >> 2) * (kRows * 128) + (ks & 3) * 32);
+                const uint64_t db = panel_descriptor(b0 + (ks >> 2) * (kMaxWords * 128) + (ks & 3) * 32);
+                asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                             ::"r"(tmem_base), "l"(da), "l"(db), "r"(kMmaShape), "r"(ks) : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_a) : "memory");
+            big[(s + 1) & 1] = 0;  // read two stages ago, raised by this stage's update
+        }
+        if (s + 1 < S) fetch_table(s + 1);  // its buffer was last read by the previous stage's update
+        // |c|^2 per word (eight lanes per word when the caller gave none), largest by an integer atomic maximum
+        {
+            float top = 0.0f;
+            if (sqnorm_in == nullptr) {
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                    const int k = warp * 16 + it * 4 + (lane >> 3);
+                    float v = group8_sqnorm_ordered<DSUB>([&](int i) { return __half2float(tab[L::tab_at(k, i)]); }, lane);
+                    if (k >= K) v = inf;  // padding words can never be chosen
+                    else if (v == v) top = fmaxf(top, v);
+                    if ((lane & 7) == 0) {
+                        nrm[k] = v;
+                        seed[k] = -0.5f * v;
+                    }
+                }
+            } else if (norm_k >= 0) {
+                nrm[norm_k] = norm_v;
+                seed[norm_k] = -0.5f * norm_v;
+                if (norm_k < K && norm_v == norm_v) top = norm_v;
+            }
+            if (sqnorm_in == nullptr || norm_k >= 0) {  // warp-uniform
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+                if (lane == 0) atomicMax(reinterpret_cast<int *>(cc_max), __float_as_int(top));
+            }
+        }
+        // |r|^2 in the library's order from the four sets of partial sums: threads q == 1 (warps 4-7)
+        if (q == 1) {
+            const float4 *e = reinterpret_cast<const float4 *>(exch + row * 36);
+            float mine[8];
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const float4 s0 = e[hf], s1 = e[2 + hf], s2 = e[4 + hf], s3 = e[6 + hf];
+                mine[4 * hf + 0] = __fadd_rn(__fadd_rn(__fadd_rn(s0.x, s1.x), s2.x), s3.x);
+                mine[4 * hf + 1] = __fadd_rn(__fadd_rn(__fadd_rn(s0.y, s1.y), s2.y), s3.y);
+                mine[4 * hf + 2] = __fadd_rn(__fadd_rn(__fadd_rn(s0.z, s1.z), s2.z), s3.z);
+                mine[4 * hf + 3] = __fadd_rn(__fadd_rn(__fadd_rn(s0.w, s1.w), s2.w), s3.w);
+            }
+            float total = mine[0];
+#pragma unroll
+            for (int j = 1; j < 8; ++j) total = __fadd_rn(total, mine[j]);
+            xxs[row] = total;
+            best[row] = ~0ull;
+        }
+        __syncthreads();
+
+        // ---- approximate scores from tensor memory: 64 words of quarter q per thread ----------------
+        {
+            int done = 0;
+            for (int spin = 0; spin < (1 << 22) && !done; ++spin)  // bounded wait for the products issued above
+                asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.s32 %0, 1, 0, p;\n}"
+                             : "=r"(done) : "r"(mbar_a), "r"((uint32_t)(s & 1)) : "memory");
+            if (!done) {  // never seen; the stage then re-evaluates every pair, so the codes stay exact
+                *tm_fail = 1;
+                atomicAdd(&g_tensor_memory_timeouts, 1u);
+            }
+            __syncwarp();
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float sc[64];
+        {
+            uint32_t v[64];
+            tmem_load32(v, score_addr);
+            tmem_load32(v + 32, score_addr + 32);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float top = -inf;
+#pragma unroll
+            for (int j = 0; j < 64; j += 4) {
+                const float4 sv = *reinterpret_cast<const float4 *>(seed + q * 64 + j);
+                sc[j] = __uint_as_float(v[j]) + sv.x;
+                sc[j + 1] = __uint_as_float(v[j + 1]) + sv.y;
+                sc[j + 2] = __uint_as_float(v[j + 2]) + sv.z;
+                sc[j + 3] = __uint_as_float(v[j + 3]) + sv.w;
+                top = fmaxf(fmaxf(top, fmaxf(sc[j], sc[j + 1])), fmaxf(sc[j + 2], sc[j + 3]));
+            }
+            rowmax[q * kRows + row] = top;
+        }
+        __syncthreads();
+        const bool everything = big[s & 1] != 0 || *tm_fail != 0;
+        {
+            const float top = fmaxf(fmaxf(rowmax[row], rowmax[kRows + row]), fmaxf(rowmax[2 * kRows + row], rowmax[3 * kRows + row]));
+            const float cm = *cc_max, xx = xxs[row];
+            const float margin = 1.220703125e-03f * sqrtf(xx * cm) + 6.103515625e-05f * (xx + cm) + 3.814697265625e-06f * sqrtf(cm);
+            const float limit = everything ? -inf : top - margin;
+            uint32_t lo = 0u, hi32 = 0u;
+#pragma unroll
+            for (int j = 31; j >= 0; --j) {
+                lo = __funnelshift_l(__float_as_uint(sc[j] - limit), lo, 1);
+                hi32 = __funnelshift_l(__float_as_uint(sc[32 + j] - limit), hi32, 1);
+            }
+            todo = everything ? ~0ull : ~(((uint64_t)hi32 << 32) | lo);  // set = not below the limit
+            cnt[q * kRows + row] = __popcll(todo);
+        }
+        __syncthreads();
+        if (tid == 0) *cc_max = 0.0f;  // read above; gathered again after the next stage's first barrier
+        // ---- decide: a row's only candidate is its code; otherwise the exact chains of every candidate ------
+        {
+            const int listed = cnt[row] + cnt[kRows + row] + cnt[2 * kRows + row] + cnt[3 * kRows + row];
+            if (!everything && listed == 1) {
+                if (todo != 0ull) best[row] = (unsigned long long)(q * 64 + __ffsll((long long)todo) - 1);
+                todo = 0ull;
+            }
+            const float xx = xxs[row];
+            while (__any_sync(0xffffffffu, todo != 0ull)) {
+                const bool active = todo != 0ull;
+                int k = 0;
+                if (active) {
+                    k = q * 64 + __ffsll((long long)todo) - 1;
+                    todo &= todo - 1ull;
+                }
+                const bool real = active && k < K;
+                float dot = 0.0f;
+#pragma unroll 1
+                for (int c32 = 0; c32 < DSUB / 32; ++c32) {
+                    uint32_t rv[32];
+                    tmem_load32(rv, res_addr + c32 * 32);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (real) {
+#pragma unroll
+                        for (int i8 = 0; i8 < 4; ++i8) {
+                            float c[8];
+                            unpack8_half(*reinterpret_cast<const uint4 *>(tab + L::tab_at(k, c32 * 32 + i8 * 8)), c);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) dot = __fmaf_rn(__uint_as_float(rv[i8 * 8 + j]), c[j], dot);
+                        }
+                    }
+                }
+                if (real) {
+                    const float dist = distance_expr(xx, nrm[k], dot);
+                    if (dist == dist) {  // a NaN distance never wins, as in a strict '<' scan
+                        const unsigned long long key = ((unsigned long long)ordered_bits(dist) << 32) | (unsigned)k;
+                        atomicMin(best + row, key);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        // ---- update: subtract the chosen word from this thread's pieces, refresh the fp16 copy, next partial sums ----
+        {
+            const unsigned long long key = best[row];
+            const int pick = (key == ~0ull) ? 0 : (int)(key & 0xffffffffull);
+            uint32_t rv[kOwn][8];
+#pragma unroll
+            for (int m = 0; m < kOwn; ++m) tmem_load8(rv[m], res_addr + 8 * (q + 4 * m));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float part[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f}, top = 0.0f;
+#pragma unroll
+            for (int m = 0; m < kOwn; ++m) {
+                const int e0 = 8 * (q + 4 * m);
+                float c[8], nv[8];
+                unpack8_half(*reinterpret_cast<const uint4 *>(tab + L::tab_at(pick, e0)), c);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    nv[j] = __fsub_rn(__uint_as_float(rv[m][j]), c[j]);
+                    part[j] = __fadd_rn(part[j], __fmul_rn(nv[j], nv[j]));
+                    top = fmaxf(top, fabsf(nv[j]));
+                }
+                tmem_store8(res_addr + e0, nv);
+                *reinterpret_cast<uint4 *>(hi + L::hi_at(row, e0)) = pack8_half(nv);
+            }
+            *reinterpret_cast<float4 *>(exch + row * 36 + q * 8) = make_float4(part[0], part[1], part[2], part[3]);
+            *reinterpret_cast<float4 *>(exch + row * 36 + q * 8 + 4) = make_float4(part[4], part[5], part[6], part[7]);
+            if (!(top < 32768.0f)) big[(s + 1) & 1] = 1;
+            if (q == 0) {
+                hist[row * S + s] = (uint8_t)pick;
+                if (code_at != nullptr) code_at[(int64_t)s * G] = (uint8_t)pick;
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+    }
+
+    if (recon != nullptr) {
+        __syncthreads();
+        constexpr int kPass = kThreads / kChunks;
+        const int my_c = tid % kChunks, my_r = tid / kChunks;
+        // stage loop outermost: the gathers of a stage (this thread's rows and pieces) travel together
+        constexpr int kMine = kRows / kPass;
+        float4 sum[kMine][2];
+#pragma unroll
+        for (int i = 0; i < kMine; ++i) sum[i][0] = sum[i][1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const __half *words = tables + ((int64_t)h * S * G + g) * (int64_t)K * DSUB + 4 * my_c;
+        const int64_t stage_words = (int64_t)G * K * DSUB;
+#pragma unroll 1
+        for (int s = 0; s < S; ++s) {
+            uint2 raw[kMine][2];
+#pragma unroll
+            for (int i = 0; i < kMine; ++i) {
+                const __half *word = words + s * stage_words + (int64_t)hist[(my_r + i * kPass) * S + s] * DSUB;
+                raw[i][0] = *reinterpret_cast<const uint2 *>(word);
+                raw[i][1] = *reinterpret_cast<const uint2 *>(word + DSUB / 2);
+            }
+#pragma unroll
+            for (int i = 0; i < kMine; ++i) {
+#pragma unroll
+                for (int piece = 0; piece < 2; ++piece) {
+                    const __half2 *c2 = reinterpret_cast<const __half2 *>(&raw[i][piece]);
+                    const float2 w0 = __half22float2(c2[0]), w1 = __half22float2(c2[1]);
+                    float4 &acc = sum[i][piece];
+                    acc = make_float4(__fadd_rn(acc.x, w0.x), __fadd_rn(acc.y, w0.y), __fadd_rn(acc.z, w1.x), __fadd_rn(acc.w, w1.y));
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kMine; ++i) {
+            const uint32_t grow = tile + my_r + i * kPass;
+            if (grow >= rows) continue;
+            const uint32_t b = grow / (uint32_t)T, t = grow % (uint32_t)T;
+#pragma unroll
+            for (int piece = 0; piece < 2; ++piece) {
+                const int at = piece * (DSUB / 2) + 4 * my_c;
+                const int64_t o = (((int64_t)b * H + h) * T + t) * ((int64_t)G * DSUB) + (int64_t)g * DSUB + at;
+                if (recon_dtype == TACVQ_F16) {
+                    __half2 out[2] = {__floats2half2_rn(sum[i][piece].x, sum[i][piece].y), __floats2half2_rn(sum[i][piece].z, sum[i][piece].w)};
+                    *reinterpret_cast<uint2 *>((__half *)recon + o) = *reinterpret_cast<const uint2 *>(out);
+                } else {
+                    *reinterpret_cast<float4 *>((float *)recon + o) = sum[i][piece];
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
 #ifndef TACVQ_ENCODE_TENSOR_MEMORY
-#define TACVQ_ENCODE_TENSOR_MEMORY 1  // 0: d = 64 and 128 also score with mma.sync from registers
+#define TACVQ_ENCODE_TENSOR_MEMORY 2  // 2: residual tile in tensor memory; 1: scores only; 0: mma.sync from registers
 #endif
 
 template <int DSUB>
 static int launch_tc_large(const EncodeArgs &a) {
     // tcgen05 panels have 64-element rows, so the tensor-memory path carries d = 64 and 128
     constexpr bool TM = TACVQ_ENCODE_TENSOR_MEMORY != 0 && DSUB >= 64;
-    const size_t smem = TcLargeLayout<DSUB, TM>::bytes(a.S);
+    constexpr bool TM2 = TACVQ_ENCODE_TENSOR_MEMORY == 2 && DSUB >= 64;
+    size_t smem = TcLargeLayout<DSUB, TM>::bytes(a.S);
+    if constexpr (TM2) smem = TmLargeLayout<DSUB>::bytes(a.S);
     if (smem > 227 * 1024) return TACVQ_ERR_UNSUPPORTED;
     const int64_t rows = (int64_t)a.B * a.T;
     if (rows >= (int64_t)1 << 31) return TACVQ_ERR_UNSUPPORTED;
@@ -651,6 +1093,10 @@ static int launch_tc_large(const EncodeArgs &a) {
                                                    a.recon, a.recon_dtype, a.B, a.H, a.T, a.G, a.S, a.K, a.t0, a.T_cap, vec_ok);
         return launch_status();
     };
+    if constexpr (TM2) {
+        if (a.x_dtype == TACVQ_F16) return launch(encode_tm_large_kernel<DSUB, __half>, (const __half *)a.x);
+        return launch(encode_tm_large_kernel<DSUB, float>, (const float *)a.x);
+    }
     if (a.x_dtype == TACVQ_F16) return launch(encode_tc_large_kernel<DSUB, __half, TM>, (const __half *)a.x);
     return launch(encode_tc_large_kernel<DSUB, float, TM>, (const float *)a.x);
 }
