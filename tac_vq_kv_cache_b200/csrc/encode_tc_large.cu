@@ -1096,9 +1096,10 @@ static int launch_tc_large(const EncodeArgs &a) {
     if constexpr (TM2) {
         if (a.x_dtype == TACVQ_F16) return launch(encode_tm_large_kernel<DSUB, __half>, (const __half *)a.x);
         return launch(encode_tm_large_kernel<DSUB, float>, (const float *)a.x);
+    } else {
+        if (a.x_dtype == TACVQ_F16) return launch(encode_tc_large_kernel<DSUB, __half, TM>, (const __half *)a.x);
+        return launch(encode_tc_large_kernel<DSUB, float, TM>, (const float *)a.x);
     }
-    if (a.x_dtype == TACVQ_F16) return launch(encode_tc_large_kernel<DSUB, __half, TM>, (const __half *)a.x);
-    return launch(encode_tc_large_kernel<DSUB, float, TM>, (const float *)a.x);
 }
 
 // Returns TACVQ_ERR_UNSUPPORTED when the geometry is not this kernel's, so the caller can go on to
