@@ -5,12 +5,11 @@
 //   1. keeps, next to the fp32 residual tile, its fp16 rounding in shared memory,
 //   2. scores all 128 x 256 (row, word) pairs on the tensor cores; a score is t = r.c - |c|^2/2 and the
 //      distance is |r|^2 - 2t.
-//      d = 64, 128: both operands lie in shared memory as K-major panels with the 128-byte swizzle; one
-//      thread issues d/16 tcgen05.mma (M 128, N 256, K 16, fp16 x fp16 -> fp32) into 256 columns of tensor
-//      memory and commits them to an mbarrier, the other warps compute the row norms meanwhile, and every
-//      warp then reads its 32 rows x 64 words with tcgen05.ld (thread = row) and adds -|c|^2/2.
-//      d = 32: mma.sync.m16n8k16 with ldmatrix fragments, accumulators seeded with -|c|^2/2, each of
-//      16 warps owning 32 rows x 64 words,
+//      d = 64, 128 (encode_tm_large_kernel, further down): tcgen05.mma from shared-memory panels into
+//      tensor memory, where the fp32 residual tile lives too; that kernel has its own description.
+//      d = 32 (encode_tc_large_kernel): mma.sync.m16n8k16 with ldmatrix fragments, accumulators seeded with
+//      -|c|^2/2, each of 16 warps owning 32 rows x 64 words.  Built with TACVQ_ENCODE_TENSOR_MEMORY=1 this
+//      kernel also carries d = 64, 128, with the tcgen05 product but the residual tile in shared memory.
 //   3. takes the row maxima over the four word quarters and lists every pair whose score lies within
 //      a margin of its row's maximum,
 //   4. re-evaluates the listed pairs in the library's exact fp32 order (one d-step FMA chain each,
