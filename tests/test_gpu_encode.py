@@ -147,7 +147,7 @@ def test_encode_is_bit_exact_with_the_c_oracle(device, name, shape, dtype, stage
         assert torch.equal(recon.cpu(), ref_recon)
 
 
-@pytest.mark.parametrize("sub", [4, 8, 32, 128])
+@pytest.mark.parametrize("sub", [4, 8, 32, 64, 128])
 @pytest.mark.parametrize("regime", ["ties", "midpoints", "tiny", "huge", "mixed_scale"])
 def test_filtered_search_is_exact_on_adversarial_rows(device, regime, sub):
     """8-wide and wide groups go through the tensor-core filters; the exact re-evaluation must still
