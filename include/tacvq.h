@@ -74,8 +74,9 @@ TACVQ_API int tacvq_table_sqnorm(const uint16_t *tables_f16, float *out, int64_t
 /*
  * Diagnostic of the wide-group encode (d = 64, 128), whose approximate scores are tensor-core products
  * (tcgen05) kept in tensor memory: *count = how many times, on the current device since the library was
- * loaded, a block stopped waiting for those products and re-evaluated every pair of the stage instead
- * (codes stay exact either way).  Synchronises the device.  Expected value: 0.  No counterpart in the
+ * loaded, a block stopped waiting for those products and re-evaluated every pair of the stage instead,
+ * or stopped waiting for a table copy of the copy engine (TMA) and copied the table itself, plus the number
+ * of launches that could not get a tensor map for their tables at all (codes stay exact either way).  Synchronises the device.  Expected value: 0.  No counterpart in the
  * reference.
  */
 TACVQ_API int tacvq_encode_tensor_memory_timeouts(unsigned int *count);

@@ -27,6 +27,11 @@
 //
 // Reference statements: src/jointkv/closed_loop_vq.py:52-76 (search), :343-395 (stage recursion).
 
+#include <atomic>
+#include <cstring>
+
+#include <cuda.h>  // CUtensorMap and the driver's encoder signature; the entry point is looked up at run time
+
 #include "common.cuh"
 
 namespace tacvq {
@@ -654,7 +659,8 @@ encode_tc_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
 //     the library's |r|^2 order is made of, so the residual update also yields the next stage's partial
 //     sums, and a 16 KB exchange through shared memory finishes the norm.
 //   * With the residual out of shared memory there is room for two table buffers: the next stage's table
-//     arrives by cp.async while the current stage is searched.
+//     arrives while the current stage is searched, as two cp.async.bulk.tensor (TMA) copies of a
+//     [256 words x 64] box each, issued by one thread, which land in the swizzled panel order directly.
 //   * A thread keeps the candidate mask of its 64 words; there is no list.  Rows with a single candidate
 //     take it; otherwise every thread runs the exact chain for its own candidates, reading its row from
 //     tensor memory 32 columns at a time (warp-wide loads, so the loop is warp-uniform).
@@ -712,7 +718,8 @@ template <int DSUB, typename XT>
 __global__ void __launch_bounds__(kThreads, 1)
 encode_tm_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64_t sxt, const __half *__restrict__ tables,
                        const float *__restrict__ sqnorm_in, uint8_t *__restrict__ codes, void *__restrict__ recon,
-                       int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap, int vec_ok) {
+                       int recon_dtype, int B, int H, int T, int G, int S, int K, int64_t t0, int64_t T_cap, int vec_ok,
+                       const __grid_constant__ CUtensorMap table_map, int use_map) {
     using L = TmLargeLayout<DSUB>;
     constexpr int kChunks = DSUB / 8;   // 16-byte pieces per row
     constexpr int kOwn = DSUB / 32;     // pieces a thread owns per row: q, q + 4, ...
@@ -733,6 +740,7 @@ encode_tm_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
     int *big = reinterpret_cast<int *>(smem_raw + L::kMisc + 12);      // [2]: some residual element of stage parity p does not fit fp16
     int *tm_fail = reinterpret_cast<int *>(smem_raw + L::kMisc + 20);
     float *cc_max = reinterpret_cast<float *>(smem_raw + L::kMisc + 24);
+    const uint32_t tma_bar = (uint32_t)__cvta_generic_to_shared(smem_raw + L::kMisc + 32);  // counts the bytes of a table copy
     uint8_t *hist = smem_raw + L::kHist;
 
     const int hg = blockIdx.y;
@@ -744,11 +752,23 @@ encode_tm_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
     const uint32_t tile = blockIdx.x * kRows;
     const float inf = __int_as_float(0x7f800000);
 
-    // table of stage s -> buffer s & 1, zero rows past K
+    // Table of stage s -> buffer s & 1.  Normally one thread asks the copy engine (TMA) for the table's 64-column
+    // panels, which arrive in the 128-byte-swizzled order the tensor core reads and are counted by an
+    // mbarrier; rows past K then hold whatever follows the group's words (never chosen: their norm is +inf).
+    // Without a tensor map (use_map == 0), or if the wait for a copy ever ran out, all threads copy with cp.async.
+    auto request_table = [&](int s) {
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(tab_buf) + (uint32_t)(s & 1) * (uint32_t)L::kTabBytes;
+        const int first_word = (((h * S + s) * G + g)) * K;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tma_bar), "r"((uint32_t)L::kTabBytes) : "memory");
+#pragma unroll
+        for (int panel = 0; panel < DSUB / 64; ++panel)
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                         ::"r"(dst + panel * (kMaxWords * 128)), "l"(&table_map), "r"(panel * 64), "r"(first_word), "r"(tma_bar) : "memory");
+    };
     auto fetch_table = [&](int s) {
         const __half *src = tables + (((int64_t)h * S + s) * G + g) * (int64_t)K * DSUB;
         const uint32_t dst = (uint32_t)__cvta_generic_to_shared(tab_buf) + (uint32_t)(s & 1) * (uint32_t)L::kTabBytes;
-#pragma unroll
+#pragma unroll 1
         for (int idx = tid; idx < kMaxWords * kChunks; idx += kThreads) {
             const int k = idx / kChunks, c = idx % kChunks;
             const bool real = k < K;
@@ -757,7 +777,7 @@ encode_tm_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
                          "r"(real ? 16 : 0) : "memory");
         }
     };
-    fetch_table(0);
+    if (!use_map) fetch_table(0);
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -770,11 +790,13 @@ encode_tm_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
         *tm_fail = 0;
         *cc_max = 0.0f;
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_a) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tma_bar) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (use_map && tid == 32) request_table(0);
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     const uint32_t score_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(q * 64);
     const uint32_t res_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)kMaxWords;
@@ -822,10 +844,25 @@ encode_tm_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
         const int norm_k = tid - (kThreads - kMaxWords);
         float norm_v = inf;
         if (sqnorm_in != nullptr && norm_k >= 0 && norm_k < K) norm_v = sqnorm_in[(((int64_t)h * S + s) * G + g) * K + norm_k];
+        int late = 0;
+        if (use_map) {
+            int done = 0;
+            for (int spin = 0; spin < (1 << 22) && !done; ++spin)  // bounded wait for the table's bytes
+                asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.s32 %0, 1, 0, p;\n}"
+                             : "=r"(done) : "r"(tma_bar), "r"((uint32_t)(s & 1)) : "memory");
+            late = !done;
+        }
         asm volatile("cp.async.wait_all;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads the table and the fp16 rows
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();  // table s, fp16 rows, residual and partial sums settled
+        if (__syncthreads_or(late)) {  // never seen: copy the table the plain way (same bytes wherever both land)
+            if (tid == 0) atomicAdd(&g_tensor_memory_timeouts, 1u);
+            fetch_table(s);
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncthreads();
+        }
+        // table s, fp16 rows, residual and partial sums settled
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a0 = (uint32_t)__cvta_generic_to_shared(hi), b0 = (uint32_t)__cvta_generic_to_shared(tab);
@@ -839,7 +876,10 @@ encode_tm_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_a) : "memory");
             big[(s + 1) & 1] = 0;  // read two stages ago, raised by this stage's update
         }
-        if (s + 1 < S) fetch_table(s + 1);  // its buffer was last read by the previous stage's update
+        if (s + 1 < S) {  // its buffer was last read by the previous stage's update
+            if (!use_map) fetch_table(s + 1);
+            else if (tid == 32) request_table(s + 1);
+        }
         // |c|^2 per word (eight lanes per word when the caller gave none), largest by an integer atomic maximum
         {
             float top = 0.0f;
@@ -1070,6 +1110,42 @@ encode_tm_large_kernel(const XT *__restrict__ x, int64_t sxb, int64_t sxh, int64
 #define TACVQ_ENCODE_TENSOR_MEMORY 2  // 2: residual tile in tensor memory; 1: scores only; 0: mma.sync from registers
 #endif
 
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link against the driver
+typedef CUresult (*TensorMapEncoder)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                     const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TensorMapEncoder tensor_map_encoder() {
+    static const TensorMapEncoder found = [] {
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &status) != cudaSuccess ||
+            status != cudaDriverEntryPointSuccess)
+            entry = nullptr;
+        return reinterpret_cast<TensorMapEncoder>(entry);
+    }();
+    return found;
+}
+
+// Launches whose tables had at least 256 words but got no tensor map (no encoder in the driver, or it refused):
+// added to the count that tacvq_encode_tensor_memory_timeouts reports, so a silent cp.async-only run shows up.
+static std::atomic<unsigned int> g_table_map_failures{0};
+
+// The fp16 tables as a 2-D tensor [all words][d] read in boxes of 256 words x 64 elements with the 128-byte swizzle.
+// Returns 0 when no map could be made (the kernel then copies tables with cp.async).
+static int make_table_map(CUtensorMap *map, const void *tables, int64_t words, int d) {
+    memset(map, 0, sizeof(*map));
+    const TensorMapEncoder encode = tensor_map_encoder();
+    if (encode == nullptr || words < kMaxWords) return 0;
+    const cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)words};
+    const cuuint64_t strides[1] = {(cuuint64_t)d * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)kMaxWords};
+    const cuuint32_t steps[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(tables), dims, strides, box, steps,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 1 : 0;
+}
+
 template <int DSUB>
 static int launch_tc_large(const EncodeArgs &a) {
     // tcgen05 panels have 64-element rows, so the tensor-memory path carries d = 64 and 128
@@ -1093,8 +1169,20 @@ static int launch_tc_large(const EncodeArgs &a) {
         return launch_status();
     };
     if constexpr (TM2) {
-        if (a.x_dtype == TACVQ_F16) return launch(encode_tm_large_kernel<DSUB, __half>, (const __half *)a.x);
-        return launch(encode_tm_large_kernel<DSUB, float>, (const float *)a.x);
+        CUtensorMap table_map;
+        const int64_t words = (int64_t)a.H * a.S * a.G * a.K;
+        const int use_map = make_table_map(&table_map, a.tables, words, DSUB);
+        if (!use_map && words >= kMaxWords) g_table_map_failures.fetch_add(1u);
+        auto launch_tm = [&](auto kernel, auto *xp) -> int {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            kernel<<<grid, kThreads, smem, a.stream>>>(xp, a.sxb, a.sxh, a.sxt, (const __half *)a.tables, a.sqnorm, a.codes, a.recon,
+                                                       a.recon_dtype, a.B, a.H, a.T, a.G, a.S, a.K, a.t0, a.T_cap, vec_ok, table_map,
+                                                       use_map);
+            return launch_status();
+        };
+        if (a.x_dtype == TACVQ_F16) return launch_tm(encode_tm_large_kernel<DSUB, __half>, (const __half *)a.x);
+        return launch_tm(encode_tm_large_kernel<DSUB, float>, (const float *)a.x);
     } else {
         if (a.x_dtype == TACVQ_F16) return launch(encode_tc_large_kernel<DSUB, __half, TM>, (const __half *)a.x);
         return launch(encode_tc_large_kernel<DSUB, float, TM>, (const float *)a.x);
@@ -1115,7 +1203,9 @@ int encode_tc_large_launch(const EncodeArgs &a) {
 }
 
 int tensor_memory_timeouts(unsigned int *out) {
-    return (int)cudaMemcpyFromSymbol(out, g_tensor_memory_timeouts, sizeof(unsigned int));
+    const int st = (int)cudaMemcpyFromSymbol(out, g_tensor_memory_timeouts, sizeof(unsigned int));
+    if (st == 0) *out += g_table_map_failures.load();
+    return st;
 }
 
 }  // namespace tacvq
