@@ -313,7 +313,27 @@ def run_ours(args) -> dict:
             "value": round(4 * 8192 / (wide_ms * 1e-3), 1), "unit": "tokens/s (one tensor fp16 [4,8,8192,128], 1 group x 2 stages x 128, with reconstruction)",
             "ms_per_tensor": round(wide_ms, 4),
         }
-        del k_rows, v_rows, kcodes, vcodes, wide_tab, wide_codes
+        # one layer of the all-layer configuration: K and V fp16 [16,8,16384,128] through two full-width codebooks, codes only
+        big_gen = torch.Generator(device=device).manual_seed(8601)
+        big_k = torch.randn(16, KV_HEADS, 16384, DIM, generator=big_gen, device=device).half()
+        big_codes = torch.empty(16, KV_HEADS, 16384, 2, 1, dtype=torch.uint8, device=device)
+        wide_norms = ops.table_sqnorm(wide_tab)
+        for _ in range(2):
+            ops.encode(big_k, wide_tab, codes=big_codes, want_recon=False, table_sqnorm=wide_norms)
+        torch.cuda.synchronize(device)
+        start.record()
+        for _ in range(reps):
+            ops.encode(big_k, wide_tab, codes=big_codes, want_recon=False, table_sqnorm=wide_norms)
+            ops.encode(big_k, wide_tab, codes=big_codes, want_recon=False, table_sqnorm=wide_norms)
+        end.record()
+        torch.cuda.synchronize(device)
+        layer_ms = start.elapsed_time(end) / reps
+        encode["full_width_layer"] = {
+            "value": round(16 * 16384 / (layer_ms * 1e-3), 1),
+            "unit": "tokens/s (K and V of one layer, fp16 [16,8,16384,128] each, 1 group x 2 stages x 128, codes only; synthetic N(0,1) rows stand in for both)",
+            "ms_per_layer": round(layer_ms, 4), "tflops_of_distances": round(2 * 2 * 16 * KV_HEADS * 16384 * 2 * 256 * DIM / (layer_ms * 1e-3) / 1e12, 1),
+        }
+        del k_rows, v_rows, kcodes, vcodes, wide_tab, wide_codes, big_k, big_codes
         # the timed workload once more with the rotary step inside (codes of pre-rotary keys, theta 1e6)
         rope = ops.rope_table(CONTEXT, DIM, 1.0e6, device)
         for i in range(3):
