@@ -1,6 +1,8 @@
 // C ABI of libtacvq.so: argument validation on the host, then dispatch to the kernels.
 // Declarations and the per-function contract live in include/tacvq.h.
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace tacvq {
@@ -51,21 +53,26 @@ int attn_rotary_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *
 
 constexpr int kGenericMaxSplits = 64;
 
+// Per-device caches below are atomics: first calls from several host threads may race, and every
+// racer stores the same value.
 static int sm_count() {
-    static int cached[64] = {0};
+    static std::atomic<int> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
 }
 
-// the specialised scan keeps one 64 KB score table per (batch row, KV head) pair in scratch: beyond 1024
-// pairs (64 MB) the generic kernel serves the call instead
+// the specialised scan keeps a work prefix over at most 512 batch rows in shared memory and reads its
+// query rows and tables in 16-byte pieces; other calls are served by the generic kernel
 static bool gsrq_batch_ok(int B, int Hkv) { return B <= 512 && (int64_t)B * Hkv <= 1024; }
+static bool gsrq_aligned(const void *q, const void *ktab, const void *vtab) {
+    return (((uintptr_t)q | (uintptr_t)ktab | (uintptr_t)vtab) & 15) == 0;
+}
 
 static bool dtype_ok(int t) { return t == TACVQ_F16 || t == TACVQ_F32; }
 
@@ -94,18 +101,20 @@ constexpr size_t kStaticScratchBytes = (size_t)16 << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 static int static_scratch_for_current_device(void **ptr) {
-    static void *cached[64] = {nullptr};
+    // The address is valid for the life of the device's primary context; a cudaDeviceReset invalidates it
+    // (and everything else this library has set up on that device).
+    static std::atomic<void *> cached[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return TACVQ_ERR_DEVICE;
-    if (cached[dev] == nullptr) {
-        void *p = nullptr;
+    void *p = cached[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         e = cudaGetSymbolAddress(&p, g_static_scratch);
         if (e != cudaSuccess) return (int)e;
-        cached[dev] = p;
+        cached[dev].store(p, std::memory_order_release);
     }
-    *ptr = cached[dev];
+    *ptr = p;
     return TACVQ_OK;
 }
 
@@ -231,10 +240,11 @@ int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_
         return TACVQ_ERR_WORKSPACE;
     if ((((uintptr_t)kcodes | (uintptr_t)vcodes) & 15) != 0) return TACVQ_ERR_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
-    if (attn_gsrq_supported(Hq, Hkv, D, G, S, K) && gsrq_batch_ok(B, Hkv)) {
-        return attn_gsrq_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
-                                  (const __half *)vtab_f16, seq_start, seq_end, workspace, (__half *)out_f16, state_out,
-                                  B, Hq, Hkv, T_cap, sm_count(), s);
+    if (attn_gsrq_supported(Hq, Hkv, D, G, S, K) && gsrq_batch_ok(B, Hkv) && gsrq_aligned(q_f16, ktab_f16, vtab_f16)) {
+        const int fast = attn_gsrq_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
+                                            (const __half *)vtab_f16, seq_start, seq_end, workspace, (__half *)out_f16,
+                                            state_out, B, Hq, Hkv, T_cap, sm_count(), s);
+        if (fast != TACVQ_ERR_UNSUPPORTED) return fast;  // sizes beyond the specialised scan: the generic kernel below
     }
     int splits = attn_generic_splits(B, Hkv, T_cap, sm_count());
     if (attn_fullwidth_supported(Hq, Hkv, D, G, S, K) && (T_cap + 8191) / 8192 <= kGenericMaxSplits) {
@@ -345,10 +355,11 @@ int tacvq_decode_step(const uint16_t *q_f16, const void *k_rows, const void *v_r
                                                      (const __half *)vtab_f16, kcodes, vcodes, seq_start, seq_end, (int)new_start,
                                                      (int)new_end, B, Hkv, T_new, D, G, S, K, length, T_cap, s);
             if (pro == TACVQ_OK) {
-                if (attn_gsrq_supported(Hq, Hkv, D, G, S, K) && gsrq_batch_ok(B, Hkv)) {
-                    return attn_gsrq_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
-                                              (const __half *)vtab_f16, seq_start, seq_end, workspace, (__half *)out_f16,
-                                              state_out, B, Hq, Hkv, T_cap, sm_count(), s, true);
+                if (attn_gsrq_supported(Hq, Hkv, D, G, S, K) && gsrq_batch_ok(B, Hkv) && gsrq_aligned(q_f16, ktab_f16, vtab_f16)) {
+                    const int fast = attn_gsrq_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
+                                                        (const __half *)vtab_f16, seq_start, seq_end, workspace,
+                                                        (__half *)out_f16, state_out, B, Hq, Hkv, T_cap, sm_count(), s, true);
+                    if (fast != TACVQ_ERR_UNSUPPORTED) return fast;
                 }
                 return tacvq_attn_decode(q_f16, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, workspace,
                                          workspace_bytes, out_f16, state_out, B, Hq, Hkv, D, G, S, K, T_cap, stream);

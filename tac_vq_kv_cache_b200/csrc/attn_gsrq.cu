@@ -9,23 +9,44 @@
 //           as four 13-bit fixed-point fields, so four heads cost one load and the sums are
 //           exact integer adds (two 32-bit adds add four heads).            32 x 8 B = 256 B
 //   values  one 16-byte fp16 codeword per V code, fetched once and shared by the 4 heads
-//           through a tensor-core product P^T.V (mma.sync m16n8k16).        32 x 16 B = 512 B
-// 768 B / 128 B/clk = 6 clocks per (token, KV head) per SM is the floor of this design.
+//           through a tensor-core product P^T.V (mma.sync m16n8k8).         32 x 16 B = 512 B
+// 768 B / 128 B/clk = 6 clocks per (token, KV head) per SM is the floor of this design; everything
+// else that touches the shared-memory pipe (code staging, probabilities, shuffles) is kept small:
+//   K codes  two 16-byte global loads per token (lane = token), no staging
+//   V codes  two 16-byte cp.async per token into a 1 KB buffer per warp, read back by two
+//            ldmatrix.x4.trans, which hand every lane the codes of exactly the (token pair, group
+//            pair) its A fragment covers - no byte shuffling in registers
+//   softmax  the running reference is only re-derived (20 shuffles) when some lane's score exceeds
+//            it by more than 8 octaves (one vote per tile); otherwise a tile costs no shuffle
 //
 // Conflict-free addressing for arbitrary codes.  Both tables are laid out so that the shared-memory
 // bank is decided by the code SLOT (stage, group), never by the code value, and at every step the
 // lanes that are served together work on different slots:
 //   score table   entry(code, slot) at code*256 + slot*8; lane = token; at step i lane l handles
 //                 slot i XOR perm(l), so the 16 lanes of a half warp hit 16 different bank pairs.
-//   value table   entry(code, slot) at code*512 + pos(slot)*16; the 8 lanes of a quarter warp
-//                 fetch 8 different slots.  The lanes that share an A-fragment row visit their two
-//                 groups in opposite order; the product keeps them apart by giving the 8 columns
-//                 of the B operand to (4 heads) x (2 visiting orders).
+//   value table   entry(code, slot) at code*512 + pos(slot)*16, pos = (g/4)*8 + stage*4 + g%4; the 8
+//                 lanes of a quarter warp (two group pairs x four token pairs) fetch 8 different
+//                 slots: the four token pairs visit (stage, group of the pair) in four different
+//                 orders.  Stage order is flipped by the cp.async that lands the codes (odd token
+//                 pairs swap their stage halves), group order by the byte selector; lanes whose order
+//                 swaps the two A-fragment rows are kept apart in the product by giving the 8
+//                 columns of the B operand to (4 heads) x (2 visiting orders).
 //
-// Work split.  A persistent grid (one block per SM) walks the flattened (KV head, batch row, 32-token
-// tile) space; every block gets an equal share of tiles, rebuilds the score table when it enters a new
-// (batch row, KV head) pair and writes one partial softmax state per pair it touches.  A second
-// kernel merges the partials of each pair (log-sum-exp) and writes fp16 output and/or fp32 state.
+// Two launches per call, chained as programmatic dependents (each lets its successor be scheduled at
+// once; the successor waits for it before touching its results):
+//   prepare  one block per (batch row, KV head, stage): the score table of the pair (q . codeword for
+//            4096 codewords x 4 heads straight from the fp16 K tables, quantised to 13 bits), written to
+//            scratch in the order the scan's shared memory wants.  A build costs about 5 us of a 512-thread
+//            block per stage (64 values per thread, quarter-rate conversions); building inside the scan
+//            was measured twice and repeats that for every block that enters a pair (3.3 per pair).
+//   scan     a persistent grid (one block per SM) walks the flattened (KV head, batch row, 32-token
+//            tile) space; every block gets an equal share of work units.  When it enters a new (batch
+//            row, KV head) pair it copies that pair's score table (64 KB, flat) and, when the head
+//            changed, gathers the head's V codewords from the fp16 V tables into their bank-striped
+//            order (for its first pair before it waits for the prepare grid).  It writes one partial
+//            softmax state per pair it touches, then marks it; the block that finds every partial of a
+//            pair marked merges them (log-sum-exp) and writes fp16 output and/or fp32 state.  A pair
+//            that lies inside one block's share is written directly.
 //
 // Semantics replaced: experiments_followup_mistral/evaluate_mistral_longbench.py:112-122 and the
 // decoded window of :53-70 (no rotary step).  Differences from that dense path, all inside the
@@ -33,7 +54,7 @@
 // key to fp16 first), entries are quantised to 13 bits of the widest slot range of their head,
 // probabilities enter the tensor-core product as fp16, and the two V stages are added in fp16.
 
-#include <mma.h>
+#include <atomic>
 
 #include "common.cuh"
 
@@ -49,35 +70,38 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kDim = 128, kGroups = 16, kStages = 2, kSub = 8, kRep = 4, kSlots = 32, kWords = 256;
 constexpr int kTile = 32;          // tokens per warp tile
 constexpr int kMaxBatch = 512;
-[[maybe_unused]] constexpr int kBulkPiece = 16384;     // bytes per bulk copy instruction
-#ifndef TACVQ_FUSED_MERGE
-#define TACVQ_FUSED_MERGE 0  // 1: the last scan block of a pair merges it (no merge launch); measured slower
-#endif
-#ifndef TACVQ_BULK_TABLES
-#define TACVQ_BULK_TABLES 0  // 1: table copies as cp.async.bulk + mbarrier (measured 1 % slower than 16-byte cp.async by all threads)
-#endif
-#ifndef TACVQ_PDL
-#define TACVQ_PDL 1  // scan and merge are launched as programmatic dependents of their predecessor
-#endif
 #ifndef TACVQ_ITEM_COST
-#define TACVQ_ITEM_COST 32
+#define TACVQ_ITEM_COST 64
 #endif
+#ifndef TACVQ_GSRQ_UNROLL_K
+#define TACVQ_GSRQ_UNROLL_K 2  // 1: the two stages of the score phase as a rolled loop, 2: unrolled
+#endif
+#ifndef TACVQ_GSRQ_UNROLL_V
+#define TACVQ_GSRQ_UNROLL_V 1  // 1: the two 16-token halves of the value phase as a rolled loop, 2: unrolled
+#endif
+#ifndef TACVQ_GSRQ_EARLY_K
+#define TACVQ_GSRQ_EARLY_K 0  // 1: the next tile's K codes are requested before the score phase (8 more registers live)
+#endif
+#ifndef TACVQ_GSRQ_LAZY_MAX
+#define TACVQ_GSRQ_LAZY_MAX 1  // 0: every tile reduces its maximum over the warp (20 shuffles)
+#endif
+constexpr int kUnrollScore = TACVQ_GSRQ_UNROLL_K, kUnrollValue = TACVQ_GSRQ_UNROLL_V;
 constexpr int kItemCost = TACVQ_ITEM_COST;         // fixed cost of starting a (row, head) pair in a block, in 32-token tiles
 constexpr int kMaxScanBlocks = 256;  // persistent grid size (one block per SM) never exceeds this
 constexpr int kStateWidth = kDim + 2;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr float kRescaleGap = 8.0f;  // log2 units a tile may exceed the running reference before rescaling
+constexpr float kRescaleGap = 8.0f;  // log2 units a score may exceed the running reference before rescaling
 constexpr int kEntryMax = 8191;      // 13-bit fields: 8 of them sum below 2^16
 
 // shared-memory carve-up (bytes)
 constexpr int kLutBytes = kWords * kSlots * 8;              // 65536
 constexpr int kVtabBytes = kWords * kSlots * 16;            // 131072
-constexpr int kVBlock = 144;                                // 32 words + 16 B pad: staggers the banks of odd/even tokens
-constexpr int kVStage = 8 * kVBlock;                        // 1152
-constexpr int kStagePerWarp = kVStage + 256;                // transposed V codes + fp16 probabilities
-constexpr int kStageBytes = kWarps * kStagePerWarp;         // 20480 (also min/max scratch of the table build)
-constexpr int kPrefixBytes = (kMaxBatch + 1) * 4 + 12;      // 2064
+constexpr int kVCodeBytes = kTile * 32;                     // one tile of V codes per warp
+constexpr int kProbStride = 72;                             // bytes per head of the fp16 probabilities: 64 + 8, so the four heads' reads hit different banks
+constexpr int kStagePerWarp = kVCodeBytes + 4 * kProbStride + 32;  // + fp16 probabilities [4 heads][32 tokens], 64-byte multiple
+constexpr int kStageBytes = kWarps * kStagePerWarp;         // 20480 at 16 warps (also scratch of the table build)
+constexpr int kPrefixBytes = (kMaxBatch + 8) * 4 + 12 * 4;
 constexpr int kSmemBytes = kLutBytes + kVtabBytes + kStageBytes + kPrefixBytes;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -97,11 +121,19 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
 __device__ __forceinline__ void sts16(uint32_t addr, unsigned short v) {
     asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
+}
+// four 8x8 b16 matrices, transposed: lane (r8 = lane/4, kq = lane%4) receives of matrix j the elements
+// [row 2kq][column r8] (low half) and [row 2kq+1][column r8] (high half); lane l supplies the address of
+// row l%8 of matrix l/8
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&d)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(addr));
 }
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t d;
@@ -133,13 +165,6 @@ __device__ __forceinline__ float fast_exp2(float x) {  // 2^x, ex2.approx: 2^-in
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
 __device__ __forceinline__ void mma1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
     asm volatile(
         "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
@@ -160,101 +185,75 @@ __device__ __forceinline__ long long block_first_tile(long long total, int block
     return total * block / blocks;
 }
 
-// ------------------------------------------------------------------------------------------------
-// prepare kernel: everything that depends only on (query, tables), laid out for shared memory
-// ------------------------------------------------------------------------------------------------
-//   blocks [0, 2*B*Hkv)      one residual stage of the score table of pair p = h*B + b:
-//                            lut_g[p][code][slot] (8 bytes: four 13-bit fields) and
-//                            scale_g[p][stage] = (step_r * log2 e, offset_r * log2 e), r = 0..3;
-//                            each stage has its own step, so the finer second stage keeps its precision
-//   blocks [2*B*Hkv, +Hkv)   value codewords of head h in the bank-striped order the scan uses
-// A lane always works on group lane % 16, so the per-group value range is a reduction over warps
-// and the table is written 128 contiguous bytes at a time.
+// position of slot (stage s, group g) inside a code's 512-byte row of the value table
+__device__ __forceinline__ int value_pos(int s, int g) { return (g >> 2) * 8 + s * 4 + (g & 3); }
 
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------------
+// prepare kernel: block (pair p = h*B + b, stage) builds one stage of the pair's score table
+// ------------------------------------------------------------------------------------------------
+//   lut_g[p][code][slot]   8 bytes: four 13-bit fields, field r = round((q_r . word - min_slot_r) / step_stage_r)
+//   scale_g[p][stage*8+r]  step_stage_r * log2 e;  [stage*8+4+r] = sum over the stage's slots of min_slot_r * log2 e
+// A lane always works on group lane % 16 and on one of the two codes its warp covers per round, so the
+// 16 lanes of a half warp read sixteen 4 KB-strided table rows in 32-byte sectors that the other half
+// warp completes, and write 128 contiguous bytes.  Each stage has its own step, so the finer second
+// stage keeps its precision.
 constexpr int kPrepThreads = 512;
 constexpr int kPrepWarps = kPrepThreads / 32;
-constexpr int kPrepCodes = kWords / (2 * kPrepWarps);  // codes per thread (a warp covers 2 codes x 16 groups per round)
-constexpr int kPrepVBlocks = 8;                          // blocks that reorder one head's value table
-constexpr int kPrepSlotStride = kWords * 16 + 16;      // padded so that lanes (= groups) read different banks
-constexpr int kPrepSmemBytes = kGroups * kPrepSlotStride + kRep * kDim * 4 + kPrepWarps * 32 * 8 * 4;
+constexpr int kPrepCodes = kWords / (2 * kPrepWarps);  // codes per thread
 
 __global__ void __launch_bounds__(kPrepThreads)
-attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict__ ktab,
-                         const __half *__restrict__ vtab, uint2 *__restrict__ lut_g, uint4 *__restrict__ vperm_g,
-                         float *__restrict__ scale_g, int *__restrict__ tickets, const int32_t *__restrict__ seq_start,
-                         const int32_t *__restrict__ seq_end, __half *__restrict__ out, float *__restrict__ state_out,
-                         int B, int Hkv, int T_cap, int chained) {
-    // chained != 0: launched as a programmatic dependent of a kernel that is still writing the visible
-    // ranges and the newest codes (one decode step).  Nothing here reads those (the ranges of a decode step
-    // are never empty, so the empty-row case below is skipped); before it ends, every thread waits for
-    // that kernel, so that the scan, which waits for this grid, also sees that kernel's results.
+attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict__ ktab, const __half *__restrict__ vtab,
+                         uint2 *__restrict__ lut_g, float *__restrict__ scale_g, uint4 *__restrict__ vperm_g, int B, int Hkv) {
+    __shared__ float red[kPrepWarps * 8 * 32];  // [warp][min x4, max x4][lane]
+    __shared__ float red2[8 * 32];
+    launch_dependents();  // the scan may be scheduled as soon as SMs free up; it waits for this grid itself
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int pairs = B * Hkv;
-    if ((int)blockIdx.x >= 2 * pairs) {
-        const int h = (blockIdx.x - 2 * pairs) / kPrepVBlocks, part = (blockIdx.x - 2 * pairs) % kPrepVBlocks;
-        constexpr int kPer = kWords * kSlots / kPrepVBlocks;
-#pragma unroll
-        for (int j = part * kPer + tid; j < (part + 1) * kPer; j += kPrepThreads) {
-            const int code = j >> 5, pos = j & 31;
-            const int bq = pos & 7, u = pos >> 3;
-            const int s = bq >> 2, gh = (bq >> 1) & 1;
-            const int g = (bq & 1) | (u << 1) | (gh << 3);
-            const __half *src = vtab + ((((size_t)h * kStages + s) * kGroups + g) * kWords + code) * kSub;
-            vperm_g[(size_t)h * (kWords * kSlots) + j] = __ldg(reinterpret_cast<const uint4 *>(src));
-        }
-        if (chained) wait_for_previous_kernel();
-        return;
-    }
-    extern __shared__ __align__(128) unsigned char psm[];
-    unsigned char *ktab_s = psm;                                                   // [group][256 words x 16 B + pad]
-    float *q_s = reinterpret_cast<float *>(psm + kGroups * kPrepSlotStride);        // [4][128]
-    float *red = q_s + kRep * kDim;                                                 // [warp][lane][min x4, max x4]
     const int pair = blockIdx.x >> 1, stage = blockIdx.x & 1;
     const int h = pair / B, b = pair % B;
     const int Hq = Hkv * kRep;
-    if (stage == 0) {
-        if (tid == 0) tickets[pair] = 0;  // the scan counts finished blocks per pair from zero
-        if (!chained && row_tokens(seq_start, seq_end, b, T_cap) == 0) {
-            // an empty range never reaches the scan: its result is defined here (out 0, m -inf, l 0, acc 0)
-            for (int o = tid; o < kRep * kDim; o += kPrepThreads) {
-                const size_t row = (size_t)b * Hq + h * kRep + (o >> 7);
-                if (out) out[row * kDim + (o & 127)] = __float2half_rn(0.0f);
-                if (state_out) {
-                    state_out[row * kStateWidth + 2 + (o & 127)] = 0.0f;
-                    if ((o & 127) == 0) {
-                        state_out[row * kStateWidth] = -INFINITY;
-                        state_out[row * kStateWidth + 1] = 0.0f;
-                    }
-                }
-            }
+    const int g = lane & 15, half = lane >> 4;
+    // inputs of this kernel (q, K and V tables) are not produced by the kernels of this chain: read at once
+    // this block's share of the V codewords in the scan's bank-striped order: entry (head, code, pos) <- 16 bytes
+    constexpr int kPermPerThread = 8;
+    const int perm_total = Hkv * kWords * kSlots;
+    const int perm_per_block = (perm_total + (int)gridDim.x - 1) / (int)gridDim.x;
+    uint4 perm[kPermPerThread];
+#pragma unroll
+    for (int i = 0; i < kPermPerThread; ++i) {
+        const int local = tid + i * kPrepThreads;
+        const int e = blockIdx.x * perm_per_block + local;
+        perm[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (local < perm_per_block && e < perm_total) {
+            const int hh = e >> 13, code = (e >> 5) & 255, pos = e & 31;
+            const int s = (pos >> 2) & 1, gg = ((pos >> 3) << 2) | (pos & 3);
+            perm[i] = __ldg(reinterpret_cast<const uint4 *>(vtab + ((((size_t)hh * kStages + s) * kGroups + gg) * kWords + code) * kSub));
         }
     }
-    {   // one stage of the head's K tables is a contiguous 64 KB block [group][word]: coalesced copy, padded rows
-        const unsigned char *src = reinterpret_cast<const unsigned char *>(
-            ktab + ((size_t)h * kStages + stage) * kGroups * kWords * kSub);
-        for (int u = tid; u < kGroups * kWords; u += kPrepThreads)
-            cp_async16(smem_u32(ktab_s) + (u >> 8) * kPrepSlotStride + (u & 255) * 16, src + (size_t)u * 16);
-    }
-    for (int i = tid; i < kRep * kDim; i += kPrepThreads)
-        q_s[i] = __half2float(q[((size_t)b * Hq + h * kRep + (i >> 7)) * kDim + (i & 127)]);
-    cp_async_wait_all();
-    __syncthreads();
-    const int g = lane & 15, half = lane >> 4;  // lane = (group, which of the warp's two codes per round)
+    const uint4 *tab = reinterpret_cast<const uint4 *>(ktab + (((size_t)h * kStages + stage) * kGroups + g) * kWords * kSub);
+    uint4 raw[kPrepCodes];
+#pragma unroll
+    for (int c = 0; c < kPrepCodes; ++c) raw[c] = __ldg(tab + warp * 2 + half + 2 * kPrepWarps * c);
     float qv[kRep][kSub];
 #pragma unroll
-    for (int r = 0; r < kRep; ++r)
+    for (int r = 0; r < kRep; ++r) {
+        const uint4 qr = __ldg(reinterpret_cast<const uint4 *>(q + ((size_t)b * Hq + h * kRep + r) * kDim + g * kSub));
+        const __half2 *hp = reinterpret_cast<const __half2 *>(&qr);
 #pragma unroll
-        for (int i = 0; i < kSub; ++i) qv[r][i] = q_s[r * kDim + g * kSub + i];
-    const uint32_t tab_u32 = smem_u32(ktab_s) + g * kPrepSlotStride;
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(hp[i]);
+            qv[r][2 * i] = f.x;
+            qv[r][2 * i + 1] = f.y;
+        }
+    }
     float val[kPrepCodes][kRep];
     float mn[kRep], mx[kRep];
 #pragma unroll
     for (int r = 0; r < kRep; ++r) { mn[r] = INFINITY; mx[r] = -INFINITY; }
 #pragma unroll
     for (int c = 0; c < kPrepCodes; ++c) {
-        const int code = warp * 2 + half + 2 * kPrepWarps * c;
-        const uint4 raw = lds128(tab_u32 + code * 16);
-        const __half2 *hp = reinterpret_cast<const __half2 *>(&raw);
+        const __half2 *hp = reinterpret_cast<const __half2 *>(&raw[c]);
         float w[kSub];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -272,24 +271,30 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
             mx[r] = fmaxf(mx[r], dot);
         }
     }
+    // range of every (group, head) over the 256 codes: over warps through shared memory in two levels
+    // (8 x 32 threads fold the warps), then over the two lane halves and, for the common step, over the
+    // 16 groups by shuffles
 #pragma unroll
     for (int r = 0; r < kRep; ++r) {
         red[(warp * 8 + r) * 32 + lane] = mn[r];       // lane-major: conflict-free writes and reads
         red[(warp * 8 + 4 + r) * 32 + lane] = mx[r];
     }
     __syncthreads();
-#pragma unroll
-    for (int r = 0; r < kRep; ++r) { mn[r] = INFINITY; mx[r] = -INFINITY; }
-    for (int w = 0; w < kPrepWarps; ++w) {
-#pragma unroll
-        for (int r = 0; r < kRep; ++r) {
-            mn[r] = fminf(mn[r], red[(w * 8 + r) * 32 + lane]);
-            mx[r] = fmaxf(mx[r], red[(w * 8 + 4 + r) * 32 + lane]);
+    if (tid < 8 * 32) {
+        const int v = tid >> 5;
+        float t = red[v * 32 + lane];
+        for (int w = 1; w < kPrepWarps; ++w) {
+            const float o = red[(w * 8 + v) * 32 + lane];
+            t = v < 4 ? fminf(t, o) : fmaxf(t, o);
         }
+        red2[v * 32 + lane] = t;
     }
-    float inv_step[kRep];
+    __syncthreads();
+    float inv_step[kRep], scale_step[kRep], scale_offs[kRep];
 #pragma unroll
     for (int r = 0; r < kRep; ++r) {
+        mn[r] = red2[r * 32 + lane];
+        mx[r] = red2[(4 + r) * 32 + lane];
         // the two lane halves hold the two codes of a round for the same group: fold them first
         mn[r] = fminf(mn[r], __shfl_xor_sync(0xffffffffu, mn[r], 16));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
@@ -302,59 +307,98 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
         }
         const float step = range > 0.0f ? range / (float)kEntryMax : 1.0f;
         inv_step[r] = 1.0f / step;
-        if (tid == 0) {
-            scale_g[((size_t)pair * kStages + stage) * 8 + r] = step * kLog2e;
-            scale_g[((size_t)pair * kStages + stage) * 8 + 4 + r] = offs * kLog2e;
-        }
+        scale_step[r] = step * kLog2e;
+        scale_offs[r] = offs * kLog2e;
     }
+    uint32_t packed[kPrepCodes][2];
+#pragma unroll
+    for (int c = 0; c < kPrepCodes; ++c) {
+        uint32_t e[kRep];
+#pragma unroll
+        for (int r = 0; r < kRep; ++r) {
+            // round to nearest by adding 2^23 (full-rate add and mask instead of a quarter-rate conversion);
+            // the argument is in [0, 8191.x]
+            const float t = fmaf(val[c][r] - mn[r], inv_step[r], 8388608.0f);
+            e[r] = min((uint32_t)kEntryMax, __float_as_uint(t) & 0x3fffu);
+        }
+        packed[c][0] = e[0] | (e[1] << 16);
+        packed[c][1] = e[2] | (e[3] << 16);
+    }
+    // The scratch written below is read by the scan of the call before this one, which may still be
+    // running when this grid starts: wait for everything before this grid, then write.
+    wait_for_previous_kernel();
 #pragma unroll
     for (int c = 0; c < kPrepCodes; ++c) {
         const int code = warp * 2 + half + 2 * kPrepWarps * c;
-        uint32_t e[kRep];
+        lut_g[((size_t)pair * kWords + code) * kSlots + stage * kGroups + g] = make_uint2(packed[c][0], packed[c][1]);
+    }
+    if (tid == 0) {
 #pragma unroll
-        for (int r = 0; r < kRep; ++r)
-            e[r] = min((uint32_t)kEntryMax, __float2uint_rn((val[c][r] - mn[r]) * inv_step[r]));
-        uint2 packed;
-        packed.x = e[0] | (e[1] << 16);
-        packed.y = e[2] | (e[3] << 16);
-        lut_g[((size_t)pair * kWords + code) * kSlots + stage * kGroups + g] = packed;
+        for (int r = 0; r < kRep; ++r) {
+            scale_g[((size_t)pair * kStages + stage) * 8 + r] = scale_step[r];
+            scale_g[((size_t)pair * kStages + stage) * 8 + 4 + r] = scale_offs[r];
+        }
     }
-    if (chained) wait_for_previous_kernel();
+#pragma unroll
+    for (int i = 0; i < kPermPerThread; ++i) {
+        const int local = tid + i * kPrepThreads;
+        const int e = blockIdx.x * perm_per_block + local;
+        if (local < perm_per_block && e < perm_total) vperm_g[e] = perm[i];
+    }
+    for (int local = tid + kPermPerThread * kPrepThreads; local < perm_per_block; local += kPrepThreads) {  // tiny batches only
+        const int e = blockIdx.x * perm_per_block + local;
+        if (e < perm_total) {
+            const int hh = e >> 13, code = (e >> 5) & 255, pos = e & 31;
+            const int s = (pos >> 2) & 1, gg = ((pos >> 3) << 2) | (pos & 3);
+            vperm_g[e] = __ldg(reinterpret_cast<const uint4 *>(vtab + ((((size_t)hh * kStages + s) * kGroups + gg) * kWords + code) * kSub));
+        }
+    }
 }
 
-// Scan blocks whose share of work units [start_c, start_{c+1}) gives them at least one tile of the pair
-// occupying units [pair_first, pair_end): the partial states that exist for this pair.  Index = pair + c.
-__device__ int list_pair_parts(int pair_first, int pair_end, int total_units, int blocks, int pair, int *parts) {
-    const int c_lo = (int)(((long long)(pair_first + 1) * blocks - 1) / total_units);
-    const int c_hi = (int)(((long long)pair_end * blocks - 1) / total_units);
-    int n = 0;
-    long long s0 = block_first_tile(total_units, c_lo, blocks);
-    for (int c = c_lo; c <= c_hi; ++c) {
-        const long long s1 = block_first_tile(total_units, c + 1, blocks);
-        const long long lo = s0 > pair_first ? s0 : pair_first, hi = s1 < pair_end ? s1 : pair_end;
-        const long long t_lo = lo - pair_first - kItemCost, t_hi = hi - pair_first - kItemCost;
-        if (hi > lo && t_hi > (t_lo > 0 ? t_lo : 0) && n < kMaxScanBlocks) parts[n++] = pair + c;
-        s0 = s1;
-    }
-    return n;
+// ------------------------------------------------------------------------------------------------
+// partial states of a pair: who writes them, how they are merged
+// ------------------------------------------------------------------------------------------------
+// Block c owns work units [total*c/blocks, total*(c+1)/blocks); unit u therefore lies in block
+// ((u+1)*blocks - 1) / total.  The blocks that scan tiles of a pair are exactly those from the owner of the
+// pair's first tile unit to the owner of its last unit; block c stores its partial state at index pair + c.
+__device__ __forceinline__ int block_of_unit(int unit, int total_units, int blocks) {
+    return (int)(((long long)(unit + 1) * blocks - 1) / total_units);
 }
 
-// log-sum-exp merge of the listed partial states of one pair by a 512-thread block (4 heads x 128 channels)
-__device__ void merge_pair_parts(const float *part, const int *parts, int n_parts, int b, int h, int Hkv,
-                                 __half *out, float *state_out) {
+// log-sum-exp merge of n_parts consecutive partial states by the whole block (4 heads x 128 channels); the
+// states are fetched eight at a time in one round trip
+__device__ void merge_pair_parts(const float *part, int first, int n_parts, int b, int h, int Hkv, __half *out,
+                                 float *state_out) {
     const int Hq = Hkv * kRep;
     for (int o = threadIdx.x; o < kRep * kDim; o += blockDim.x) {
         const int r = o >> 7, dim = o & 127;
-        float top = -INFINITY;
-        for (int i = 0; i < n_parts; ++i) top = fmaxf(top, __ldcg(part + ((size_t)parts[i] * kRep + r) * kStateWidth));
-        float lsum = 0.0f, asum = 0.0f;
-        for (int i = 0; i < n_parts; ++i) {
-            const float *st = part + ((size_t)parts[i] * kRep + r) * kStateWidth;
-            const float mc = __ldcg(st);
-            if (mc == -INFINITY) continue;
-            const float sc = __expf(mc - top);
-            lsum += sc * __ldcg(st + 1);
-            asum += sc * __ldcg(st + 2 + dim);
+        float top = -INFINITY, lsum = 0.0f, asum = 0.0f;
+        for (int i0 = 0; i0 < n_parts; i0 += 8) {
+            float mc[8], lc[8], ac[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float *st = part + ((size_t)(first + min(i0 + i, n_parts - 1)) * kRep + r) * kStateWidth;
+                mc[i] = __ldcg(st);
+                lc[i] = __ldcg(st + 1);
+                ac[i] = __ldcg(st + 2 + dim);
+            }
+            float ntop = top;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (i0 + i < n_parts) ntop = fmaxf(ntop, mc[i]);
+            if (ntop == -INFINITY) continue;
+            const float f = __expf(top - ntop);  // 0 while nothing has been added yet
+            lsum *= f;
+            asum *= f;
+            top = ntop;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (i0 + i < n_parts && mc[i] != -INFINITY) {
+                    const float sc = __expf(mc[i] - top);
+                    lsum += sc * lc[i];
+                    asum += sc * ac[i];
+                }
+            }
         }
         const size_t row = (size_t)b * Hq + h * kRep + r;
         if (out) out[row * kDim + dim] = __float2half_rn(lsum > 0.0f ? asum / lsum : 0.0f);
@@ -369,53 +413,95 @@ __device__ void merge_pair_parts(const float *part, const int *parts, int n_part
     }
 }
 
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // ------------------------------------------------------------------------------------------------
 // scan kernel
 // ------------------------------------------------------------------------------------------------
+#ifdef TACVQ_GSRQ_TRACE
+__device__ unsigned long long g_trace[256][16];
+__device__ __forceinline__ void trace(int slot) {
+    if (threadIdx.x == 0 && slot < 16) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_trace[blockIdx.x][slot] = t;
+    }
+}
+#define TRACE(slot) trace(slot)
+#else
+#define TRACE(slot)
+#endif
 
 __global__ void __launch_bounds__(kThreads, 1)
-attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
-                      const uint8_t *__restrict__ vcodes, const uint2 *__restrict__ lut_g,
-                      const uint4 *__restrict__ vperm_g, const float *__restrict__ scale_g,
-                      const int32_t *__restrict__ seq_start, const int32_t *__restrict__ seq_end,
-                      float *__restrict__ part, int *__restrict__ tickets, __half *__restrict__ out,
-                      float *__restrict__ state_out, int B, int Hkv, int T_cap) {
+attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes, const uint8_t *__restrict__ vcodes,
+                      const uint2 *__restrict__ lut_g, const float *__restrict__ scale_g,
+                      const uint4 *__restrict__ vperm_g, const int32_t *__restrict__ seq_start,
+                      const int32_t *__restrict__ seq_end, float *__restrict__ part, unsigned long long *__restrict__ marks,
+                      __half *__restrict__ out, float *__restrict__ state_out, int B, int Hkv, int T_cap,
+                      unsigned long long epoch) {
     extern __shared__ __align__(128) unsigned char smem[];
-#if TACVQ_FUSED_MERGE
-    __shared__ int n_parts_s;
-    __shared__ int parts_s[kMaxScanBlocks];
-#endif
     unsigned char *lut_s = smem;
     unsigned char *vtab_s = smem + kLutBytes;
     unsigned char *stage_s = vtab_s + kVtabBytes;
     int *prefix_s = reinterpret_cast<int *>(stage_s + kStageBytes);
+    float *scale_s = reinterpret_cast<float *>(prefix_s + kMaxBatch + 8);  // 16-byte aligned: 12 floats
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int Hq = Hkv * kRep;
 
+    TRACE(0);
+#ifdef TACVQ_GSRQ_TRACE
+    int trace_item = 0;
+    if (tid == 0) for (int i = 1; i < 16; ++i) g_trace[blockIdx.x][i] = 0;
+#endif
     // ---- work prefix over batch rows: a non-empty row costs its tiles plus kItemCost units (table
     //      copies, pipeline fill and drain, merge), so blocks that enter more pairs get fewer tiles ------
-    if (warp == 0) {
-        int running = 0;
-        for (int b0 = 0; b0 < B; b0 += 32) {
-            const int b = b0 + lane;
-            int tiles = (b < B) ? (row_tokens(seq_start, seq_end, b, T_cap) + kTile - 1) / kTile : 0;
-            if (tiles > 0) tiles += kItemCost;
-            int incl = tiles;
+    auto work_prefix = [&]() {
+        if (warp == 0) {
+            int running = 0;
+            for (int b0 = 0; b0 < B; b0 += 32) {
+                const int b = b0 + lane;
+                int tiles = (b < B) ? (row_tokens(seq_start, seq_end, b, T_cap) + kTile - 1) / kTile : 0;
+                if (tiles > 0) tiles += kItemCost;
+                int incl = tiles;
 #pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int n = __shfl_up_sync(0xffffffffu, incl, off);
-                if (lane >= off) incl += n;
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int n = __shfl_up_sync(0xffffffffu, incl, off);
+                    if (lane >= off) incl += n;
+                }
+                if (b < B) prefix_s[b] = running + incl - tiles;
+                running += __shfl_sync(0xffffffffu, incl, 31);
             }
-            if (b < B) prefix_s[b] = running + incl - tiles;  // 'tiles' already includes the item cost, see below
-            running += __shfl_sync(0xffffffffu, incl, 31);
+            if (lane == 0) prefix_s[B] = running;
         }
-        if (lane == 0) prefix_s[B] = running;
-    }
-    __syncthreads();
+        __syncthreads();
+    };
+    // value codewords of a head, which the prepare grid wrote in the bank-striped order: a flat 128 KB copy
+    auto copy_value_table = [&](int h) {
+        const uint4 *src = vperm_g + (size_t)h * (kWords * kSlots);
+        for (int e = tid; e < kWords * kSlots; e += kThreads) cp_async16(smem_u32(vtab_s) + e * 16, src + e);
+    };
+
+    // The score and value tables come from the prepare grid, and the visible ranges and newest code rows may
+    // still be being written two kernels back (a decode step's prologue lets its successors start early): of
+    // the kernels of this chain, nothing is read before this wait.
+    int loaded_head = -1;
+    wait_for_previous_kernel();
+    launch_dependents();  // the next kernel on the stream may take SMs as they free up; it waits for this grid itself
+    TRACE(1);
+    work_prefix();
     const int tiles_per_head = prefix_s[B];
     const int total_tiles = tiles_per_head * Hkv;  // fits: checked by the dispatcher
-    int cursor = (int)block_first_tile(total_tiles, blockIdx.x, gridDim.x);
-    const int my_end = (int)block_first_tile(total_tiles, blockIdx.x + 1, gridDim.x);
+    const int blocks = min((int)gridDim.x, max(total_tiles, 1));  // every working block owns at least one unit
+    int cursor = 0, my_end = 0;
+    if ((int)blockIdx.x < blocks) {
+        cursor = (int)block_first_tile(total_tiles, blockIdx.x, blocks);
+        my_end = (int)block_first_tile(total_tiles, blockIdx.x + 1, blocks);
+    }
 
     // ---- per-lane constants ------------------------------------------------------------------
     // score side: lane = token, slot visiting order permuted by XOR so a half warp covers 16 bank pairs
@@ -425,38 +511,37 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
     uint32_t k_sel[4];
 #pragma unroll
     for (int bi = 0; bi < 4; ++bi) k_sel[bi] = 0x4404u | (((bi ^ k_byte_xor) & 3u) << 4);
-    // value side: lane = (row r8, token-pair column kq) of the A fragment
+    // value side: lane = (row r8, token-pair column kq) of the A fragment; rows r8 / r8+8 carry groups
+    // 2*r8 / 2*r8+1.  Static step (sp, gsel) fetches stage sp ^ (kq & 1), group 2*r8 + (gsel ^ (kq >> 1)).
     const int r8 = lane >> 2, kq = lane & 3;
-    uint32_t v_sel[4], v_off[4];
+    uint32_t v_off[2][2], v_sel[2][2];
 #pragma unroll
-    for (int st = 0; st < 4; ++st) {
-        const int combo = st ^ kq;
-        const int s = combo & 1, gh = combo >> 1;
-        const int g = r8 + 8 * gh;
-        const int bq = (g & 1) | (gh << 1) | (s << 2);
-        const int pos = bq + 8 * ((g >> 1) & 3);
-        v_off[st] = smem_u32(vtab_s) + pos * 16;
-        v_sel[st] = 0x4404u | ((uint32_t)(s * 2 + gh) << 4);
-    }
+    for (int sp = 0; sp < 2; ++sp)
+#pragma unroll
+        for (int gsel = 0; gsel < 2; ++gsel) {
+            const int s = sp ^ (kq & 1), gh = gsel ^ (kq >> 1);
+            v_off[sp][gsel] = smem_u32(vtab_s) + value_pos(s, 2 * r8 + gh) * 16;
+        }
+#pragma unroll
+    for (int tk = 0; tk < 2; ++tk)
+#pragma unroll
+        for (int gsel = 0; gsel < 2; ++gsel)
+            v_sel[tk][gsel] = 0x4404u | ((uint32_t)(tk * 2 + (gsel ^ (kq >> 1))) << 4);  // code byte -> bits 8..15
     const int x_class = kq >> 1;                 // which visiting order this lane's tokens use
     const int b_head = r8 & 3;                   // B-fragment column n = r8: head n&3, class n>>2
     const bool b_valid = (r8 >> 2) == x_class;
     const uint32_t lut_base = smem_u32(lut_s);
+    const uint32_t scale_u32 = smem_u32(scale_s);
     const uint32_t vstage_u32 = smem_u32(stage_s) + warp * kStagePerWarp;
-    const uint32_t pstage_u32 = vstage_u32 + kVStage;
-
-    int loaded_head = -1;
-#if TACVQ_BULK_TABLES
-    __shared__ __align__(8) unsigned long long mbar;
-    const uint32_t mbar_a = smem_u32(&mbar);
-    uint32_t mbar_phase = 0;
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_a));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-#endif
-    wait_for_previous_kernel();  // everything above used only kernel arguments and the range arrays
+    const uint32_t pstage_u32 = vstage_u32 + kVCodeBytes;
+    // landing place of this lane's (= token's) two 16-byte stage halves: odd token pairs swap the halves
+    // (stage order of the value look-ups), and tokens 4..7 of every eight swap them once more so that the
+    // eight 16-byte rows of an ldmatrix tile cover all 32 banks
+    const uint32_t v_land = vstage_u32 + lane * 32 + ((((lane >> 1) ^ (lane >> 2)) & 1) * 16);
+    // ldmatrix row addresses for tokens 0..15 of the tile (the second call adds 512 bytes): matrix j = lane / 8
+    // holds tokens 8*(j/2) .. +7 of half j%2, row = lane % 8
+    const uint32_t v_row0 = vstage_u32 + (8 * (lane >> 4) + (lane & 7)) * 32 + ((((lane >> 3) & 1) ^ ((lane >> 2) & 1)) * 16);
+    const uint32_t p_read = pstage_u32 + (uint32_t)(b_head * kProbStride + kq * 4);  // B fragment of step ks: + ks * 16
 
     while (cursor < my_end) {
         // ---- which (head, batch row) does the cursor fall in ---------------------------------
@@ -486,57 +571,25 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
 
         __syncthreads();  // previous item fully merged: tables and staging may be overwritten
 
-        // ---- tables of this item: both were laid out for shared memory by the prepare kernel, so they
-        //      arrive as flat copies - bulk asynchronous copies (TMA) issued by one thread and counted by an
-        //      mbarrier, or, if that wait ever ran out, plain 16-byte cp.async by all threads
-        const bool need_v = h != loaded_head;
-        loaded_head = h;
-        const unsigned char *v_src = reinterpret_cast<const unsigned char *>(vperm_g) + (size_t)h * kVtabBytes;
-        const unsigned char *l_src = reinterpret_cast<const unsigned char *>(lut_g) + (size_t)pair * kLutBytes;
-#if TACVQ_BULK_TABLES
-        if (tid == 0) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // earlier generic accesses before async writes
-            const uint32_t bytes = kLutBytes + (need_v ? kVtabBytes : 0);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar_a), "r"(bytes) : "memory");
-            for (int off = 0; off < kLutBytes; off += kBulkPiece)
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 lut_base + off), "l"(l_src + off), "r"(kBulkPiece), "r"(mbar_a) : "memory");
-            if (need_v)
-                for (int off = 0; off < kVtabBytes; off += kBulkPiece)
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                     smem_u32(vtab_s) + off), "l"(v_src + off), "r"(kBulkPiece), "r"(mbar_a) : "memory");
+        // ---- tables of this item: the head's V codewords when the head changed, and the pair's score table,
+        //      which the prepare grid laid out for shared memory (a flat copy) ----------------------------------
+        if (h != loaded_head) {
+            loaded_head = h;
+            copy_value_table(h);
         }
-#else
-        if (need_v)
-            for (int j = tid; j < kVtabBytes / 16; j += kThreads) cp_async16(smem_u32(vtab_s) + j * 16, v_src + (size_t)j * 16);
-        for (int j = tid; j < kLutBytes / 16; j += kThreads) cp_async16(lut_base + j * 16, l_src + (size_t)j * 16);
-#endif
-        float step_l2[kStages][kRep], offs_l2[kRep];
-#pragma unroll
-        for (int r = 0; r < kRep; ++r) {
-            step_l2[0][r] = __ldg(scale_g + (size_t)pair * 16 + r);
-            step_l2[1][r] = __ldg(scale_g + (size_t)pair * 16 + 8 + r);
-            offs_l2[r] = __ldg(scale_g + (size_t)pair * 16 + 4 + r) + __ldg(scale_g + (size_t)pair * 16 + 12 + r);
-        }
-#if TACVQ_BULK_TABLES
         {
-            int ok = 0;
-            for (int spin = 0; spin < (1 << 20) && !ok; ++spin)  // bounded wait on the copy's byte count
-                asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.s32 %0, 1, 0, p;\n}"
-                             : "=r"(ok) : "r"(mbar_a), "r"(mbar_phase) : "memory");
-            mbar_phase ^= 1u;
-            if (!__syncthreads_and(ok)) {  // never seen; keeps the result independent of the copy engine
-                if (need_v)
-                    for (int j = tid; j < kVtabBytes / 16; j += kThreads) cp_async16(smem_u32(vtab_s) + j * 16, v_src + (size_t)j * 16);
-                for (int j = tid; j < kLutBytes / 16; j += kThreads) cp_async16(lut_base + j * 16, l_src + (size_t)j * 16);
-                cp_async_wait_all();
-                __syncthreads();
-            }
+            const unsigned char *l_src = reinterpret_cast<const unsigned char *>(lut_g) + (size_t)pair * kLutBytes;
+            for (int j = tid; j < kLutBytes / 16; j += kThreads) cp_async16(lut_base + j * 16, l_src + (size_t)j * 16);
         }
-#else
+        // the pair's steps and offset stay in shared memory (three broadcast loads per tile) rather than in
+        // twelve registers of every thread: scale_s = step of stage 0 x4, step of stage 1 x4, total offset x4
+        if (tid < 12) {
+            const float *sg = scale_g + (size_t)pair * 16;
+            scale_s[tid] = tid < 4 ? __ldg(sg + tid) : tid < 8 ? __ldg(sg + 4 + tid) : __ldg(sg + tid - 4) + __ldg(sg + tid + 4);
+        }
         cp_async_wait_all();
         __syncthreads();  // tables ready
-#endif
+        TRACE(2 + 4 * trace_item);
 
         // ---- scan this block's tiles of the pair ----------------------------------------------
         float acc[8][4];
@@ -551,77 +604,66 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
         const size_t row_base = ((size_t)b * Hkv + h) * (size_t)T_cap;
 
         // codes of a tile: lane = token; rows past the end of the range re-read the last valid row
-        auto code_offset = [=](int tile) -> size_t {  // byte offset of this lane's 32-byte code row
-            const int tok = tile * kTile + lane;
-            return (row_base + (size_t)(tok_lo_row + min(tok, n_tokens - 1))) * 32;
+        const uint8_t *k_row = kcodes + (row_base + (size_t)tok_lo_row) * 32, *v_row_g = vcodes + (row_base + (size_t)tok_lo_row) * 32;
+        auto code_offset = [=](int tile) -> uint32_t {  // byte offset of this lane's 32-byte code row (T_cap <= 2^26)
+            return (uint32_t)min(tile * kTile + lane, n_tokens - 1) * 32u;
         };
-        uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0, v0 = k0, v1 = k0;
+        uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0;
         if (tile_lo + warp < tile_hi) {
-            const size_t off = code_offset(tile_lo + warp);
-            const uint4 *kp = reinterpret_cast<const uint4 *>(kcodes + off), *vp = reinterpret_cast<const uint4 *>(vcodes + off);
+            const uint32_t off = code_offset(tile_lo + warp);
+            const uint4 *kp = reinterpret_cast<const uint4 *>(k_row + off);
             k0 = ldg_stream(kp); k1 = ldg_stream(kp + 1);
-            v0 = ldg_stream(vp); v1 = ldg_stream(vp + 1);
+            cp_async16(v_land, v_row_g + off);
+            cp_async16(v_land ^ 16u, v_row_g + off + 16);
         }
 
         for (int tile = tile_lo + warp; tile < tile_hi; tile += kWarps) {
             const bool live = tile * kTile + lane < n_tokens;
-            // -- value codes: byte transpose so that word r holds this token's 4 codes of groups r, r+8
-            {
-                const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                uint32_t tw[8];
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const uint32_t t0 = prmt(w[half], w[half + 2], 0x5140u), t1 = prmt(w[half], w[half + 2], 0x7362u);
-                    const uint32_t t2 = prmt(w[half + 4], w[half + 6], 0x5140u), t3 = prmt(w[half + 4], w[half + 6], 0x7362u);
-                    tw[half * 4 + 0] = prmt(t0, t2, 0x5410u);
-                    tw[half * 4 + 1] = prmt(t0, t2, 0x7632u);
-                    tw[half * 4 + 2] = prmt(t1, t3, 0x5410u);
-                    tw[half * 4 + 3] = prmt(t1, t3, 0x7632u);
-                }
-                __syncwarp();  // previous tile's readers are done with the staging area
-                const uint32_t dst = vstage_u32 + (((lane >> 3) * 2 + (lane & 1)) * kVBlock) + (((lane >> 1) & 3) * 32);
-                sts128(dst, tw[0], tw[1], tw[2], tw[3]);
-                sts128(dst + 16, tw[4], tw[5], tw[6], tw[7]);
-            }
+            const bool more = tile + kWarps < tile_hi;
+            __syncwarp();  // the previous tile's readers are done with the probability staging
+            const uint32_t next_off = code_offset(tile + kWarps);
 
             // -- scores: 32 look-ups of 8 bytes, four 13-bit fields each, flushed every 8 look-ups
-            uint32_t kw[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
-            if (tile + kWarps < tile_hi) {  // next tile's codes travel while this tile is computed
-                const size_t off = code_offset(tile + kWarps);
-                const uint4 *kp = reinterpret_cast<const uint4 *>(kcodes + off), *vp = reinterpret_cast<const uint4 *>(vcodes + off);
+            //    (the two stages run as a rolled loop: half the code and half the values in flight per pass)
+#if TACVQ_GSRQ_EARLY_K
+            const uint4 kc0 = k0, kc1 = k1;
+            if (more) {  // the next tile's K codes travel during this whole tile
+                const uint4 *kp = reinterpret_cast<const uint4 *>(k_row + next_off);
                 k0 = ldg_stream(kp); k1 = ldg_stream(kp + 1);
-                v0 = ldg_stream(vp); v1 = ldg_stream(vp + 1);
-                if (tile + 3 * kWarps < tile_hi) {  // and warm L2 two more rounds ahead
-                    prefetch_l2(reinterpret_cast<const unsigned char *>(kp) + (size_t)2 * kWarps * kTile * 32);
-                    prefetch_l2(reinterpret_cast<const unsigned char *>(vp) + (size_t)2 * kWarps * kTile * 32);
-                }
+                if (tile + 3 * kWarps < tile_hi) prefetch_l2(reinterpret_cast<const unsigned char *>(kp) + (size_t)2 * kWarps * kTile * 32);  // L2 two rounds ahead
             }
-            if (k_word_swap & 1) {
-#pragma unroll
-                for (int i = 0; i < 8; i += 2) { const uint32_t t = kw[i]; kw[i] = kw[i + 1]; kw[i + 1] = t; }
-            }
-            if (k_word_swap & 2) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if ((i & 2) == 0) { const uint32_t t = kw[i]; kw[i] = kw[i + 2]; kw[i + 2] = t; }
-                }
-            }
+#else
+            const uint4 &kc0 = k0, &kc1 = k1;
+#endif
             float sc[kRep];
-#pragma unroll
-            for (int r = 0; r < kRep; ++r) sc[r] = offs_l2[r];
-#pragma unroll
-            for (int st = 0; st < kStages; ++st) {  // words 0-3 hold stage 0, words 4-7 stage 1
+            {
+                const uint4 ofs = lds128(scale_u32 + 32);
+                sc[0] = __uint_as_float(ofs.x); sc[1] = __uint_as_float(ofs.y);
+                sc[2] = __uint_as_float(ofs.z); sc[3] = __uint_as_float(ofs.w);
+            }
+#pragma unroll kUnrollScore
+            for (int st = 0; st < kStages; ++st) {  // k0 holds the codes of stage 0, k1 those of stage 1
+                uint32_t kw[4] = {st ? kc1.x : kc0.x, st ? kc1.y : kc0.y, st ? kc1.z : kc0.z, st ? kc1.w : kc0.w};
+                if (k_word_swap & 1) {
+                    uint32_t t = kw[0]; kw[0] = kw[1]; kw[1] = t;
+                    t = kw[2]; kw[2] = kw[3]; kw[3] = t;
+                }
+                if (k_word_swap & 2) {
+                    uint32_t t = kw[0]; kw[0] = kw[2]; kw[2] = t;
+                    t = kw[1]; kw[1] = kw[3]; kw[3] = t;
+                }
+                const uint32_t lut_st = lut_base + (uint32_t)st * (kGroups * 8);
                 uint32_t isum[kRep] = {0u, 0u, 0u, 0u};
 #pragma unroll
                 for (int wp = 0; wp < 2; ++wp) {
                     uint32_t lo = 0u, hi = 0u;
 #pragma unroll
                     for (int wj = 0; wj < 2; ++wj) {
-                        const int wi = st * 4 + wp * 2 + wj;
+                        const int wi = wp * 2 + wj;
 #pragma unroll
                         for (int bi = 0; bi < 4; ++bi) {
                             const uint32_t code256 = prmt(kw[wi], 0u, k_sel[bi]);
-                            const uint32_t addr = ((code256 | (uint32_t)(wi * 32 + bi * 8)) ^ k_lane_xor) + lut_base;
+                            const uint32_t addr = ((code256 | (uint32_t)(wi * 32 + bi * 8)) ^ k_lane_xor) + lut_st;
                             const uint2 e = lds64(addr);
                             lo += e.x;
                             hi += e.y;
@@ -632,27 +674,42 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
                     isum[2] += hi & 0xffffu;
                     isum[3] += hi >> 16;
                 }
-#pragma unroll
-                for (int r = 0; r < kRep; ++r) sc[r] = fmaf((float)isum[r], step_l2[st][r], sc[r]);
+                const uint4 stp = lds128(scale_u32 + st * 16);
+                sc[0] = fmaf((float)isum[0], __uint_as_float(stp.x), sc[0]);
+                sc[1] = fmaf((float)isum[1], __uint_as_float(stp.y), sc[1]);
+                sc[2] = fmaf((float)isum[2], __uint_as_float(stp.z), sc[2]);
+                sc[3] = fmaf((float)isum[3], __uint_as_float(stp.w), sc[3]);
             }
 
-            // -- softmax bookkeeping (log2 domain), lazy rescale of the running reference
-            float tmax[kRep];
+#if !TACVQ_GSRQ_EARLY_K
+            if (more) {  // the next tile's K codes travel during the value phase and take over the registers freed above
+                const uint4 *kp = reinterpret_cast<const uint4 *>(k_row + next_off);
+                k0 = ldg_stream(kp); k1 = ldg_stream(kp + 1);
+                if (tile + 3 * kWarps < tile_hi) prefetch_l2(reinterpret_cast<const unsigned char *>(kp) + (size_t)2 * kWarps * kTile * 32);  // L2 two rounds ahead
+            }
+#endif
+
+            // -- softmax bookkeeping (log2 domain).  The reference m_ref only has to stay within
+            //    kRescaleGap of the largest score seen; it is re-derived when some live lane exceeds that.
             bool grow = false;
 #pragma unroll
             for (int r = 0; r < kRep; ++r) {
                 if (!live) sc[r] = -INFINITY;
-                float t = sc[r];
-#pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, off));
-                tmax[r] = t;
-                grow = grow || (t > m_ref[r] + kRescaleGap);
+                grow = grow || (sc[r] > m_ref[r] + kRescaleGap);
             }
-            if (grow) {  // warp-uniform
+#if TACVQ_GSRQ_LAZY_MAX
+            grow = __any_sync(0xffffffffu, grow);
+#else
+            grow = true;
+#endif
+            if (grow) {  // warp-uniform; always taken by a warp's first tile (m_ref = -inf)
                 float f[kRep];
 #pragma unroll
                 for (int r = 0; r < kRep; ++r) {
-                    const float nref = fmaxf(m_ref[r], tmax[r]);
+                    float t = sc[r];
+#pragma unroll
+                    for (int off = 16; off >= 1; off >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, off));
+                    const float nref = fmaxf(m_ref[r], t);
                     f[r] = fast_exp2(m_ref[r] - nref);  // 0 on the first tile (m_ref = -inf)
                     m_ref[r] = nref;
                     l_lane[r] *= f[r];
@@ -669,35 +726,55 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
             for (int r = 0; r < kRep; ++r) {
                 const float p = fast_exp2(sc[r] - m_ref[r]);
                 l_lane[r] += p;
-                sts16(pstage_u32 + (uint32_t)(r * kTile + lane) * 2, __half_as_ushort(__float2half_rn(p)));
+                sts16(pstage_u32 + (uint32_t)(r * kProbStride + lane * 2), __half_as_ushort(__float2half_rn(p)));
             }
-            __syncwarp();
+            // -- value codes of this tile: landed by cp.async, handed out by ldmatrix; register j of call a holds,
+            //    for the lane's token pair of 8-token step 2a + j/2, the two group codes of stage (j%2) ^ (kq&1)
+            cp_async_wait_all();
+            __syncwarp();  // also orders the probabilities written above before their reads below
 
             // -- values: per 8-token step gather this lane's two tokens (4 codewords each), add the two
-            //    stages, pair the tokens into A fragments and issue 8 m16n8k8 products
+            //    stages, pair the tokens into A fragments and issue 8 m16n8k8 products; 16 tokens per pass of a
+            //    rolled loop
+            uint32_t vm_lo[4], vm_hi[4];  // tokens 0..15 and 16..31 of the tile
+            ldmatrix_x4_trans(vm_lo, v_row0);
+            ldmatrix_x4_trans(vm_hi, v_row0 + 512);
+            __syncwarp();  // every lane has all its codes: the buffer may take the next tile, a whole tile ahead of its use
+            if (more) {
+                cp_async16(v_land, v_row_g + next_off);
+                cp_async16(v_land ^ 16u, v_row_g + next_off + 16);
+                if (tile + 3 * kWarps < tile_hi) prefetch_l2(v_row_g + next_off + (size_t)2 * kWarps * kTile * 32);
+            }
+#pragma unroll kUnrollValue
+            for (int a = 0; a < 2; ++a) {
+                const uint32_t vm[4] = {a ? vm_hi[0] : vm_lo[0], a ? vm_hi[1] : vm_lo[1], a ? vm_hi[2] : vm_lo[2], a ? vm_hi[3] : vm_lo[3]};
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                uint32_t b0 = 0u;
-                if (b_valid) b0 = lds32(pstage_u32 + (uint32_t)(b_head * kTile * 2 + (ks * 4 + kq) * 4));
-                uint4 sa[2], sb[2];
+                for (int ksl = 0; ksl < 2; ++ksl) {
+                    uint32_t b0 = 0u;
+                    if (b_valid) b0 = lds32(p_read + (uint32_t)(a * 2 + ksl) * 16);
+                    uint4 sa[2], sb[2];
 #pragma unroll
-                for (int tk = 0; tk < 2; ++tk) {
-                    const uint32_t word = lds32(vstage_u32 + (uint32_t)((ks * 2 + tk) * kVBlock + kq * 32 + r8 * 4));
-                    uint4 gth[4];
+                    for (int tk = 0; tk < 2; ++tk) {
+                        uint4 gth[2][2];
 #pragma unroll
-                    for (int st = 0; st < 4; ++st) {
-                        const uint32_t code256 = prmt(word, 0u, v_sel[st]);
-                        gth[st] = lds128(v_off[st] + code256 + code256);
+                        for (int sp = 0; sp < 2; ++sp)
+#pragma unroll
+                            for (int gsel = 0; gsel < 2; ++gsel) {
+                                const uint32_t code256 = prmt(vm[ksl * 2 + sp], 0u, v_sel[tk][gsel]);
+                                gth[sp][gsel] = lds128(v_off[sp][gsel] + code256 + code256);
+                            }
+                        sa[tk] = make_uint4(hadd2(gth[0][0].x, gth[1][0].x), hadd2(gth[0][0].y, gth[1][0].y),
+                                            hadd2(gth[0][0].z, gth[1][0].z), hadd2(gth[0][0].w, gth[1][0].w));
+                        sb[tk] = make_uint4(hadd2(gth[0][1].x, gth[1][1].x), hadd2(gth[0][1].y, gth[1][1].y),
+                                            hadd2(gth[0][1].z, gth[1][1].z), hadd2(gth[0][1].w, gth[1][1].w));
                     }
-                    sa[tk] = make_uint4(hadd2(gth[0].x, gth[1].x), hadd2(gth[0].y, gth[1].y), hadd2(gth[0].z, gth[1].z), hadd2(gth[0].w, gth[1].w));
-                    sb[tk] = make_uint4(hadd2(gth[2].x, gth[3].x), hadd2(gth[2].y, gth[3].y), hadd2(gth[2].z, gth[3].z), hadd2(gth[2].w, gth[3].w));
-                }
-                const uint32_t a0[4] = {sa[0].x, sa[0].y, sa[0].z, sa[0].w}, a1[4] = {sa[1].x, sa[1].y, sa[1].z, sa[1].w};
-                const uint32_t c0[4] = {sb[0].x, sb[0].y, sb[0].z, sb[0].w}, c1[4] = {sb[1].x, sb[1].y, sb[1].z, sb[1].w};
+                    const uint32_t a0[4] = {sa[0].x, sa[0].y, sa[0].z, sa[0].w}, a1[4] = {sa[1].x, sa[1].y, sa[1].z, sa[1].w};
+                    const uint32_t c0[4] = {sb[0].x, sb[0].y, sb[0].z, sb[0].w}, c1[4] = {sb[1].x, sb[1].y, sb[1].z, sb[1].w};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    mma1688(acc[2 * i], prmt(a0[i], a1[i], 0x5410u), prmt(c0[i], c1[i], 0x5410u), b0);
-                    mma1688(acc[2 * i + 1], prmt(a0[i], a1[i], 0x7632u), prmt(c0[i], c1[i], 0x7632u), b0);
+                    for (int i = 0; i < 4; ++i) {
+                        mma1688(acc[2 * i], prmt(a0[i], a1[i], 0x5410u), prmt(c0[i], c1[i], 0x5410u), b0);
+                        mma1688(acc[2 * i + 1], prmt(a0[i], a1[i], 0x7632u), prmt(c0[i], c1[i], 0x7632u), b0);
+                    }
                 }
             }
         }
@@ -711,7 +788,9 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
             for (int off = 16; off >= 1; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
             l_warp[r] = t;
         }
+        TRACE(3 + 4 * trace_item);  // thread 0's warp is done
         __syncthreads();  // every warp is done with the tables' score part and the staging area
+        TRACE(4 + 4 * trace_item);
         static_assert(kWarps * 32 * 32 * 4 <= kLutBytes, "merge scratch must fit in the score table");
         float *wm = reinterpret_cast<float *>(stage_s);    // [warps][4]
         float *wl = wm + kWarps * kRep;                     // [warps][4]
@@ -734,6 +813,9 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
                 base[(mm * 4 + 3) * 32] = acc[mm][3];
             }
         }
+        // the blocks that hold a partial state of this pair (this block among them)
+        const int c_lo = block_of_unit(pair_first + kItemCost, total_tiles, blocks);
+        const int n_parts = block_of_unit(pair_end - 1, total_tiles, blocks) - c_lo + 1;
         __syncthreads();
         for (int o = tid; o < kRep * kDim; o += kThreads) {
             // output o <-> (product mm, register j, lane of visiting-order class 0); its class-1 twin is
@@ -742,7 +824,7 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
             const int src_r8 = l16 >> 1, src_kq = l16 & 1;
             const int lane0 = src_r8 * 4 + src_kq;
             const int r = 2 * src_kq + (j & 1);
-            const int dim = (src_r8 + 8 * (j >> 1)) * 8 + mm;
+            const int dim = (2 * src_r8 + (j >> 1)) * 8 + mm;  // row r8 holds group 2*r8, row r8+8 group 2*r8+1
             float top = -INFINITY;
             for (int w = 0; w < kWarps; ++w) top = fmaxf(top, wm[w * kRep + r]);
             float lsum = 0.0f, asum = 0.0f;
@@ -754,59 +836,70 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes,
                 const float *src = wacc + (size_t)w * 1024;
                 asum += sc * (src[(mm * 4 + j) * 32 + lane0] + src[(mm * 4 + (j ^ 2)) * 32 + (lane0 ^ 2)]);
             }
-            float *dst = part + ((size_t)(pair + blockIdx.x) * kRep + r) * kStateWidth;
-            if (dim == 0) {
-                dst[0] = top * kLn2;  // natural-log units outside the kernel
-                dst[1] = lsum;
+            if (n_parts == 1) {  // the whole pair was scanned here: this is the result
+                const size_t row = (size_t)b * Hq + h * kRep + r;
+                if (out) out[row * kDim + dim] = __float2half_rn(lsum > 0.0f ? asum / lsum : 0.0f);
+                if (state_out) {
+                    float *dst = state_out + row * kStateWidth;
+                    if (dim == 0) {
+                        dst[0] = top * kLn2;  // natural-log units outside the kernel
+                        dst[1] = lsum;
+                    }
+                    dst[2 + dim] = asum;
+                }
+            } else {
+                float *dst = part + ((size_t)(pair + blockIdx.x) * kRep + r) * kStateWidth;
+                if (dim == 0) {
+                    dst[0] = top * kLn2;
+                    dst[1] = lsum;
+                }
+                dst[2 + dim] = asum;
             }
-            dst[2 + dim] = asum;
         }
-
-#if TACVQ_FUSED_MERGE
-        // ---- the block that finishes a pair last merges the pair's partial states -----------------
-        __threadfence();   // this block's partial state is visible device-wide before its ticket is drawn
-        __syncthreads();
-        if (tid == 0) {
-            const int n = list_pair_parts(pair_first, pair_end, total_tiles, gridDim.x, pair, parts_s);
-            const int drawn = atomicAdd(tickets + pair, 1);
-            n_parts_s = (drawn == n - 1) ? n : 0;  // 0: another block will finish this pair
-            __threadfence();
+        if (n_parts > 1) {
+            // Mark this partial with the call's epoch; whoever then finds every partial of the pair marked
+            // merges them.  The fences order (partial, mark) and (mark, reading the other marks), so the block
+            // whose mark lands last always sees all of them; two blocks may both see them and then write the same
+            // result.  A merging block clears the marks, so a replayed launch (same epoch) starts clean.
+            __syncthreads();
+            if (tid == 0) {
+                __threadfence();  // the block's partial (ordered before this by the barrier) is visible before its mark
+                marks[pair + blockIdx.x] = epoch;
+                __threadfence();
+            }
+            __syncthreads();
+            const int seen = tid < n_parts ? (ld_acquire_u64(marks + pair + c_lo + tid) == epoch) : 1;
+            if (__syncthreads_and(seen)) {
+                __threadfence();
+                merge_pair_parts(part, pair + c_lo, n_parts, b, h, Hkv, out, state_out);
+                if (tid < n_parts) marks[pair + c_lo + tid] = 0ull;
+            }
         }
-        __syncthreads();
-        if (n_parts_s > 0) merge_pair_parts(part, parts_s, n_parts_s, b, h, Hkv, out, state_out);
-#endif
         cursor = item_end;
+        TRACE(5 + 4 * trace_item);
+#ifdef TACVQ_GSRQ_TRACE
+        ++trace_item;
+#endif
     }
-}
 
-// ------------------------------------------------------------------------------------------------
-// merge kernel: one block per (batch row, KV head) pair merges the partial states its scan blocks wrote
-// ------------------------------------------------------------------------------------------------
-
-__global__ void __launch_bounds__(kRep * kDim)
-attn_gsrq_merge_kernel(const float *__restrict__ part, const int32_t *__restrict__ seq_start,
-                       const int32_t *__restrict__ seq_end, __half *__restrict__ out, float *__restrict__ state_out,
-                       int B, int Hkv, int T_cap, int scan_blocks) {
-    __shared__ int n_parts_s;
-    __shared__ int parts_s[kMaxScanBlocks];
-    const int pair = blockIdx.x, h = pair / B, b = pair % B;
-    wait_for_previous_kernel();
-    if (threadIdx.x == 0) {
-        int before = 0, mine = 0, per_head = 0;  // work units, exactly as the scan kernel counts them
-        for (int i = 0; i < B; ++i) {
-            int units = (row_tokens(seq_start, seq_end, i, T_cap) + kTile - 1) / kTile;
-            if (units > 0) units += kItemCost;
-            if (i < b) before += units;
-            if (i == b) mine = units;
-            per_head += units;
+    // ---- rows with an empty range never enter the loop: their defined result (out 0, m -inf, l 0, acc 0) ----
+    for (int pair = blockIdx.x; pair < B * Hkv; pair += gridDim.x) {
+        const int h = pair / B, b = pair % B;
+        if (prefix_s[b + 1] != prefix_s[b]) continue;
+        for (int o = tid; o < kRep * kDim; o += kThreads) {
+            const size_t row = (size_t)b * Hq + h * kRep + (o >> 7);
+            if (out) out[row * kDim + (o & 127)] = __float2half_rn(0.0f);
+            if (state_out) {
+                state_out[row * kStateWidth + 2 + (o & 127)] = 0.0f;
+                if ((o & 127) == 0) {
+                    state_out[row * kStateWidth] = -INFINITY;
+                    state_out[row * kStateWidth + 1] = 0.0f;
+                }
+            }
         }
-        const int first = h * per_head + before;
-        n_parts_s = mine > 0 ? list_pair_parts(first, first + mine, per_head * Hkv, scan_blocks, pair, parts_s) : 0;
     }
-    __syncthreads();
-    if (n_parts_s > 0) merge_pair_parts(part, parts_s, n_parts_s, b, h, Hkv, out, state_out);
+    TRACE(15);
 }
-
 
 }  // namespace gsrq
 
@@ -834,16 +927,16 @@ static cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 b
 
 static size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
 
-struct GsrqWorkspace {
-    size_t part, lut, vperm, scale, tickets, total;
+struct GsrqWorkspace {  // offsets into the caller's scratch; slot index = pair + scan block
+    size_t part, marks, lut, vperm, scale, total;
     GsrqWorkspace(int B, int Hkv, int sms) {
-        const size_t pairs = (size_t)B * Hkv;
-        part = 0;
-        lut = align256((pairs + (size_t)sms) * gsrq::kRep * gsrq::kStateWidth * sizeof(float));
+        const size_t pairs = (size_t)B * Hkv, slots = pairs + (size_t)sms;
+        part = 0;  // one partial softmax state per (pair, scan block) incidence
+        marks = align256(slots * gsrq::kRep * gsrq::kStateWidth * sizeof(float));
+        lut = align256(marks + slots * sizeof(unsigned long long));
         vperm = lut + pairs * gsrq::kLutBytes;
         scale = vperm + (size_t)Hkv * gsrq::kVtabBytes;
-        tickets = align256(scale + pairs * gsrq::kStages * 8 * sizeof(float));
-        total = align256(tickets + pairs * sizeof(int));
+        total = align256(scale + pairs * gsrq::kStages * 8 * sizeof(float));
     }
 };
 
@@ -853,80 +946,61 @@ size_t attn_gsrq_workspace_bytes(int B, int Hq, int Hkv, int D, int sms) {
     return GsrqWorkspace(B, Hkv, sms).total;
 }
 
+// Calls are numbered process-wide; a partial state is valid for the call whose number marks it.  The
+// counter starts at a value that uninitialised scratch is unlikely to hold (and marks are 64 bits wide).
+static std::atomic<unsigned long long> g_epoch{0x9e3779b97f4a7c15ull};
+
 int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
                        const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, void *workspace,
                        __half *out, float *state_out, int B, int Hq, int Hkv, int64_t T_cap, int sms,
                        cudaStream_t stream, bool after_prologue) {
     (void)Hq;
+    (void)after_prologue;  // every kernel of the chain waits for its predecessor by itself
     if (B > gsrq::kMaxBatch || sms > gsrq::kMaxScanBlocks) return TACVQ_ERR_UNSUPPORTED;
+    if (T_cap > ((int64_t)1 << 26)) return TACVQ_ERR_UNSUPPORTED;  // byte offsets inside a row's codes are 32-bit
     if (((T_cap + gsrq::kTile - 1) / gsrq::kTile + gsrq::kItemCost) * B * Hkv > 0x7fffffffLL) return TACVQ_ERR_UNSUPPORTED;
-    static bool configured[64] = {false};
+    if ((((uintptr_t)ktab | (uintptr_t)vtab | (uintptr_t)q) & 15) != 0) return TACVQ_ERR_ALIGN;
+    // first use on a device raises the scan's dynamic shared-memory limit; concurrent first calls all
+    // store the same value
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(gsrq::attn_gsrq_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              gsrq::kSmemBytes);
         if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(gsrq::attn_gsrq_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 gsrq::kPrepSmemBytes);
-        if (e != cudaSuccess) return (int)e;
         // both kernels ask for the largest shared-memory carve-out, so the SMs are not re-partitioned
-        // between the prepare and the scan launch of every step
-        e = cudaFuncSetAttribute(gsrq::attn_gsrq_prepare_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                 cudaSharedmemCarveoutMaxShared);
-        if (e != cudaSuccess) return (int)e;
+        // between the prepare and the scan launch of every call
         e = cudaFuncSetAttribute(gsrq::attn_gsrq_scan_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return (int)e;
-        configured[dev] = true;
+        e = cudaFuncSetAttribute(gsrq::attn_gsrq_prepare_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
+        if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
     const GsrqWorkspace ws(B, Hkv, sms);
     unsigned char *base = (unsigned char *)workspace;
     float *part = (float *)(base + ws.part);
+    unsigned long long *marks = (unsigned long long *)(base + ws.marks);
     uint2 *lut = (uint2 *)(base + ws.lut);
-    uint4 *vperm = (uint4 *)(base + ws.vperm);
     float *scale = (float *)(base + ws.scale);
-    int *tickets = (int *)(base + ws.tickets);
-    int st;
-    if (after_prologue && TACVQ_PDL) {
-        // the previous launch on this stream is the decode-step prologue, which lets this grid start at once
-        cudaError_t e = launch_dependent(gsrq::attn_gsrq_prepare_kernel, dim3(2 * B * Hkv + gsrq::kPrepVBlocks * Hkv),
-                                         dim3(gsrq::kPrepThreads), gsrq::kPrepSmemBytes, stream, q, ktab, vtab, lut, vperm, scale,
-                                         tickets, seq_start, seq_end, out, state_out, B, Hkv, (int)T_cap, 1);
-        st = e == cudaSuccess ? launch_status() : (int)e;
-    } else {
-        gsrq::attn_gsrq_prepare_kernel<<<2 * B * Hkv + gsrq::kPrepVBlocks * Hkv, gsrq::kPrepThreads, gsrq::kPrepSmemBytes, stream>>>(
-            q, ktab, vtab, lut, vperm, scale, tickets, seq_start, seq_end, out, state_out, B, Hkv, (int)T_cap, 0);
-        st = launch_status();
-    }
+    uint4 *vperm = (uint4 *)(base + ws.vperm);
+    const unsigned long long epoch = g_epoch.fetch_add(2, std::memory_order_relaxed);  // odd, so never 0 (= cleared)
+    cudaError_t e = launch_dependent(gsrq::attn_gsrq_prepare_kernel, dim3(2 * B * Hkv), dim3(gsrq::kPrepThreads), 0, stream, q,
+                                     ktab, vtab, lut, scale, vperm, B, Hkv);
+    int st = e == cudaSuccess ? launch_status() : (int)e;
     if (st != TACVQ_OK) return st;
-#if TACVQ_PDL
-    {
-        cudaError_t e = launch_dependent(gsrq::attn_gsrq_scan_kernel, dim3(sms), dim3(gsrq::kThreads), gsrq::kSmemBytes, stream,
-                                         kcodes, vcodes, lut, vperm, scale, seq_start, seq_end, part, tickets, out, state_out,
-                                         B, Hkv, (int)T_cap);
-        st = e == cudaSuccess ? launch_status() : (int)e;
-    }
-#else
-    gsrq::attn_gsrq_scan_kernel<<<sms, gsrq::kThreads, gsrq::kSmemBytes, stream>>>(
-        kcodes, vcodes, lut, vperm, scale, seq_start, seq_end, part, tickets, out, state_out, B, Hkv, (int)T_cap);
-    st = launch_status();
-#endif
-#if !TACVQ_FUSED_MERGE
-    if (st != TACVQ_OK) return st;
-#if TACVQ_PDL
-    {
-        cudaError_t e = launch_dependent(gsrq::attn_gsrq_merge_kernel, dim3(B * Hkv), dim3(gsrq::kRep * gsrq::kDim), 0, stream,
-                                         (const float *)part, seq_start, seq_end, out, state_out, B, Hkv, (int)T_cap, sms);
-        st = e == cudaSuccess ? launch_status() : (int)e;
-    }
-#else
-    gsrq::attn_gsrq_merge_kernel<<<B * Hkv, gsrq::kRep * gsrq::kDim, 0, stream>>>(part, seq_start, seq_end, out, state_out, B, Hkv,
-                                                                     (int)T_cap, sms);
-    st = launch_status();
-#endif
-#endif
-    return st;
+    e = launch_dependent(gsrq::attn_gsrq_scan_kernel, dim3(sms), dim3(gsrq::kThreads), gsrq::kSmemBytes, stream, kcodes, vcodes,
+                         (const uint2 *)lut, (const float *)scale, (const uint4 *)vperm, seq_start, seq_end, part, marks, out,
+                         state_out, B, Hkv, (int)T_cap, epoch);
+    return e == cudaSuccess ? launch_status() : (int)e;
 }
+
+#ifdef TACVQ_GSRQ_TRACE
+extern "C" __attribute__((visibility("default"))) int tacvq_dev_trace(unsigned long long *host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, gsrq::g_trace, sizeof(unsigned long long) * 256 * 16);
+}
+#endif
 
 }  // namespace tacvq
