@@ -71,7 +71,7 @@ constexpr int kDim = 128, kGroups = 16, kStages = 2, kSub = 8, kRep = 4, kSlots 
 constexpr int kTile = 32;          // tokens per warp tile
 constexpr int kMaxBatch = 512;
 #ifndef TACVQ_ITEM_COST
-#define TACVQ_ITEM_COST 64
+#define TACVQ_ITEM_COST 48
 #endif
 #ifndef TACVQ_GSRQ_UNROLL_K
 #define TACVQ_GSRQ_UNROLL_K 2  // 1: the two stages of the score phase as a rolled loop, 2: unrolled
@@ -422,20 +422,6 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
 // ------------------------------------------------------------------------------------------------
 // scan kernel
 // ------------------------------------------------------------------------------------------------
-#ifdef TACVQ_GSRQ_TRACE
-__device__ unsigned long long g_trace[256][16];
-__device__ __forceinline__ void trace(int slot) {
-    if (threadIdx.x == 0 && slot < 16) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_trace[blockIdx.x][slot] = t;
-    }
-}
-#define TRACE(slot) trace(slot)
-#else
-#define TRACE(slot)
-#endif
-
 __global__ void __launch_bounds__(kThreads, 1)
 attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes, const uint8_t *__restrict__ vcodes,
                       const uint2 *__restrict__ lut_g, const float *__restrict__ scale_g,
@@ -453,11 +439,6 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes, const uint8_t *__restr
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = Hkv * kRep;
 
-    TRACE(0);
-#ifdef TACVQ_GSRQ_TRACE
-    int trace_item = 0;
-    if (tid == 0) for (int i = 1; i < 16; ++i) g_trace[blockIdx.x][i] = 0;
-#endif
     // ---- work prefix over batch rows: a non-empty row costs its tiles plus kItemCost units (table
     //      copies, pipeline fill and drain, merge), so blocks that enter more pairs get fewer tiles ------
     auto work_prefix = [&]() {
@@ -492,7 +473,6 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes, const uint8_t *__restr
     int loaded_head = -1;
     wait_for_previous_kernel();
     launch_dependents();  // the next kernel on the stream may take SMs as they free up; it waits for this grid itself
-    TRACE(1);
     work_prefix();
     const int tiles_per_head = prefix_s[B];
     const int total_tiles = tiles_per_head * Hkv;  // fits: checked by the dispatcher
@@ -589,7 +569,6 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes, const uint8_t *__restr
         }
         cp_async_wait_all();
         __syncthreads();  // tables ready
-        TRACE(2 + 4 * trace_item);
 
         // ---- scan this block's tiles of the pair ----------------------------------------------
         float acc[8][4];
@@ -788,9 +767,7 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes, const uint8_t *__restr
             for (int off = 16; off >= 1; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
             l_warp[r] = t;
         }
-        TRACE(3 + 4 * trace_item);  // thread 0's warp is done
         __syncthreads();  // every warp is done with the tables' score part and the staging area
-        TRACE(4 + 4 * trace_item);
         static_assert(kWarps * 32 * 32 * 4 <= kLutBytes, "merge scratch must fit in the score table");
         float *wm = reinterpret_cast<float *>(stage_s);    // [warps][4]
         float *wl = wm + kWarps * kRep;                     // [warps][4]
@@ -876,10 +853,6 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes, const uint8_t *__restr
             }
         }
         cursor = item_end;
-        TRACE(5 + 4 * trace_item);
-#ifdef TACVQ_GSRQ_TRACE
-        ++trace_item;
-#endif
     }
 
     // ---- rows with an empty range never enter the loop: their defined result (out 0, m -inf, l 0, acc 0) ----
@@ -898,7 +871,6 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes, const uint8_t *__restr
             }
         }
     }
-    TRACE(15);
 }
 
 }  // namespace gsrq
@@ -996,11 +968,5 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
                          state_out, B, Hkv, (int)T_cap, epoch);
     return e == cudaSuccess ? launch_status() : (int)e;
 }
-
-#ifdef TACVQ_GSRQ_TRACE
-extern "C" __attribute__((visibility("default"))) int tacvq_dev_trace(unsigned long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, gsrq::g_trace, sizeof(unsigned long long) * 256 * 16);
-}
-#endif
 
 }  // namespace tacvq
