@@ -63,6 +63,26 @@ def encode(states: torch.Tensor, tables_f16: torch.Tensor, *, want_recon: bool =
     return codes, recon
 
 
+def encode_whitened(states: torch.Tensor, tables_f16: torch.Tensor, whitener: torch.Tensor, *, want_recon: bool = True):
+    """Whitened assignment: ``whitener`` fp32 ``[H,G,d,d]``; -> (codes [B,H,T,S,G], recon in states.dtype or None)."""
+    states = states.contiguous()
+    tables_f16 = tables_f16.contiguous()
+    whitener = whitener.detach().float().contiguous()
+    b, h, t, dim = states.shape
+    _, s, g, k, d = tables_f16.shape
+    assert tables_f16.dtype == torch.float16 and g * d == dim and tuple(whitener.shape) == (h, g, d, d)
+    codes = torch.empty(b, h, t, s, g, dtype=torch.uint8)
+    recon = torch.empty_like(states) if want_recon else None
+    _check(
+        lib().tacvq_oracle_encode_whitened(
+            _p(states), _DT[states.dtype], _p(tables_f16), _p(whitener), _p(codes), _p(recon), _DT[states.dtype],
+            b, h, t, dim, g, s, k, ctypes.c_int64(0), ctypes.c_int64(t),
+        ),
+        "encode_whitened",
+    )
+    return codes, recon
+
+
 def decode(codes: torch.Tensor, tables_f16: torch.Tensor, dtype: torch.dtype = torch.float16, *, depth: int | None = None, t0: int = 0, tokens: int | None = None):
     codes = codes.contiguous()
     tables_f16 = tables_f16.contiguous()

@@ -155,6 +155,95 @@ int tacvq_oracle_encode(const void *x, int x_dtype, const uint16_t *tables_f16, 
     return 0;
 }
 
+/*
+ * Encode with a whitened assignment geometry (closed_loop_vq.py:312-320, 384-390: one [D,D] matrix per head,
+ * G = 1; cq_tac.py:80-85: one [d,d] matrix per (head, group), S = 1).  whitener[H,G,d,d] row-major:
+ *   search row   y_i = sum_j W[i][j] x_j          search word  c'_i = sum_j c_j W[i][j]
+ * each one fused-multiply-add chain over j ascending, starting from 0.  The search runs on y against c'
+ * (norms of c' and of the running search residual in the order above) and subtracts the selected c';
+ * codes index the plain tables and the reconstruction sums plain fp16 words.
+ */
+int tacvq_oracle_encode_whitened(const void *x, int x_dtype, const uint16_t *tables_f16, const float *whitener,
+                                 uint8_t *codes, void *recon, int recon_dtype, int B, int H, int T, int D, int G,
+                                 int S, int K, int64_t t0, int64_t T_cap) {
+    if (G <= 0 || D % G != 0 || K <= 0 || K > 256 || D / G > 512) return -1;
+    const int d = D / G;
+    const half_t *tab = (const half_t *)tables_f16;
+    const int64_t words = (int64_t)H * S * G * K;
+    float *tabf = (float *)malloc(sizeof(float) * words * d);   /* plain words */
+    float *tabw = (float *)malloc(sizeof(float) * words * d);   /* transformed words */
+    float *norm = (float *)malloc(sizeof(float) * words);
+    if (!tabf || !tabw || !norm) return -2;
+    for (int64_t i = 0; i < words * d; ++i) tabf[i] = (float)tab[i];
+#pragma omp parallel for schedule(static)
+    for (int64_t w = 0; w < words; ++w) {
+        const int g = (int)((w / K) % G);
+        const int h = (int)(w / ((int64_t)K * G * S));
+        const float *mat = whitener + ((int64_t)h * G + g) * d * d;
+        for (int i = 0; i < d; ++i) {
+            float acc = 0.0f;
+            for (int j = 0; j < d; ++j) acc = fmaf(tabf[w * d + j], mat[i * d + j], acc);
+            tabw[w * d + i] = acc;
+        }
+        norm[w] = sqnorm_ordered(tabw + w * d, d);
+    }
+    const int64_t rows = (int64_t)B * H * T;
+#pragma omp parallel for schedule(static)
+    for (int64_t row = 0; row < rows; ++row) {
+        const int t = (int)(row % T);
+        const int h = (int)((row / T) % H);
+        const int b = (int)(row / ((int64_t)T * H));
+        float raw[512], res[512], dec[512];
+        for (int g = 0; g < G; ++g) {
+            const float *mat = whitener + ((int64_t)h * G + g) * d * d;
+            for (int i = 0; i < d; ++i) {
+                raw[i] = load_state(x, x_dtype, row * D + g * d + i);
+                dec[i] = 0.0f;
+            }
+            for (int i = 0; i < d; ++i) {
+                float acc = 0.0f;
+                for (int j = 0; j < d; ++j) acc = fmaf(mat[i * d + j], raw[j], acc);
+                res[i] = acc;
+            }
+            for (int s = 0; s < S; ++s) {
+                const int64_t base = (((int64_t)h * S + s) * G + g) * K;
+                const float xx = sqnorm_ordered(res, d);
+                float best = 0.0f;
+                int arg = 0;
+                for (int k = 0; k < K; ++k) {
+                    const float *c = tabw + (base + k) * d;
+                    float dot = 0.0f;
+                    for (int i = 0; i < d; ++i) dot = fmaf(res[i], c[i], dot);
+                    float lhs = xx + norm[base + k];
+                    float dist = lhs - 2.0f * dot;
+                    if (k == 0 || dist < best) {
+                        best = dist;
+                        arg = k;
+                    }
+                }
+                const float *cw = tabw + (base + arg) * d, *cp = tabf + (base + arg) * d;
+                for (int i = 0; i < d; ++i) {
+                    dec[i] = dec[i] + cp[i];
+                    res[i] = res[i] - cw[i];
+                }
+                codes[((((int64_t)b * H + h) * T_cap + t0 + t) * S + s) * G + g] = (uint8_t)arg;
+            }
+            if (recon) {
+                for (int i = 0; i < d; ++i) {
+                    if (recon_dtype == TACVQ_F16)
+                        ((half_t *)recon)[row * D + g * d + i] = (half_t)dec[i];
+                    else
+                        ((float *)recon)[row * D + g * d + i] = dec[i];
+                }
+            }
+        }
+    }
+    free(tabf);
+    free(tabw);
+    free(norm);
+    return 0;
+}
+
 /* Rebuild rows from codes[B,H,T_cap,S,G] (tokens t0..t0+T) using the first S_use stages. */
 int tacvq_oracle_decode(const uint8_t *codes, const uint16_t *tables_f16, void *out, int out_dtype, int B, int H,
                         int T, int D, int G, int S, int S_use, int K, int64_t t0, int64_t T_cap) {

@@ -16,6 +16,9 @@ Cases (reference entry point -> archive):
   * ``hard_grouped_cq`` and the folded ``hard_residual_vq_exits`` on reduced
     copies of the benchmark geometries (G=16,S=1,d=8 fp32; G=16,S=2,d=8 fp16
     with outlier channels; G=1,S=2,d=128 fp16; G=32,S=1,d=4) ..... encode.npz
+  * the whitened assignment at deployed sizes: ``hard_residual_vq_exits`` with a random
+    well-conditioned ``[H,128,128]`` whitener (K=256, D=128, 3 stages, fp16 and fp32 rows) and
+    ``hard_grouped_cq`` with random ``[H,G,d,d]`` selector whiteners (G=16,d=8 and G=32,d=4) ... whitened.npz
   * ``ClosedLoopUniformResidualVQ`` / ``ClosedLoopGroupedCQ`` forward ........ modules.npz
   * gradients of the hard forward (identity to states, gather to tables) ..... grads.npz
   * ``residual_vq_ledger`` and ``pack_fixed_width`` ............................ ledger.json
@@ -144,6 +147,32 @@ def encode_cases(ref, cq) -> dict:
     tables = (torch.randn(2, 4, 256, 128, generator=gen) * 0.3).half()
     exits, idx = ref.hard_residual_vq_exits(x, tables.float(), prefixes=(4,), token_chunk_size=1024, straight_through_states=False)
     out.update({"g1s4_t1.states": _np(x), "g1s4_t1.tables": _np(tables[:, :, None]), "g1s4_t1.codes": _np(idx[..., None]), "g1s4_t1.recon": _np(exits[4])})
+    return out
+
+
+def whitened_cases(ref, cq) -> dict:
+    """Whitened assignment at the sizes the deployable codecs carry (K = 256)."""
+    out = {}
+    gen = torch.Generator().manual_seed(8619)
+
+    def whitener(*lead, d):  # identity plus a dense perturbation: condition number of a few units
+        return torch.eye(d).expand(*lead, d, d) + 0.3 * torch.randn(*lead, d, d, generator=gen) / d**0.5
+
+    for name, dtype in (("rvq128_f16", torch.float16), ("rvq128_f32", torch.float32)):
+        x = torch.randn(1, 2, 64, 128, generator=gen).to(dtype)
+        tables = torch.stack([torch.randn(2, 256, 128, generator=gen) * (0.09 * 0.6**s) for s in range(3)], dim=1).half()  # [H,S,K,D]
+        w = whitener(2, d=128)
+        exits, idx = ref.hard_residual_vq_exits(x, tables.float(), prefixes=(1, 3), assignment_whiteners=w, token_chunk_size=1024,
+                                                straight_through_states=False)
+        out.update({f"{name}.states": _np(x), f"{name}.tables": _np(tables[:, :, None]), f"{name}.whitener": _np(w[:, None]),
+                    f"{name}.codes": _np(idx[..., None]), f"{name}.recon": _np(exits[3]), f"{name}.recon_depth1": _np(exits[1])})
+    for name, (g, d, dtype) in {"cq16x8": (16, 8, torch.float16), "cq32x4": (32, 4, torch.float32)}.items():
+        x = torch.randn(1, 2, 64, 128, generator=gen).to(dtype)
+        cb = (torch.randn(2, g, 256, d, generator=gen) * 0.5).half()
+        w = whitener(2, g, d=d)
+        recon, codes = cq.hard_grouped_cq(x, cb.float(), selector_whiteners=w, token_chunk_size=64, straight_through_states=False)
+        out.update({f"{name}.states": _np(x), f"{name}.tables": _np(cb[:, None]), f"{name}.whitener": _np(w),
+                    f"{name}.codes": _np(codes[:, :, :, None, :]), f"{name}.recon": _np(recon)})
     return out
 
 
@@ -318,7 +347,12 @@ def main() -> None:
         np.savez(HERE / "rotary.npz", **rotary_cases(ref))
         print("rotary.npz", (HERE / "rotary.npz").stat().st_size)
         return
+    if args.only == "whitened":
+        np.savez(HERE / "whitened.npz", **whitened_cases(ref, cq))
+        print("whitened.npz", (HERE / "whitened.npz").stat().st_size)
+        return
     np.savez(HERE / "rotary.npz", **rotary_cases(ref))
+    np.savez(HERE / "whitened.npz", **whitened_cases(ref, cq))
     np.savez(HERE / "reftests.npz", **reftests(ref))
     np.savez(HERE / "encode.npz", **encode_cases(ref, cq))
     np.savez(HERE / "modules.npz", **module_cases(uni, cq))

@@ -20,6 +20,26 @@ def test_c_encode_reproduces_reference_golden(golden, case):
     assert torch.equal(C.decode(codes, tables, states.dtype), g(f"{case}.recon"))
 
 
+@pytest.mark.parametrize("case", ["rvq128_f16", "rvq128_f32", "cq16x8", "cq32x4"])
+def test_whitened_assignment_oracles_reproduce_reference_golden(golden, case):
+    """Whitened assignment at deployed sizes (K = 256; D = 128 with a [H,128,128] matrix, 16 x 8 and 32 x 4
+    with per-group matrices): the order-explicit C oracle and the torch restatement both reproduce the
+    reference's codes and reconstructions exactly."""
+    g = golden("whitened.npz")
+    states, tables, w = g(f"{case}.states"), g(f"{case}.tables"), g(f"{case}.whitener")
+    codes, recon = C.encode_whitened(states, tables, w)
+    assert torch.equal(codes, g(f"{case}.codes")), int((codes != g(f"{case}.codes")).sum())
+    assert torch.equal(recon, g(f"{case}.recon"))
+    if case.startswith("rvq"):
+        exits, t_codes = O.residual_vq_encode(states, tables[:, :, 0].float(), prefixes=(1, 3), whiteners=w[:, 0])
+        assert torch.equal(t_codes[..., None], g(f"{case}.codes"))
+        assert torch.equal(exits[3], g(f"{case}.recon")) and torch.equal(exits[1], g(f"{case}.recon_depth1"))
+        assert torch.equal(C.decode(codes, tables, states.dtype, depth=1), g(f"{case}.recon_depth1"))
+    else:
+        t_recon, t_codes = O.grouped_cq_encode(states, tables[:, 0].float(), whiteners=w)
+        assert torch.equal(t_codes[:, :, :, None, :], g(f"{case}.codes")) and torch.equal(t_recon, g(f"{case}.recon"))
+
+
 def test_c_encode_equals_torch_restatement_on_the_cpu_benchmark_config():
     """fp32 [1,8,2048,128] rows, 16 groups x 256 words x 8 dims, seed 8601: 262,144 codes."""
     gen = torch.Generator().manual_seed(8601)

@@ -67,6 +67,56 @@ def test_reference_unit_test_cases_through_the_drop_in_api(golden, device, case,
         assert torch.equal(exits[depth].cpu(), g(f"{case}.exit{depth}"))
 
 
+@pytest.mark.parametrize("case", ["rvq128_f16", "rvq128_f32", "cq16x8", "cq32x4"])
+def test_whitened_assignment_matches_reference_golden(golden, device, case):
+    """Whitened assignment at deployed sizes through the drop-in functions: a random well-conditioned
+    [H,128,128] matrix with 256 x 128 tables (3 stages, fp16 and fp32 rows), and per-group [H,G,d,d]
+    matrices for 16 x 8 and 32 x 4 grouped codebooks.  Codes and reconstructions equal the reference's."""
+    from tac_vq_kv_cache_b200.jointkv.closed_loop_vq import hard_residual_vq_exits
+    from tac_vq_kv_cache_b200.jointkv.cq_tac import hard_grouped_cq
+
+    g = golden("whitened.npz")
+    states, tables, w = g(f"{case}.states").to(device), g(f"{case}.tables").to(device), g(f"{case}.whitener").to(device)
+    if case.startswith("rvq"):
+        exits, codes = hard_residual_vq_exits(states, tables[:, :, 0].float(), prefixes=(1, 3), assignment_whiteners=w[:, 0],
+                                              straight_through_states=False)
+        assert torch.equal(codes.cpu()[..., None], g(f"{case}.codes")), int((codes.cpu()[..., None] != g(f"{case}.codes")).sum())
+        assert torch.equal(exits[3].cpu(), g(f"{case}.recon")) and torch.equal(exits[1].cpu(), g(f"{case}.recon_depth1"))
+    else:
+        recon, codes = hard_grouped_cq(states, tables[:, 0].float(), selector_whiteners=w, straight_through_states=False)
+        assert torch.equal(codes.cpu()[:, :, :, None, :], g(f"{case}.codes")), int((codes.cpu()[:, :, :, None, :] != g(f"{case}.codes")).sum())
+        assert torch.equal(recon.cpu(), g(f"{case}.recon"))
+
+
+@pytest.mark.parametrize(
+    "name,shape,dtype,stages,groups,want_recon",
+    [
+        ("gsrq_parent_fp16", (2, 8, 2048, 128), torch.float16, 2, 1, True),    # [H,128,128] matrix, 256 x 128 tables
+        ("gsrq_parent_fp32", (1, 8, 1500, 128), torch.float32, 3, 1, False),
+        ("cq_16x8_fp16", (2, 8, 1024, 128), torch.float16, 1, 16, True),       # [H,16,8,8] selector matrices
+        ("cq_32x4_fp32", (1, 8, 777, 128), torch.float32, 1, 32, True),        # [H,32,4,4]
+        ("two_64_wide_groups", (1, 4, 300, 128), torch.float16, 2, 2, True),   # [H,2,64,64]
+        ("four_32_wide_groups", (1, 2, 200, 128), torch.float32, 2, 4, True),  # [H,4,32,32]
+    ],
+)
+def test_whitened_assignment_is_bit_exact_with_the_c_oracle(device, name, shape, dtype, stages, groups, want_recon):
+    """Layer-sized whitened encodes: transformed rows and words (one multiply-add chain per element), the
+    search on them, plain-word reconstruction - codes and rows equal the order-explicit oracle bit for bit."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(8619 + len(name))
+    states = make_states(gen, shape, dtype)
+    sub = shape[-1] // groups
+    tables = make_tables(gen, shape[1], stages, groups, sub, [0.09 * 0.6**s for s in range(stages)] if sub >= 32 else None)
+    w = torch.eye(sub).expand(shape[1], groups, sub, sub) + 0.3 * torch.randn(shape[1], groups, sub, sub, generator=gen) / sub**0.5
+    want_codes, want_recon_rows = C.encode_whitened(states, tables, w, want_recon=want_recon)
+    codes, recon = ops.encode(states.to(device), tables.to(device), whitener=w.to(device), want_recon=want_recon)
+    assert torch.equal(codes.cpu(), want_codes), int((codes.cpu() != want_codes).sum())
+    if want_recon:
+        assert torch.equal(recon.cpu(), want_recon_rows)
+    plain, _ = C.encode(states, tables, want_recon=False)
+    assert int((plain != want_codes).sum()) > 0  # the matrix does change assignments: the test is not vacuous
+
+
 def test_modules_match_reference_golden(golden, device):
     from tac_vq_kv_cache_b200.jointkv.cq_tac import ClosedLoopGroupedCQ
     from tac_vq_kv_cache_b200.jointkv.uniform_depth_tac import ClosedLoopUniformResidualVQ
