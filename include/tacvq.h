@@ -201,18 +201,44 @@ TACVQ_API int tacvq_decode_step(const uint16_t *q_f16, const void *k_rows, const
                                 int D, int G, int S, int K, int T_new, int64_t T_cap, tacvq_stream_t stream);
 
 /*
+ * tacvq_decode_step for a host that holds the new token's rows and wants the result in HOST memory: one call
+ * enqueues the host-to-device copy of the rows, the decode step and the device-to-host copy of the result,
+ * and optionally waits for the stream.  It covers one iteration of the reference's generation loop around
+ * its per-layer adapter (experiments_followup_mistral/evaluate_mistral_longbench.py:156-197 calls the model
+ * once per token; :94-98, 112-122 is the per-layer body), for hosts that drive a layer from another process
+ * or language and pay per call.
+ *
+ *   host_rows     host buffer (pinned for an asynchronous copy): q [B,Hq,D] fp16, then the new K rows
+ *                 [B,Hkv,T_new,D], then the new V rows, K and V in rows_dtype, packed back to back
+ *   dev_rows      device buffer of the same size, 16-byte aligned: the landing place of host_rows
+ *   dev_out       device [B,Hq,D] fp16;  host_out  host buffer of the same size receiving it
+ *   synchronize   non-zero: return after the stream has finished (host_out is valid on return)
+ * Other arguments and status codes as tacvq_decode_step.
+ */
+TACVQ_API int tacvq_decode_step_host(const void *host_rows, void *dev_rows, int rows_dtype, const uint16_t *ktab_f16,
+                                     const uint16_t *vtab_f16, uint8_t *kcodes, uint8_t *vcodes, int32_t *seq_start,
+                                     int32_t *seq_end, int64_t length, int64_t window, void *workspace,
+                                     size_t workspace_bytes, uint16_t *dev_out, void *host_out, int B, int Hq, int Hkv,
+                                     int D, int G, int S, int K, int T_new, int64_t T_cap, int synchronize,
+                                     tacvq_stream_t stream);
+
+/*
  * tacvq_attn_decode for callers that must not allocate device memory.  It has no counterpart in the
  * reference.  Some hosts of this library cannot call cudaMalloc at the point where they need
  * attention: a plugin running inside another runtime's memory pool, a callback on a thread that is
  * not allowed to touch the allocator, a process whose device memory was handed out in full at start-up.
  * For them the scratch is a fixed 16 MiB array inside the library image
  * (tacvq_attn_static_scratch_bytes() returns that figure); the caller passes only inputs and outputs.
- * The call allocates and frees nothing, on the device or through any library.
+ * After the set-up call described below a call allocates and frees nothing, on the device or through any library.
  *
  *   - Limit: geometries whose tacvq_attn_workspace_bytes(...) exceeds 16 MiB are refused with
  *     TACVQ_ERR_WORKSPACE (nothing is launched).  The benchmark geometry at batch 8 needs 8.1 MiB.
- *   - The first call on each device looks up the array's device address (one cudaGetSymbolAddress
- *     with that device current).  Make that first call outside any stream capture.
+ *   - The first call on each device is a set-up call: the CUDA runtime loads this library's kernels and the
+ *     array onto that device when they are first used, and the call looks up the array's device address
+ *     (one cudaGetSymbolAddress with that device current, kept for later calls; first calls from several
+ *     host threads may overlap, they store the same address).  Make one warm-up call per device at
+ *     start-up, outside any stream capture; calls after it allocate nothing.  A cudaDeviceReset
+ *     invalidates the address together with everything else the library has set up on that device.
  *   - All calls on a device share the one array: two calls whose kernels may overlap on the GPU
  *     (different streams without ordering between them) race on it.  Calls on one stream are safe.
  *     The array keeps the previous call's contents; nothing in it has to start at zero, because

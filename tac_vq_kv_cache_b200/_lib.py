@@ -30,6 +30,8 @@ _SIGNATURES = {
     "tacvq_attn_decode": (c_int, [c_void_p] * 8 + [c_size_t, c_void_p, c_void_p] + [c_int] * 7 + [c_int64, c_void_p]),
     "tacvq_decode_step": (c_int, [c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 6 + [c_int64, c_int64, c_void_p, c_size_t,
                                   c_void_p, c_void_p] + [c_int] * 8 + [c_int64, c_void_p]),
+    "tacvq_decode_step_host": (c_int, [c_void_p, c_void_p, c_int] + [c_void_p] * 6 + [c_int64, c_int64, c_void_p, c_size_t,
+                                       c_void_p, c_void_p] + [c_int] * 8 + [c_int64, c_int, c_void_p]),
     "tacvq_set_ranges": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tacvq_attn_static_scratch_bytes": (c_size_t, []),
     "tacvq_attn_decode_static": (c_int, [c_void_p] * 7 + [c_void_p, c_void_p] + [c_int] * 7 + [c_int64, c_void_p]),

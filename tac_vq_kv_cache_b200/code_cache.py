@@ -63,6 +63,7 @@ class VQCodeCache:
         self._range_is = (0, 0)
         self._workspace: torch.Tensor | None = None
         self._step_key, self._step_args = None, None  # decode_step's checked and marshalled arguments
+        self._host_key, self._host_call = None, None  # decode_step_host's
         self.rope = None if rope_theta is None else ops.rope_table(self.max_tokens, self.dim, float(rope_theta), self.device)
 
     def reset(self) -> None:
@@ -170,3 +171,51 @@ class VQCodeCache:
         self.length += tokens
         self._range_is = self.visible()
         return out
+
+    def decode_step_host(self, host_rows: torch.Tensor, host_out: torch.Tensor, q_heads: int, *, tokens: int = 1,
+                         synchronize: bool = True) -> torch.Tensor:
+        """One decode step driven from HOST buffers in a single library call (``tacvq_decode_step_host``).
+
+        ``host_rows``: pinned CPU fp16 tensor holding, back to back, the scaled query ``[B,Hq,D]``, the new K
+        rows ``[B,H,tokens,D]`` and the new V rows; ``host_out``: pinned CPU fp16 ``[B,Hq,D]`` that receives the
+        result.  The call enqueues the copy to the device, the encode + append + attention of
+        :meth:`decode_step` and the copy back, and by default waits for them.  A decoding loop passes the same
+        buffers every step: checks and argument marshalling happen once per pair of buffers.
+        """
+        from . import _lib
+
+        if self.rope is not None:
+            raise ValueError("the single-call host path has no rotary step; use append() + attend()")
+        key = (host_rows.data_ptr(), host_out.data_ptr(), int(q_heads), int(tokens), host_rows.numel(), host_out.numel())
+        if key != self._host_key:
+            nq, nkv = self.batch * int(q_heads) * self.dim, self.batch * self.heads * int(tokens) * self.dim
+            if host_rows.device.type != "cpu" or host_out.device.type != "cpu" or not (host_rows.is_pinned() and host_out.is_pinned()):
+                raise ValueError("host_rows and host_out must be pinned CPU tensors")
+            if host_rows.dtype != torch.float16 or host_out.dtype != torch.float16:
+                raise ValueError("host buffers must be fp16")
+            if host_rows.numel() != nq + 2 * nkv or host_out.numel() != nq or not (host_rows.is_contiguous() and host_out.is_contiguous()):
+                raise ValueError("host_rows must hold q, K rows and V rows back to back; host_out must be [B,Hq,D]")
+            if self._workspace is None:
+                need = ops.attn_workspace_bytes(self.batch, int(q_heads), self.heads, self.dim, self.groups, self.stages)
+                if need == 0:
+                    raise ValueError("attention geometry not supported")
+                self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+            dev_rows = torch.empty(nq + 2 * nkv, dtype=torch.float16, device=self.device)
+            dev_out = torch.empty(nq, dtype=torch.float16, device=self.device)
+            head = (host_rows.data_ptr(), dev_rows.data_ptr(), ops._DTYPE_TAG[torch.float16], self.key_tables.data_ptr(),
+                    self.value_tables.data_ptr(), self.key.data_ptr(), self.value.data_ptr(), self._range[0].data_ptr(),
+                    self._range[1].data_ptr())
+            mid = (self._workspace.data_ptr(), self._workspace.numel(), dev_out.data_ptr(), host_out.data_ptr(), self.batch,
+                   int(q_heads), self.heads, self.dim, self.groups, self.stages, int(self.key_tables.shape[-2]), int(tokens),
+                   self.max_tokens)
+            self._host_key, self._host_call = key, (head, mid, dev_rows, dev_out, _lib.load().tacvq_decode_step_host)
+        head, mid, _dev_rows, _dev_out, call = self._host_call
+        if self.length + tokens > self.max_tokens:
+            raise ValueError("code cache is full")
+        with ops._on(self.device):
+            status = call(*head, self.length, 0 if self.window is None else self.window, *mid, 1 if synchronize else 0,
+                          ops._stream(self.device))
+        _lib.check("tacvq_decode_step_host", status)
+        self.length += tokens
+        self._range_is = self.visible()
+        return host_out

@@ -24,9 +24,11 @@ int attn_generic_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t 
 int attn_combine_dispatch(const float *states, int n_parts, __half *out, float *merged, int64_t rows, int D,
                           cudaStream_t stream);
 bool attn_fullwidth_supported(int Hq, int Hkv, int D, int G, int S, int K);
+int attn_fullwidth_splits(int B, int Hkv, int64_t T_cap, int sms);
 int attn_fullwidth_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
-                            const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, float *part, int B,
-                            int Hq, int Hkv, int S, int64_t T_cap, int splits, cudaStream_t stream);
+                            const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, float *part,
+                            __half *out, float *state_out, int B, int Hq, int Hkv, int S, int64_t T_cap, int splits,
+                            cudaStream_t stream);
 bool attn_gsrq_supported(int Hq, int Hkv, int D, int G, int S, int K);
 size_t attn_gsrq_workspace_bytes(int B, int Hq, int Hkv, int D, int sms);
 int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
@@ -247,21 +249,17 @@ int tacvq_attn_decode(const uint16_t *q_f16, const uint8_t *kcodes, const uint8_
         if (fast != TACVQ_ERR_UNSUPPORTED) return fast;  // sizes beyond the specialised scan: the generic kernel below
     }
     int splits = attn_generic_splits(B, Hkv, T_cap, sm_count());
-    if (attn_fullwidth_supported(Hq, Hkv, D, G, S, K) && (T_cap + 8191) / 8192 <= kGenericMaxSplits) {
-        // every block builds its own score table and multiplies its histogram by the V tables (2 x S x 64 KB of
-        // table reads), so few, long splits are cheaper than many short ones
-        splits = (sm_count() + B * Hkv - 1) / (B * Hkv);
-        if (splits > kGenericMaxSplits) splits = kGenericMaxSplits;
-        if ((int64_t)splits * 1024 > T_cap) splits = (int)((T_cap + 1023) / 1024);
-        if (splits < 1) splits = 1;
-        const int64_t by_range = (T_cap + 8191) / 8192;  // a block's histogram holds at most 8192 tokens
-        if (splits < by_range) splits = (int)by_range;
-
-        int fw = attn_fullwidth_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
-                                         (const __half *)vtab_f16, seq_start, seq_end, (float *)workspace, B, Hq, Hkv, S,
-                                         T_cap, splits, s);
-        if (fw != TACVQ_OK) return fw;
-        return attn_combine_dispatch((const float *)workspace, splits, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);
+    if (attn_fullwidth_supported(Hq, Hkv, D, G, S, K) && (((uintptr_t)ktab_f16 | (uintptr_t)vtab_f16) & 15) == 0) {
+        splits = attn_fullwidth_splits(B, Hkv, T_cap, sm_count());
+        if (splits <= kGenericMaxSplits) {
+            // a single block per pair writes the result itself; several blocks leave partial states to merge
+            int fw = attn_fullwidth_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
+                                             (const __half *)vtab_f16, seq_start, seq_end, (float *)workspace,
+                                             (__half *)out_f16, state_out, B, Hq, Hkv, S, T_cap, splits, s);
+            if (fw != TACVQ_OK || splits == 1) return fw;
+            return attn_combine_dispatch((const float *)workspace, splits, (__half *)out_f16, state_out, (int64_t)B * Hq, D, s);
+        }
+        splits = attn_generic_splits(B, Hkv, T_cap, sm_count());
     }
     if (attn_rotary_staged_supported(Hq, Hkv, D, G, S, K) && (((uintptr_t)ktab_f16 | (uintptr_t)vtab_f16) & 15) == 0) {
         // head_dim 128 in pieces of 8 channels, at most two stages (e.g. one-stage grouped CQ): score table and
@@ -379,6 +377,34 @@ int tacvq_decode_step(const uint16_t *q_f16, const void *k_rows, const void *v_r
     if (st != TACVQ_OK) return st;
     return tacvq_attn_decode(q_f16, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, workspace, workspace_bytes,
                              out_f16, state_out, B, Hq, Hkv, D, G, S, K, T_cap, stream);
+}
+
+int tacvq_decode_step_host(const void *host_rows, void *dev_rows, int rows_dtype, const uint16_t *ktab_f16,
+                           const uint16_t *vtab_f16, uint8_t *kcodes, uint8_t *vcodes, int32_t *seq_start, int32_t *seq_end,
+                           int64_t length, int64_t window, void *workspace, size_t workspace_bytes, uint16_t *dev_out,
+                           void *host_out, int B, int Hq, int Hkv, int D, int G, int S, int K, int T_new, int64_t T_cap,
+                           int synchronize, tacvq_stream_t stream) {
+    if (!host_rows || !dev_rows || !dev_out || !host_out) return TACVQ_ERR_NULL;
+    if (!dtype_ok(rows_dtype)) return TACVQ_ERR_DTYPE;
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || T_new <= 0) return TACVQ_ERR_GEOMETRY;
+    const size_t q_bytes = (size_t)B * Hq * D * sizeof(uint16_t);
+    const size_t kv_bytes = (size_t)B * Hkv * T_new * D * (rows_dtype == TACVQ_F16 ? 2 : 4);
+    if ((((uintptr_t)dev_rows) & 15) != 0 || (q_bytes & 15) != 0 || (kv_bytes & 15) != 0) return TACVQ_ERR_ALIGN;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(dev_rows, host_rows, q_bytes + 2 * kv_bytes, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return (int)e;
+    unsigned char *base = (unsigned char *)dev_rows;
+    const int st = tacvq_decode_step((const uint16_t *)base, base + q_bytes, base + q_bytes + kv_bytes, rows_dtype, ktab_f16,
+                                     vtab_f16, kcodes, vcodes, seq_start, seq_end, length, window, workspace, workspace_bytes,
+                                     dev_out, nullptr, B, Hq, Hkv, D, G, S, K, T_new, T_cap, stream);
+    if (st != TACVQ_OK) return st;
+    e = cudaMemcpyAsync(host_out, dev_out, q_bytes, cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return (int)e;
+    if (synchronize) {
+        e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return TACVQ_OK;
 }
 
 size_t tacvq_attn_static_scratch_bytes(void) { return kStaticScratchBytes; }

@@ -3,16 +3,22 @@
 // the "two additive 256x128 codebooks" configuration; a token and head is only S bytes per side.
 //
 // With so few codes per token the value side is cheapest as a weighted histogram: instead of fetching
-// S x 256 bytes of codewords per token, add the token's softmax weight to hist[stage][code][head]
+// S x 256 bytes of codewords per token, add the token's softmax weight to hist[stage][head][code]
 // (S x 4 shared-memory atomic adds; the weights are added as 18-bit fixed point because integer adds
 // are native shared-memory atomics and float adds are compare-and-swap loops) and multiply the
 // histogram by the V codebook once per block:
 //     acc[h][:] = sum_{s,c} hist[s][c][h] * vtab[s][c][:].
-// Scores are S look-ups of a 16-byte entry (4 heads, fp32).  The softmax reference of a block is the
-// exact maximum of its token range, found by a first pass over the K codes (2 x S bytes per token are
-// read twice; the alternative, rescaling a block-wide histogram on the fly, needs block-wide barriers).
-// Partial states go to the same [split][row][2+D] layout the generic kernel uses and are merged by
-// attn_combine_kernel.
+// Scores are S look-ups of a 16-byte entry (4 heads, fp32).  The per-block work that does not depend on
+// the number of tokens is what bounds this kernel at decode sizes (a block reads S x 64 KB of K tables
+// for its score table and S x 64 KB of V tables for the product), so:
+//   - one block takes a whole (batch row, KV head) pair whenever the pairs alone fill most of the SMs,
+//     and then writes the result itself (no partial states, no merge launch);
+//   - the score table is built with one thread per codeword (eight 16-byte loads in flight, q read
+//     as shared-memory broadcasts) instead of a warp per codeword with shuffle reductions;
+//   - codes are read straight from global memory with the widest load the stage count allows, the K
+//     codes twice (exact maximum first, then weights): the second read hits L2.
+// Partial states (several blocks per pair) go to the [split][row][2+D] layout the generic kernel uses and
+// are merged by attn_combine_kernel.
 //
 // Semantics replaced: experiments_followup_mistral/evaluate_mistral_longbench.py:112-122 (no rotary
 // step).  Differences from the dense path inside the 2e-3 tolerance: the V row is the exact sum of its
@@ -24,28 +30,63 @@
 namespace tacvq {
 namespace fullwidth {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;   // (1024 threads were measured: 14 % slower)
 constexpr int kWarps = kThreads / 32;
 constexpr int kDim = 128, kRep = 4, kWords = 256;
 constexpr int kMaxStages = 16;
-constexpr int kStageBytes = 16384;           // code bytes of one side staged in shared memory at a time
-[[maybe_unused]] constexpr int kSplitTokens = 8192;          // a block's range: 8192 weights of at most 2^18 fit 32 bits
+constexpr int kSegmentTokens = 8192;        // 8192 weights of at most 2^18 fit the 32-bit fixed-point bins: after that many
+                                           // tokens a block folds the bins into a float histogram and clears them
 constexpr float kWeightOne = 262144.0f;     // fixed-point one (2^18); the largest weight of a range is exactly 1
+constexpr int kSlices = kThreads / 16;      // word slices of the histogram-times-codebook product
 
+// S code bytes of one token as WORDS 32-bit words.  WIDE = S when one aligned load fetches them (2, 4, 8, 16),
+// 0 for any other stage count (byte loads).
+template <int WORDS, int WIDE>
+__device__ __forceinline__ void load_codes(const uint8_t *__restrict__ p, int S, uint32_t (&w)[WORDS]) {
+    if constexpr (WIDE == 2) {
+        w[0] = *reinterpret_cast<const unsigned short *>(p);
+    } else if constexpr (WIDE == 4) {
+        w[0] = *reinterpret_cast<const uint32_t *>(p);
+    } else if constexpr (WIDE == 8) {
+        const uint2 v = *reinterpret_cast<const uint2 *>(p);
+        w[0] = v.x; w[1] = v.y;
+    } else if constexpr (WIDE == 16) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(p);
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < WORDS; ++i) {
+            w[i] = 0u;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (4 * i + j < S) w[i] |= (uint32_t)p[4 * i + j] << (8 * j);
+        }
+    }
+}
+// the next code byte of a token: the words are consumed as one shift register (no indexed access)
+template <int WORDS>
+__device__ __forceinline__ int next_code(uint32_t (&w)[WORDS]) {
+    const int code = w[0] & 255;
+#pragma unroll
+    for (int i = 0; i + 1 < WORDS; ++i) w[i] = __funnelshift_r(w[i], w[i + 1], 8);
+    w[WORDS - 1] >>= 8;
+    return code;
+}
+
+template <int WORDS, int WIDE>
 __global__ void __launch_bounds__(kThreads)
 attn_fullwidth_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ kcodes,
                       const uint8_t *__restrict__ vcodes, const __half *__restrict__ ktab,
                       const __half *__restrict__ vtab, const int32_t *__restrict__ seq_start,
-                      const int32_t *__restrict__ seq_end, float *__restrict__ part, int B, int Hkv, int S,
-                      int64_t T_cap, int splits) {
+                      const int32_t *__restrict__ seq_end, float *__restrict__ part, __half *__restrict__ out,
+                      float *__restrict__ state_out, int B, int Hkv, int S, int64_t T_cap, int splits) {
     extern __shared__ __align__(16) float smem[];
     float4 *lut = reinterpret_cast<float4 *>(smem);            // [S][256] : 4 heads
-    float *hist = smem + (size_t)S * kWords * 4;                // [S][4][256] (fixed-point counts)
-    const size_t both = max((size_t)2 * S * kWords * 4, (size_t)kWarps * kRep * kDim);
-    float *q_s = smem + both;                                   // [4][128]
+    float *hist = smem + (size_t)S * kWords * 4;                // [S][4][256] (fixed-point counts of the current segment)
+    float *hist_f = hist + (size_t)S * kWords * 4;              // [S][4][256] (weights of the finished segments)
+    const size_t both = max((size_t)3 * S * kWords * 4, (size_t)kWarps * kRep * kDim);  // floats
+    float *q_s = smem + both;                                   // [128][4]: channel-major, one 16-byte read gives 4 heads
     float *red = q_s + kRep * kDim;                             // [warps][8] : max x4, sum x4
-    unsigned char *kstage = reinterpret_cast<unsigned char *>(red + kWarps * 8);  // staged K codes (+32 B slack)
-    unsigned char *vstage = kstage + kStageBytes + 32;                            // staged V codes
     __shared__ float m_s[kRep];
 
     const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -53,43 +94,40 @@ attn_fullwidth_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
     const int Hq = Hkv * kRep;
 
     for (int i = tid; i < kRep * kDim; i += kThreads)
-        q_s[i] = __half2float(q[((size_t)b * Hq + h * kRep + (i >> 7)) * kDim + (i & 127)]);
+        q_s[(i & 127) * kRep + (i >> 7)] = __half2float(q[((size_t)b * Hq + h * kRep + (i >> 7)) * kDim + (i & 127)]);
     unsigned int *hist_u = reinterpret_cast<unsigned int *>(hist);
-    for (int i = tid; i < S * kWords * 4; i += kThreads) hist_u[i] = 0u;
+    for (int i = tid; i < S * kWords * 4; i += kThreads) {
+        hist_u[i] = 0u;
+        hist_f[i] = 0.0f;
+    }
     __syncthreads();
 
-    // ---- score table: a warp takes 8 codewords at a time (their loads travel together), lanes split
-    //      the 128 channels, partial dots are folded with shuffles ----------------------------------------
-    {
-        float qa[kRep][4];  // this lane's query channels 2l, 2l+1, 64+2l, 64+2l+1 of every head
+    // ---- score table: one thread per codeword; its 256 bytes travel as 2 x 8 16-byte loads, the query
+    //      comes from shared memory (every thread reads the same address: a broadcast) -----------------------
+    for (int w0 = tid; w0 < S * kWords; w0 += kThreads) {
+        const uint4 *row = reinterpret_cast<const uint4 *>(ktab + ((size_t)h * S * kWords + w0) * kDim);
+        float dot[kRep] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+        uint4 raw[8];
 #pragma unroll
-        for (int r = 0; r < kRep; ++r) {
-            qa[r][0] = q_s[r * kDim + 2 * lane];
-            qa[r][1] = q_s[r * kDim + 2 * lane + 1];
-            qa[r][2] = q_s[r * kDim + 64 + 2 * lane];
-            qa[r][3] = q_s[r * kDim + 64 + 2 * lane + 1];
-        }
-        const __half2 *tab = reinterpret_cast<const __half2 *>(ktab + (size_t)h * S * kWords * kDim);
-        for (int w0 = warp * 8; w0 < S * kWords; w0 += kWarps * 8) {
-            __half2 lo2[8], hi2[8];
+        for (int i = 0; i < 8; ++i) raw[i] = __ldg(row + half * 8 + i);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                lo2[j] = tab[(size_t)(w0 + j) * (kDim / 2) + lane];
-                hi2[j] = tab[(size_t)(w0 + j) * (kDim / 2) + lane + 32];
-            }
+        for (int i = 0; i < 8; ++i) {  // (unrolled: raw[] must stay in registers)
+            const __half2 *hp = reinterpret_cast<const __half2 *>(&raw[i]);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float2 a = __half22float2(lo2[j]), c = __half22float2(hi2[j]);
-                float dot[kRep];
-#pragma unroll
-                for (int r = 0; r < kRep; ++r) {
-                    dot[r] = fmaf(qa[r][0], a.x, fmaf(qa[r][1], a.y, fmaf(qa[r][2], c.x, qa[r][3] * c.y)));
-#pragma unroll
-                    for (int off = 16; off >= 1; off >>= 1) dot[r] += __shfl_xor_sync(0xffffffffu, dot[r], off);
-                }
-                if (lane == 0) lut[w0 + j] = make_float4(dot[0], dot[1], dot[2], dot[3]);
+            for (int j = 0; j < 4; ++j) {
+                const float2 c = __half22float2(hp[j]);
+                const float4 qa = *reinterpret_cast<const float4 *>(q_s + (64 * half + 8 * i + 2 * j) * kRep);
+                const float4 qb = *reinterpret_cast<const float4 *>(q_s + (64 * half + 8 * i + 2 * j + 1) * kRep);
+                dot[0] = fmaf(qa.x, c.x, dot[0]); dot[1] = fmaf(qa.y, c.x, dot[1]);
+                dot[2] = fmaf(qa.z, c.x, dot[2]); dot[3] = fmaf(qa.w, c.x, dot[3]);
+                dot[0] = fmaf(qb.x, c.y, dot[0]); dot[1] = fmaf(qb.y, c.y, dot[1]);
+                dot[2] = fmaf(qb.z, c.y, dot[2]); dot[3] = fmaf(qb.w, c.y, dot[3]);
             }
         }
+        }
+        lut[w0] = make_float4(dot[0], dot[1], dot[2], dot[3]);
     }
     __syncthreads();
 
@@ -102,47 +140,30 @@ attn_fullwidth_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
     const int hi = min(lo + per, lo_all + n_all);
     const size_t row_base = ((size_t)b * Hkv + h) * (size_t)T_cap;
 
-    // Codes reach the lanes through shared memory: a chunk of the range is copied with coalesced 16-byte
-    // asynchronous copies (all in flight at once), then read byte-wise.  [begin, end) are byte offsets
-    // into the code array; the copy starts at the 16-byte boundary below `begin`.
-    const size_t total_bytes = (size_t)B * Hkv * (size_t)T_cap * S;
-    auto stage = [&](unsigned char *dst, const uint8_t *src, size_t begin, size_t end) -> int {
-        const size_t a0 = begin & ~(size_t)15;
-        const int units = (int)((end - a0 + 15) >> 4);
-        for (int u = tid; u < units; u += kThreads) {
-            const size_t off = a0 + (size_t)u * 16;
-            if (off + 16 <= total_bytes) {
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst + u * 16)), "l"(src + off));
-            } else {
-                for (int i = 0; i < 16 && off + i < total_bytes; ++i) dst[u * 16 + i] = src[off + i];
-            }
-        }
-        return (int)(begin - a0);
-    };
-    auto staged = [&]() {
-        asm volatile("cp.async.wait_all;" ::: "memory");
-        __syncthreads();
-    };
-    auto score = [&](const unsigned char *kc, float (&sc)[kRep]) {
+    constexpr int kBatch = WORDS == 1 ? 4 : WORDS == 2 ? 2 : 1;  // tokens whose code loads a thread keeps in flight together (the loop body stays small:
+                               // a larger, fully unrolled body was measured to stall on instruction fetch)
+    auto score = [&](uint32_t (&kc)[WORDS], float (&sc)[kRep]) {  // consumes kc
 #pragma unroll
         for (int r = 0; r < kRep; ++r) sc[r] = 0.0f;
         for (int s = 0; s < S; ++s) {
-            const float4 e = lut[s * kWords + kc[s]];
+            const float4 e = lut[s * kWords + next_code(kc)];
             sc[0] += e.x; sc[1] += e.y; sc[2] += e.z; sc[3] += e.w;
         }
     };
-    const int chunk_tokens = kStageBytes / S;
 
     // ---- pass 1: exact maximum of every head over the range ------------------------------------------
     float mx[kRep] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    for (int c0 = lo; c0 < hi; c0 += chunk_tokens) {
-        const int c1 = min(c0 + chunk_tokens, hi);
-        __syncthreads();  // previous chunk fully consumed
-        const int koff = stage(kstage, kcodes, (row_base + c0) * S, (row_base + c1) * S);
-        staged();
-        for (int t = c0 + tid; t < c1; t += kThreads) {
+    for (int t0 = lo + tid; t0 < hi; t0 += kBatch * kThreads) {
+        uint32_t kc[kBatch][WORDS];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {  // the loads of a batch travel together; tokens past the end repeat the last one
+            const int t = min(t0 + j * kThreads, hi - 1);
+            load_codes<WORDS, WIDE>(kcodes + (row_base + t) * S, S, kc[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
             float sc[kRep];
-            score(kstage + koff + (size_t)(t - c0) * S, sc);
+            score(kc[j], sc);
 #pragma unroll
             for (int r = 0; r < kRep; ++r) mx[r] = fmaxf(mx[r], sc[r]);
         }
@@ -165,40 +186,61 @@ attn_fullwidth_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
     for (int r = 0; r < kRep; ++r) m[r] = m_s[r];
 
     // ---- pass 2: softmax weights into the per-stage code histograms ------------------------------------
-    unsigned int lsum_u[kRep] = {0u, 0u, 0u, 0u};  // at most 32 tokens per thread: fits
-    for (int c0 = lo; c0 < hi; c0 += chunk_tokens) {
-        const int c1 = min(c0 + chunk_tokens, hi);
-        __syncthreads();
-        const int koff = stage(kstage, kcodes, (row_base + c0) * S, (row_base + c1) * S);
-        const int voff = stage(vstage, vcodes, (row_base + c0) * S, (row_base + c1) * S);
-        staged();
-        for (int t = c0 + tid; t < c1; t += kThreads) {
-            float sc[kRep];
-            score(kstage + koff + (size_t)(t - c0) * S, sc);
-            unsigned int p[kRep];
+    unsigned int lsum_u[kRep] = {0u, 0u, 0u, 0u};  // per segment: at most 16 tokens of weight <= 2^18 per thread
+    auto add_weights = [&](const float (&sc)[kRep], uint32_t (&vc)[WORDS]) {  // consumes vc
+        unsigned int p[kRep];
 #pragma unroll
-            for (int r = 0; r < kRep; ++r) {
-                p[r] = __float2uint_rn(__expf(sc[r] - m[r]) * kWeightOne);
-                lsum_u[r] += p[r];
+        for (int r = 0; r < kRep; ++r) {
+            p[r] = __float2uint_rn(__expf(sc[r] - m[r]) * kWeightOne);
+            lsum_u[r] += p[r];
+        }
+        for (int s = 0; s < S; ++s) {
+            unsigned int *bin = hist_u + (size_t)s * kRep * kWords + next_code(vc);  // [stage][head][code]: bank = code % 32
+#pragma unroll
+            for (int r = 0; r < kRep; ++r) atomicAdd(bin + r * kWords, p[r]);
+        }
+    };
+    float lsum_f[kRep] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int seg = lo; seg < hi; seg += kSegmentTokens) {
+        const int seg_hi = min(seg + kSegmentTokens, hi);
+        for (int t0 = seg + tid; t0 < seg_hi; t0 += kBatch * kThreads) {
+            uint32_t kc[kBatch][WORDS], vc[kBatch][WORDS];
+#pragma unroll
+            for (int j = 0; j < kBatch; ++j) {
+                const int t = min(t0 + j * kThreads, seg_hi - 1);
+                load_codes<WORDS, WIDE>(kcodes + (row_base + t) * S, S, kc[j]);
+                load_codes<WORDS, WIDE>(vcodes + (row_base + t) * S, S, vc[j]);
             }
-            const unsigned char *vc = vstage + voff + (size_t)(t - c0) * S;
-            for (int s = 0; s < S; ++s) {
-                unsigned int *bin = hist_u + (size_t)s * kRep * kWords + vc[s];  // [stage][head][code]: bank = code % 32
 #pragma unroll
-                for (int r = 0; r < kRep; ++r) atomicAdd(bin + r * kWords, p[r]);
+            for (int j = 0; j < kBatch; ++j) {
+                if (t0 + j * kThreads >= seg_hi) break;
+                float sc[kRep];
+                score(kc[j], sc);
+                add_weights(sc, vc[j]);
             }
         }
+        __syncthreads();  // the segment's weights are all in the bins: fold them into the float histogram
+        for (int i = tid; i < S * kWords * 4; i += kThreads) {
+            hist_f[i] += (float)hist_u[i] * (1.0f / kWeightOne);
+            hist_u[i] = 0u;
+        }
+#pragma unroll
+        for (int r = 0; r < kRep; ++r) {
+            lsum_f[r] += (float)lsum_u[r] * (1.0f / kWeightOne);
+            lsum_u[r] = 0u;
+        }
+        __syncthreads();
     }
 #pragma unroll
     for (int r = 0; r < kRep; ++r) {
-        float lsum = (float)lsum_u[r] * (1.0f / kWeightOne);
+        float lsum = lsum_f[r];
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
         if (lane == 0) red[warp * 8 + 4 + r] = lsum;
     }
     __syncthreads();
 
-    // ---- acc = hist x V codebook: thread = (8-channel chunk, one of 16 slices of the code words) -------
+    // ---- acc = hist x V codebook: thread = (8-channel chunk, one of 32 slices of the code words) -------
     const int chunk = tid & 15, slice = tid >> 4;
     float acc[kRep][8];
 #pragma unroll
@@ -207,11 +249,10 @@ attn_fullwidth_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
         for (int i = 0; i < 8; ++i) acc[r][i] = 0.0f;
     const int words = S * kWords;
     const uint4 *vt = reinterpret_cast<const uint4 *>(vtab + (size_t)h * words * kDim) + chunk;
-#pragma unroll 8
-    for (int w = slice; w < words; w += 16) {
-        const unsigned int *cnt = hist_u + (size_t)(w >> 8) * kRep * kWords + (w & 255);
-        const float4 wgt = make_float4((float)cnt[0] * (1.0f / kWeightOne), (float)cnt[kWords] * (1.0f / kWeightOne),
-                                       (float)cnt[2 * kWords] * (1.0f / kWeightOne), (float)cnt[3 * kWords] * (1.0f / kWeightOne));
+#pragma unroll 4
+    for (int w = slice; w < words; w += kSlices) {
+        const float *cnt = hist_f + (size_t)(w >> 8) * kRep * kWords + (w & 255);
+        const float4 wgt = make_float4(cnt[0], cnt[kWords], cnt[2 * kWords], cnt[3 * kWords]);
         const uint4 raw = __ldg(vt + (size_t)w * (kDim / 8));
         const __half2 *hp = reinterpret_cast<const __half2 *>(&raw);
 #pragma unroll
@@ -223,13 +264,13 @@ attn_fullwidth_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
             acc[3][2 * i] = fmaf(wgt.w, v.x, acc[3][2 * i]); acc[3][2 * i + 1] = fmaf(wgt.w, v.y, acc[3][2 * i + 1]);
         }
     }
-    // fold the 16 slices: the two slices of a warp by shuffle, the 8 warps through shared memory
+    // fold the slices: the two slices of a warp by shuffle, the warps through shared memory
 #pragma unroll
     for (int r = 0; r < kRep; ++r)
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[r][i] += __shfl_xor_sync(0xffffffffu, acc[r][i], 16);
-    __syncthreads();  // histogram fully read: its storage and the score table's are free
-    float *fold = smem;  // [8 warps][4][128]  (the launcher sizes the table area for this)
+    __syncthreads();  // histograms fully read: their storage and the score table's are free
+    float *fold = smem;  // [warps][4][128]  (the launcher sizes the table area for this)
     if (lane < 16) {
 #pragma unroll
         for (int r = 0; r < kRep; ++r)
@@ -238,19 +279,32 @@ attn_fullwidth_kernel(const __half *__restrict__ q, const uint8_t *__restrict__ 
     }
     __syncthreads();
     const int64_t rows = (int64_t)B * Hq;
-    for (int o = tid; o < kRep * (kDim + 2); o += kThreads) {
-        const int r = o / (kDim + 2), col = o % (kDim + 2);
-        float v;
-        if (col == 0) {
-            v = m[r];
-        } else if (col == 1) {
-            v = 0.0f;
-            for (int w = 0; w < kWarps; ++w) v += red[w * 8 + 4 + r];
-        } else {
-            v = 0.0f;
-            for (int w = 0; w < kWarps; ++w) v += fold[(w * kRep + r) * kDim + col - 2];
+    for (int o = tid; o < kRep * kDim; o += kThreads) {
+        const int r = o >> 7, dim = o & 127;
+        float lsum = 0.0f, asum = 0.0f;
+        for (int w = 0; w < kWarps; ++w) {
+            lsum += red[w * 8 + 4 + r];
+            asum += fold[(w * kRep + r) * kDim + dim];
         }
-        part[((int64_t)split * rows + (int64_t)b * Hq + h * kRep + r) * (kDim + 2) + col] = v;
+        const int64_t row = (int64_t)b * Hq + h * kRep + r;
+        if (splits == 1) {  // the whole pair was handled here: this is the result
+            if (out) out[row * kDim + dim] = __float2half_rn(lsum > 0.0f ? asum / lsum : 0.0f);
+            if (state_out) {
+                float *dst = state_out + row * (kDim + 2);
+                if (dim == 0) {
+                    dst[0] = m[r];  // -inf for an empty range
+                    dst[1] = lsum;
+                }
+                dst[2 + dim] = asum;
+            }
+        } else {
+            float *dst = part + ((int64_t)split * rows + row) * (kDim + 2);
+            if (dim == 0) {
+                dst[0] = m[r];
+                dst[1] = lsum;
+            }
+            dst[2 + dim] = asum;
+        }
     }
 }
 
@@ -261,22 +315,34 @@ bool attn_fullwidth_supported(int Hq, int Hkv, int D, int G, int S, int K) {
            Hq == Hkv * fullwidth::kRep;
 }
 
+// Blocks per (batch row, KV head) pair.  Every block pays the table work (2 x S x 64 KB), so a pair is split
+// only as far as idle SMs make it worthwhile.
+int attn_fullwidth_splits(int B, int Hkv, int64_t T_cap, int sms) {
+    const int64_t pairs = (int64_t)B * Hkv;
+    int64_t splits = pairs > 0 ? sms / pairs : 1;  // 1 as soon as the pairs fill more than half of the SMs
+    if (splits * 1024 > T_cap) splits = (T_cap + 1023) / 1024;
+    if (splits < 1) splits = 1;
+    return (int)splits;
+}
+
 int attn_fullwidth_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
-                            const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, float *part, int B,
-                            int Hq, int Hkv, int S, int64_t T_cap, int splits, cudaStream_t stream) {
+                            const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, float *part,
+                            __half *out, float *state_out, int B, int Hq, int Hkv, int S, int64_t T_cap, int splits,
+                            cudaStream_t stream) {
     (void)Hq;
-    const size_t tables = (size_t)S * fullwidth::kWords * 4 * sizeof(float);
-    size_t both = 2 * tables;  // score table + histogram; later reused to fold 8 warps x 4 heads x 128 channels
-    if (both < (size_t)fullwidth::kWarps * fullwidth::kRep * fullwidth::kDim * sizeof(float))
-        both = (size_t)fullwidth::kWarps * fullwidth::kRep * fullwidth::kDim * sizeof(float);
-    const size_t smem = both + (fullwidth::kRep * fullwidth::kDim + fullwidth::kWarps * 8) * sizeof(float) +
-                        2 * (fullwidth::kStageBytes + 32);
-    auto kernel = fullwidth::attn_fullwidth_kernel;
+    size_t both = (size_t)3 * S * fullwidth::kWords * 4 * sizeof(float);  // score table + two histograms ...
+    const size_t fold = (size_t)fullwidth::kWarps * fullwidth::kRep * fullwidth::kDim * sizeof(float);  // ... later the fold area
+    if (both < fold) both = fold;
+    const size_t smem = both + (fullwidth::kRep * fullwidth::kDim + fullwidth::kWarps * 8) * sizeof(float);
+    auto kernel = S == 2 ? fullwidth::attn_fullwidth_kernel<1, 2> : S == 4 ? fullwidth::attn_fullwidth_kernel<1, 4>
+                : S == 8 ? fullwidth::attn_fullwidth_kernel<2, 8> : S == 16 ? fullwidth::attn_fullwidth_kernel<4, 16>
+                : S < 4 ? fullwidth::attn_fullwidth_kernel<1, 0> : S < 8 ? fullwidth::attn_fullwidth_kernel<2, 0>
+                        : fullwidth::attn_fullwidth_kernel<4, 0>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((unsigned)splits, (unsigned)Hkv, (unsigned)B);
-    kernel<<<grid, fullwidth::kThreads, smem, stream>>>(q, kcodes, vcodes, ktab, vtab, seq_start, seq_end, part, B, Hkv, S,
-                                                       T_cap, splits);
+    kernel<<<grid, fullwidth::kThreads, smem, stream>>>(q, kcodes, vcodes, ktab, vtab, seq_start, seq_end, part, out, state_out,
+                                                       B, Hkv, S, T_cap, splits);
     return launch_status();
 }
 

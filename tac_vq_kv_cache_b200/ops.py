@@ -192,6 +192,35 @@ def codeword_grad(codes: torch.Tensor, grad_out: torch.Tensor, table_shape, *, d
     return grad
 
 
+def _attn_geometry(q, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end):
+    """Check dtypes and the full shapes of one attention call; -> (b, hq, hkv, dim, g, s, k, t_cap)."""
+    if q.dtype != torch.float16 or q.ndim != 3:
+        raise ValueError("q must be fp16 [B,Hq,D]")
+    b, hq, dim = map(int, q.shape)
+    for name, codes in (("kcodes", kcodes), ("vcodes", vcodes)):
+        if codes.dtype != torch.uint8 or codes.ndim != 5 or not codes.is_contiguous():
+            raise ValueError(f"{name} must be contiguous uint8 [B,Hkv,T,S,G]")
+    if kcodes.shape != vcodes.shape:
+        raise ValueError("kcodes and vcodes must have equal shapes")
+    cb, hkv, t_cap, s, g = map(int, kcodes.shape)
+    if cb != b:
+        raise ValueError("q and the codes differ in batch size")
+    if g == 0 or dim % g != 0 or hkv == 0 or hq % hkv != 0:
+        raise ValueError("head or group counts do not divide")
+    for name, tab in (("ktab_f16", ktab_f16), ("vtab_f16", vtab_f16)):
+        if tab.dtype != torch.float16 or tab.ndim != 5:
+            raise ValueError(f"{name} must be fp16 [Hkv,S,G,K,d]")
+        if tuple(tab.shape[:3]) != (hkv, s, g) or int(tab.shape[4]) != dim // g:
+            raise ValueError(f"{name} must be [Hkv,S,G,K,d] = [{hkv},{s},{g},K,{dim // g}], got {tuple(tab.shape)}")
+    k = int(ktab_f16.shape[3])
+    if int(vtab_f16.shape[3]) != k:
+        raise ValueError("key and value tables differ in codebook size")
+    for name, idx in (("seq_start", seq_start), ("seq_end", seq_end)):
+        if idx is not None and (idx.dtype != torch.int32 or idx.numel() != b or not idx.is_contiguous()):
+            raise ValueError(f"{name} must be contiguous int32 [B]")
+    return b, hq, hkv, dim, g, s, k, t_cap
+
+
 @functools.lru_cache(maxsize=256)
 def attn_workspace_bytes(b: int, hq: int, hkv: int, dim: int, g: int, s: int) -> int:
     return int(_lib.load().tacvq_attn_workspace_bytes(b, hq, hkv, dim, g, s))
@@ -221,32 +250,28 @@ def attn_decode(
     branch does; ``q`` is then the query already rotated at its own position.
     """
     device = _require_cuda(q, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, workspace, rope)
-    if q.dtype != torch.float16 or q.ndim != 3:
-        raise ValueError("q must be fp16 [B,Hq,D]")
+    b, hq, hkv, dim, g, s, k, t_cap = _attn_geometry(q, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end)
     q = q.contiguous()
-    b, hq, dim = map(int, q.shape)
-    if kcodes.shape != vcodes.shape or kcodes.ndim != 5 or not kcodes.is_contiguous() or not vcodes.is_contiguous():
-        raise ValueError("codes must be contiguous uint8 [B,Hkv,T,S,G] with equal shapes")
-    _b, hkv, t_cap, s, g = map(int, kcodes.shape)
-    k = int(ktab_f16.shape[-2])
+    ktab_f16, vtab_f16 = ktab_f16.contiguous(), vtab_f16.contiguous()  # bound to locals: they outlive the launch below
     need = attn_workspace_bytes(b, hq, hkv, dim, g, s)
     if need == 0:
         raise ValueError("attention geometry not supported")
     if workspace is None:
         workspace = torch.empty(need, dtype=torch.uint8, device=device)
-    for name, idx in (("seq_start", seq_start), ("seq_end", seq_end)):
-        if idx is not None and (idx.dtype != torch.int32 or idx.numel() != b or not idx.is_contiguous()):
-            raise ValueError(f"{name} must be contiguous int32 [B]")
     if want_out and out is None:
         out = torch.empty(b, hq, dim, dtype=torch.float16, device=device)
     if want_state and state is None:
         state = torch.empty(b, hq, dim + 2, dtype=torch.float32, device=device)
+    if out is not None and (out.dtype != torch.float16 or tuple(out.shape) != (b, hq, dim) or not out.is_contiguous()):
+        raise ValueError("out must be contiguous fp16 [B,Hq,D]")
+    if state is not None and (state.dtype != torch.float32 or tuple(state.shape) != (b, hq, dim + 2) or not state.is_contiguous()):
+        raise ValueError("state must be contiguous fp32 [B,Hq,2+D]")
     if rope is not None:
         if rope.dtype != torch.float16 or tuple(rope.shape) != (t_cap, 2, dim // 2) or not rope.is_contiguous():
             raise ValueError("rope must be contiguous fp16 [T_cap, 2, D/2] (cosines, sines)")
         with _on(device):
             status = _lib.load().tacvq_attn_decode_rotary(
-                _ptr(q), _ptr(kcodes), _ptr(vcodes), _ptr(ktab_f16.contiguous()), _ptr(vtab_f16.contiguous()), _ptr(rope),
+                _ptr(q), _ptr(kcodes), _ptr(vcodes), _ptr(ktab_f16), _ptr(vtab_f16), _ptr(rope),
                 _ptr(seq_start), _ptr(seq_end), _ptr(workspace), workspace.numel() * workspace.element_size(), _ptr(out),
                 _ptr(state), b, hq, hkv, dim, g, s, k, t_cap, _stream(device),
             )
@@ -254,7 +279,7 @@ def attn_decode(
         return out, state
     with _on(device):
         status = _lib.load().tacvq_attn_decode(
-            _ptr(q), _ptr(kcodes), _ptr(vcodes), _ptr(ktab_f16.contiguous()), _ptr(vtab_f16.contiguous()), _ptr(seq_start),
+            _ptr(q), _ptr(kcodes), _ptr(vcodes), _ptr(ktab_f16), _ptr(vtab_f16), _ptr(seq_start),
             _ptr(seq_end), _ptr(workspace), workspace.numel() * workspace.element_size(), _ptr(out), _ptr(state), b, hq, hkv,
             dim, g, s, k, t_cap, _stream(device),
         )
@@ -320,11 +345,14 @@ def attn_decode_static(
     tensors = [t for t in (q, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, out, state) if t is not None]
     if not all(t.is_contiguous() for t in tensors) or (out is None and state is None):
         raise ValueError("all tensors must be contiguous and at least one of out/state must be given")
-    b, hq, dim = map(int, q.shape)
-    _b, hkv, t_cap, s, g = map(int, kcodes.shape)
+    b, hq, hkv, dim, g, s, k, t_cap = _attn_geometry(q, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end)
+    if out is not None and (out.dtype != torch.float16 or tuple(out.shape) != (b, hq, dim)):
+        raise ValueError("out must be fp16 [B,Hq,D]")
+    if state is not None and (state.dtype != torch.float32 or tuple(state.shape) != (b, hq, dim + 2)):
+        raise ValueError("state must be fp32 [B,Hq,2+D]")
     with _on(device):
         status = _lib.load().tacvq_attn_decode_static(
             _ptr(q), _ptr(kcodes), _ptr(vcodes), _ptr(ktab_f16), _ptr(vtab_f16), _ptr(seq_start), _ptr(seq_end), _ptr(out),
-            _ptr(state), b, hq, hkv, dim, g, s, int(ktab_f16.shape[-2]), t_cap, _stream(device),
+            _ptr(state), b, hq, hkv, dim, g, s, k, t_cap, _stream(device),
         )
     _lib.check("tacvq_attn_decode_static", status)

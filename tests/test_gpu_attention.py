@@ -161,6 +161,40 @@ def test_benchmark_size_32k_context(device):
     assert torch.equal(out, again)  # deterministic
 
 
+def test_full_width_codebooks_at_the_all_layer_configuration(device):
+    """Two additive 256 x 128 codebooks at batch 16, 32 query / 8 KV heads, 16384 tokens: one layer of the
+    all-layer configuration (every (row, head) pair is one block that writes its result itself)."""
+    work = _workload(8604, 16, 32, 8, 16384, 1, 2, 128, [0.1, 0.1])
+    out, state = _run(device, work, want_state=True)
+    want, want_state = C.attention(*work)
+    _check(out, want)
+    _check_state(state.cpu(), want_state)
+    again, _ = _run(device, work)
+    assert torch.equal(out, again)
+
+
+def test_full_width_codebooks_split_ranges_and_deep_ladders(device):
+    """Few pairs (several blocks per pair, merged afterwards), a ragged window, and the reference's own depth-16 ladder."""
+    work = _workload(8605, 2, 8, 2, 9000, 1, 2, 128, [0.1, 0.1])
+    out, _ = _run(device, work, [100, 0], [9000, 8500])
+    want, _ = C.attention(*work, [100, 0], [9000, 8500])
+    _check(out, want)
+    work = _workload(8606, 3, 12, 3, 2100, 1, 16, 128, [0.1 * 0.7**s for s in range(16)])
+    out, _ = _run(device, work, [0, 5, 2100], [2100, 1999, 2100])  # the last row is empty
+    want, _ = C.attention(*work, [0, 5, 2100], [2100, 1999, 2100])
+    _check(out, want)
+    assert bool((out[2] == 0).all())
+
+
+def test_sliding_window_launch_of_the_benchmark(device):
+    """The benchmark's own window case: batch 8, the last 4096 of 32768 stored tokens visible."""
+    work = _workload(8607, 8, 32, 8, 32768, 16, 2, 8)
+    start, end = [32768 - 4096] * 8, [32768] * 8
+    out, _ = _run(device, work, start, end)
+    want, _ = C.attention(*work, start, end)
+    _check(out, want)
+
+
 def test_attention_argument_errors(device):
     from tac_vq_kv_cache_b200 import _lib
 

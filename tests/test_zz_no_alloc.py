@@ -28,7 +28,15 @@ def _workload(device, seed, b, hq, hkv, t, groups, stages, sub):
     return [x.to(device) for x in (q, kcodes, vcodes, ktab, vtab)]
 
 
-@pytest.mark.parametrize("geometry", [(2, 8, 2, 1500, 16, 2, 8), (2, 4, 2, 700, 1, 2, 128)])
+@pytest.mark.parametrize(
+    "geometry",
+    [
+        (2, 8, 2, 1500, 16, 2, 8),   # the specialised scan (16 groups x 2 stages)
+        (2, 4, 2, 700, 1, 2, 128),   # full-width codebooks (histogram kernel)
+        (2, 4, 2, 500, 16, 1, 8),    # one-stage grouped codebooks (two-pass kernel)
+        (2, 16, 2, 333, 8, 2, 8),    # 8 query heads per KV head, head_dim 64 (generic kernel)
+    ],
+)
 def test_static_scratch_entry_point_matches_the_ordinary_one(device, geometry):
     from tac_vq_kv_cache_b200 import _lib, ops
 
@@ -36,17 +44,27 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(device, geometry):
     b, hq, hkv, t = geometry[:4]
     dim = geometry[4] * geometry[6]
     start = torch.tensor([0, 100], dtype=torch.int32, device=device)
-    end = torch.tensor([t, t - 33], dtype=torch.int32, device=device)
+    ends = ([t, t - 33], [t, 100])  # the second call's second row is empty (start == end)
     for call in range(2):  # the array keeps the first call's contents: the second call must not care
+        end = torch.tensor(ends[call], dtype=torch.int32, device=device)
         work = _workload(device, 100 + call, *geometry)
         want_out, want_state = ops.attn_decode(*work, start, end, want_state=True)
         out = torch.empty(b, hq, dim, dtype=torch.float16, device=device)
         state = torch.empty(b, hq, dim + 2, dtype=torch.float32, device=device)
+        torch.cuda.synchronize()
+        # the first call on a device is the set-up call (the runtime loads the kernels and the array, the
+        # address is looked up); from the second call on, nothing is allocated anywhere
+        before = (torch.cuda.memory_allocated(device), torch.cuda.mem_get_info(device)[0])
         ops.attn_decode_static(*work, start, end, out, state)
         torch.cuda.synchronize()
+        after = (torch.cuda.memory_allocated(device), torch.cuda.mem_get_info(device)[0])
+        if call == 1:
+            assert after[0] == before[0] and after[1] >= before[1], (before, after)
         # same kernels, same arithmetic: the results are identical, not merely within tolerance
         assert torch.equal(out, want_out)
         assert torch.equal(state, want_state)
+        if call == 1:
+            assert bool((out[1] == 0).all()) and bool((state[1, :, 1] == 0).all())
 
 
 def test_static_scratch_entry_point_refuses_oversized_geometries(device):
