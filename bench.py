@@ -2,21 +2,25 @@
 """Benchmark of the VQ-KV hot path: decode-step attention over packed codes at 32k context.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload decode32k|cq32layers|seqsplit131k]
 
-One "step" is one decode step of one layer: batch 8, 32 query / 8 KV heads, head_dim 128,
-32768 stored tokens per sequence, K and V held as 2-stage x 16-group uint8 codes with fp16
-tables (the "packed-code decode attention" configuration).  At N > 1 every rank runs its own
-layer (weak scaling by layer, no collective on the data path).  Prints ONE JSON line.
-
-Keys beyond the basic contract:
-  roofline      dominant kernel (the code scan) against the measured HBM copy bandwidth
-  cpu_baseline  the CPU oracle timed on a bounded sample of the same workload (rank 0, N = 1)
-  e2e           the same metric through VQCodeCache with pinned host buffers: per step the new
-                token's q/k/v rows go host->device, k/v are encoded and appended in place, the
-                step attends, and the result returns device->host
-  encode        encode throughput of the 2-stage layer configuration (K and V, fp16 [4,8,8192,128])
-`--impl reference` times the reference's CPU decode path (dense fp16 window + SDPA, as its
-attention adapter does) restated in oracle/, on the host cores.
+decode32k (default, the headline): one "step" is one decode step of one layer: batch 8, 32 query /
+8 KV heads, head_dim 128, 32768 stored tokens per sequence, K and V held as 2-stage x 16-group uint8
+codes with fp16 tables.  At N > 1 every rank runs its own layer (weak scaling by layer, no collective
+on the data path).  Prints ONE JSON line.  Keys beyond the basic contract:
+  roofline      the code scan against the measured HBM copy bandwidth
+  cpu_baseline  the reference's CPU decode path (restated in oracle/) on whole steps (rank 0, N = 1)
+  e2e           the same metric through one C-ABI call per step with HOST buffers: the new token's
+                q/k/v rows go host->device, k/v are encoded and appended in place, the step attends,
+                and the result returns device->host
+  encode        encode throughput (K and V of one 2-stage layer; full-width tables) with its own CPU
+                baseline and compute roofline
+cq32layers: all 32 layers of the full-width configuration (two additive 256 x 128 codebooks, batch 16,
+16384 tokens), layers sharded over the ranks; a step is one layer: encode K and V, then one decode step.
+seqsplit131k: one 131072-token sequence split over the ranks, partial softmax states all-gathered
+(NCCL) and merged; scan, exchange and merge are timed separately.
+`--impl reference` times the reference's CPU decode path (dense fp16 window, repeat_kv, SDPA, as its
+attention adapter does; restated in oracle/) on whole steps of the same configuration, all host threads.
 """
 
 from __future__ import annotations
@@ -41,8 +45,15 @@ BATCH, Q_HEADS, KV_HEADS, DIM, GROUPS, STAGES, SUB = 8, 32, 8, 128, 16, 2, 8
 CONTEXT = 32768
 CODE_SETS = 4  # rotated between steps: 4 x 134 MB of codes > 126 MB of L2
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
 METRIC = "vq_kv_decode_attention_tokens_per_s_at_32k_ctx"
 UNIT = "decode tokens/s (per layer; batch 8, 32768-token context, GQA 32/8, 2x16 code bytes per token and side)"
+WORKLOAD = ("packed-code decode attention, one layer per GPU: batch 8, 32 query / 8 KV heads, head_dim 128, 32768-token context, "
+            "K and V as GSRQ 2-stage x 16-group uint8 codes, fp16 tables, fp16 query scaled 1/sqrt(128)")
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of the scan kernel (one ncu capture of
+# this workload): the codes once, the score tables written by the prepare grid and read back, partial states
+SCAN_TRAFFIC_BYTES = 144_018_176
+FP32_FMA_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12  # 148 SMs x 128 lanes x 2 flop at the maximum SM clock
 
 
 def algorithmic_bytes(batch: int, context: int) -> int:
@@ -53,14 +64,23 @@ def algorithmic_bytes(batch: int, context: int) -> int:
     return codes + tables + io
 
 
-def hbm_peak() -> tuple[float, str]:
+def measured_peaks() -> dict:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
         try:
-            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+            data = json.loads(path.read_text())
+            return {"hbm": float(data["hbm_gbs"]), "bf16": float(data["bf16_tflops"]), "kind": "measured"}
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback"
+    return {"hbm": FALLBACK_HBM_GBS, "bf16": FALLBACK_BF16_TFLOPS, "kind": "fallback"}
+
+
+def decode_config(world: int) -> dict:
+    return {
+        "workload": WORKLOAD, "batch": BATCH, "context": CONTEXT, "q_heads": Q_HEADS, "kv_heads": KV_HEADS, "head_dim": DIM,
+        "stages": STAGES, "groups": GROUPS, "parallelism": f"layer-sharded x{world} (no data-path collective)",
+        "l2": f"{CODE_SETS} code sets rotated between steps ({CODE_SETS * 2 * BATCH * KV_HEADS * CONTEXT * 32 // 2**20} MiB > 126 MB L2)",
+    }
 
 
 class ClockSampler:
@@ -112,17 +132,31 @@ def make_tables(gen: torch.Generator) -> tuple[torch.Tensor, torch.Tensor]:
     return one(), one()
 
 
+def dist_env():
+    return int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def timed(fn, reps: int, device) -> float:
+    """Milliseconds per call of ``fn`` over ``reps`` back-to-back calls (CUDA events on the current stream)."""
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    start.record()
+    for i in range(reps):
+        fn(i)
+    end.record()
+    torch.cuda.synchronize(device)
+    return start.elapsed_time(end) / reps
+
+
 # ------------------------------------------------------------------------------------------- ours
 
 
-def run_ours(args) -> dict:
+def run_decode32k(args) -> dict:
     from tac_vq_kv_cache_b200 import _lib, ops
     from tac_vq_kv_cache_b200.code_cache import VQCodeCache
 
     _lib.load()  # raises if the CUDA library is missing: there is no fallback to measure
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world, rank, local = dist_env()
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device for --impl ours")
     torch.cuda.set_device(local)
@@ -137,39 +171,15 @@ def run_ours(args) -> dict:
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     gen = torch.Generator().manual_seed(8601 + rank)  # rank r holds layer r
     ktab, vtab = (t.to(device) for t in make_tables(gen))
-    if args.encode_only:  # profiler case: the 2-stage layer encode alone (one K tensor, reduced batch)
-        rows = torch.randn(2, KV_HEADS, 8192, DIM, generator=gen).half().to(device)
-        codes = torch.empty(2, KV_HEADS, 8192, STAGES, GROUPS, dtype=torch.uint8, device=device)
-        for _ in range(args.warmup + args.steps):
-            ops.encode(rows, ktab, codes=codes)
-        torch.cuda.synchronize(device)
-        return {"encode_only": True, "rows": 2 * 8192, "steps": args.steps}
-    if args.decode_only:  # profiler case: rebuild fp16 rows from the 2-stage codes of one layer (batch 8 x 8192 tokens)
-        pgen = torch.Generator(device=device).manual_seed(8601)
-        codes = torch.randint(0, 256, (BATCH, KV_HEADS, 8192, STAGES, GROUPS), dtype=torch.uint8, device=device, generator=pgen)
-        for _ in range(args.warmup + args.steps):
-            ops.decode(codes, ktab, torch.float16)
-        torch.cuda.synchronize(device)
-        return {"decode_only": True, "tokens": 8192, "steps": args.steps}
-    if args.encode_wide_only:  # profiler case: two full-width codebooks (1 group x 2 stages x 128), reduced batch
-        rows = torch.randn(2, KV_HEADS, 8192, DIM, generator=gen).half().to(device)
-        wide = (torch.randn(KV_HEADS, 2, 1, 256, DIM, generator=gen) * 0.1).half().to(device)
-        codes = torch.empty(2, KV_HEADS, 8192, 2, 1, dtype=torch.uint8, device=device)
-        for _ in range(args.warmup + args.steps):
-            ops.encode(rows, wide, codes=codes)
-        torch.cuda.synchronize(device)
-        return {"encode_wide_only": True, "rows": 2 * 8192, "steps": args.steps}
-    if args.rotary_only:  # profiler case: rotary attention at batch 8 x 8192 tokens (benchmark geometry, shorter context)
-        pgen = torch.Generator(device=device).manual_seed(8601)
-        kc, vc = (torch.randint(0, 256, (BATCH, KV_HEADS, 8192, STAGES, GROUPS), dtype=torch.uint8, device=device, generator=pgen) for _ in range(2))
-        query = (torch.randn(BATCH, Q_HEADS, DIM, device=device, generator=pgen) / DIM**0.5).half()
-        rope = ops.rope_table(8192, DIM, 1.0e6, device)
-        for _ in range(args.warmup + args.steps):
-            ops.attn_decode(query, kc, vc, ktab, vtab, rope=rope)
-        torch.cuda.synchronize(device)
-        return {"rotary_only": True, "tokens": 8192, "steps": args.steps}
     dgen = torch.Generator(device=device).manual_seed(8601 + rank)
     code_sets = [
         tuple(torch.randint(0, 256, (BATCH, KV_HEADS, CONTEXT, STAGES, GROUPS), dtype=torch.uint8, device=device, generator=dgen) for _ in range(2))
@@ -188,221 +198,343 @@ def run_ours(args) -> dict:
     barrier()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     clocks = ClockSampler(local)
-    clocks.__enter__()  # samples through the timed region and the end-to-end / encode sections after it
+    clocks.__enter__()  # samples through the timed region and the sections after it
     barrier()
     start.record()
     for i in range(args.steps):
         step(i)
     end.record()
     barrier()
-    elapsed_ms = start.elapsed_time(end)
-    if world > 1:
-        t = torch.tensor([elapsed_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-    ms_per_step = elapsed_ms / args.steps
+    ms_per_step = max_over_ranks(start.elapsed_time(end)) / args.steps
     value = BATCH * world / (ms_per_step * 1e-3)
 
-    peak, peak_kind = hbm_peak()
+    peaks = measured_peaks()
     alg = algorithmic_bytes(BATCH, CONTEXT)
     achieved = alg / (ms_per_step * 1e-3) / 1e9
     roofline = {
-        "bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-        "peak_source": f"{peak_kind} copy bandwidth", "algorithmic_bytes_per_launch": alg,
-        "kernel": "attn_gsrq_scan_kernel; the timed step also holds the prepare and merge launches (3 launches per step)",
-        "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+        "bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm"], "unit": "GB/s", "frac": round(achieved / peaks["hbm"], 4),
+        "peak_source": f"{peaks['kind']} copy bandwidth", "algorithmic_bytes_per_launch": alg,
+        "kernel": "attn_gsrq_scan_kernel; the timed step is its launch plus the prepare launch before it (2 launches per step)",
+        "traffic": SCAN_TRAFFIC_BYTES, "traffic_source": "one ncu capture of this workload (static figure, not re-measured per run)",
     }
 
-    # ---- end to end through the public API with host buffers -----------------------------------
-    e2e = None
-    encode = None
-    rotary = None
-    window = None
-    reconstruct = None
+    # ---- end to end: one C-ABI call per step with host buffers -----------------------------------
+    e2e_steps = 200
+    cache = VQCodeCache(ktab, vtab, batch=BATCH, max_tokens=CONTEXT + 2 * e2e_steps + 64, device=device)
+    cache.key[:, :, :CONTEXT].copy_(code_sets[0][0])
+    cache.value[:, :, :CONTEXT].copy_(code_sets[0][1])
+    cache.length = CONTEXT
+    hgen = torch.Generator().manual_seed(7)
+    nq, nk = BATCH * Q_HEADS * DIM, BATCH * KV_HEADS * DIM
+    # the new token's q, k and v rows, packed in one pinned buffer per step: one copy each way
+    host_rows = [torch.cat([(torch.randn(nq, generator=hgen) / DIM**0.5).half(), torch.randn(nk, generator=hgen).half(),
+                            torch.randn(nk, generator=hgen).half()]).pin_memory() for _ in range(4)]
+    host_out = torch.empty(BATCH, Q_HEADS, DIM, dtype=torch.float16).pin_memory()
+    for i in range(8):
+        cache.decode_step_host(host_rows[i % 4], host_out, Q_HEADS)  # waits for the result: the next token depends on it
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        cache.decode_step_host(host_rows[i % 4], host_out, Q_HEADS)
+    barrier()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
+    # host share: the same calls without waiting (enqueue cost only), then one wait
+    t0 = time.perf_counter()
+    for i in range(50):
+        cache.decode_step_host(host_rows[i % 4], host_out, Q_HEADS, synchronize=False)
+    enqueue_ms = (time.perf_counter() - t0) * 1e3 / 50
+    torch.cuda.synchronize(device)
+    e2e = {
+        "value": round(BATCH * world / (e2e_ms * 1e-3), 1), "unit": UNIT, "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps,
+        "h2d_bytes_per_step": host_rows[0].numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2,
+        "host_enqueue_ms_per_step": round(enqueue_ms, 4),
+        "api": "tacvq_decode_step_host through VQCodeCache.decode_step_host: copy the token's rows from pinned host memory, "
+               "encode + append K and V, attend, copy the result back, wait; code cache resident in HBM",
+    }
+    del cache
+
+    extras = {}
     cpu = None
-    extras = not args.kernel_only
-    if extras and (rank == 0 or world > 1):
-        e2e_steps = max(10, min(args.steps, 100))
-        cache = VQCodeCache(ktab, vtab, batch=BATCH, max_tokens=CONTEXT + e2e_steps + args.warmup + 8, device=device)
-        cache.key[:, :, :CONTEXT].copy_(code_sets[0][0])
-        cache.value[:, :, :CONTEXT].copy_(code_sets[0][1])
-        cache.length = CONTEXT
-        hgen = torch.Generator().manual_seed(7)
-        nq, nk = BATCH * Q_HEADS * DIM, BATCH * KV_HEADS * DIM
-        # the new token's q, k and v rows, packed in one pinned buffer per step: one copy each way
-        host_rows = []
-        for _ in range(4):
-            packed = torch.cat([
-                (torch.randn(nq, generator=hgen) / DIM**0.5).half(), torch.randn(nk, generator=hgen).half(), torch.randn(nk, generator=hgen).half()
-            ]).pin_memory()
-            host_rows.append(packed)
-        dev_rows = torch.empty(nq + 2 * nk, dtype=torch.float16, device=device)
-        dev_q = dev_rows[:nq].view(BATCH, Q_HEADS, DIM)
-        dev_k = dev_rows[nq : nq + nk].view(BATCH, KV_HEADS, 1, DIM)
-        dev_v = dev_rows[nq + nk :].view(BATCH, KV_HEADS, 1, DIM)
-        dev_out = torch.empty(BATCH, Q_HEADS, DIM, dtype=torch.float16, device=device)
-        host_out = torch.empty(BATCH, Q_HEADS, DIM, dtype=torch.float16).pin_memory()
-        stream = torch.cuda.current_stream(device)
-
-        def e2e_step(i: int):
-            dev_rows.copy_(host_rows[i % 4], non_blocking=True)
-            cache.decode_step(dev_q, dev_k, dev_v, out=dev_out)  # encode + append K and V, then attend
-            host_out.copy_(dev_out, non_blocking=True)
-            stream.synchronize()  # the next token depends on this result
-
-        for i in range(max(3, args.warmup // 2)):
-            e2e_step(i)
-        barrier()
-        t0 = time.perf_counter()
-        for i in range(e2e_steps):
-            e2e_step(i)
-        barrier()
-        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-        if world > 1:
-            t = torch.tensor([e2e_ms], device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = float(t.item())
-        e2e = {
-            "value": round(BATCH * world / (e2e_ms * 1e-3), 1), "unit": UNIT, "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps,
-            "h2d_bytes_per_step": host_rows[0].numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2,
-            "api": "VQCodeCache.decode_step(q, k, v) = encode+append the new token, attend; code cache resident in HBM, the token's rows from pinned host memory",
-        }
-        del cache
-
-    if extras and rank == 0:
-        # ---- encode throughput: one 2-stage layer, K (with outlier channels) and V ------------
-        egen = torch.Generator().manual_seed(8601)
-        k_rows = torch.randn(4, KV_HEADS, 8192, DIM, generator=egen)
-        for h in range(KV_HEADS):
-            k_rows[:, h, :, torch.randperm(DIM, generator=egen)[:4]] *= 8.0
-        k_rows = k_rows.half().to(device)
-        v_rows = torch.randn(4, KV_HEADS, 8192, DIM, generator=egen).half().to(device)
-        kcodes = torch.empty(4, KV_HEADS, 8192, STAGES, GROUPS, dtype=torch.uint8, device=device)
-        vcodes = torch.empty_like(kcodes)
-        for _ in range(3):
-            ops.encode(k_rows, ktab, codes=kcodes)
-            ops.encode(v_rows, vtab, codes=vcodes)
-        torch.cuda.synchronize(device)
-        reps = 5
-        start.record()
-        for _ in range(reps):
-            ops.encode(k_rows, ktab, codes=kcodes)
-            ops.encode(v_rows, vtab, codes=vcodes)
-        end.record()
-        torch.cuda.synchronize(device)
-        enc_ms = start.elapsed_time(end) / reps
-        distances = 2 * 4 * KV_HEADS * 8192 * STAGES * GROUPS * 256
-        encode = {
-            "value": round(4 * 8192 / (enc_ms * 1e-3), 1), "unit": "tokens/s (K and V of one layer, fp16 [4,8,8192,128], 2 stages x 16 groups, with reconstruction)",
-            "ms_per_layer": round(enc_ms, 4), "distances_per_s": round(distances / (enc_ms * 1e-3), 1),
-            "bound": "instruction issue (tensor cores score every codeword, exact fp32 re-evaluation of the near-minimum ones decides the code)",
-        }
-        # the same K rows through two full-width codebooks (1 group x 2 stages x 128): the wide-group kernel
-        wide_tab = (torch.randn(KV_HEADS, 2, 1, 256, DIM, generator=egen) * 0.1).half().to(device)
-        wide_codes = torch.empty(4, KV_HEADS, 8192, 2, 1, dtype=torch.uint8, device=device)
-        for _ in range(3):
-            ops.encode(k_rows, wide_tab, codes=wide_codes)
-        torch.cuda.synchronize(device)
-        start.record()
-        for _ in range(reps):
-            ops.encode(k_rows, wide_tab, codes=wide_codes)
-        end.record()
-        torch.cuda.synchronize(device)
-        wide_ms = start.elapsed_time(end) / reps
-        encode["full_width"] = {
-            "value": round(4 * 8192 / (wide_ms * 1e-3), 1), "unit": "tokens/s (one tensor fp16 [4,8,8192,128], 1 group x 2 stages x 128, with reconstruction)",
-            "ms_per_tensor": round(wide_ms, 4),
-        }
-        # one layer of the all-layer configuration: K and V fp16 [16,8,16384,128] through two full-width codebooks, codes only
-        big_gen = torch.Generator(device=device).manual_seed(8601)
-        big_k = torch.randn(16, KV_HEADS, 16384, DIM, generator=big_gen, device=device).half()
-        big_codes = torch.empty(16, KV_HEADS, 16384, 2, 1, dtype=torch.uint8, device=device)
-        wide_norms = ops.table_sqnorm(wide_tab)
-        for _ in range(2):
-            ops.encode(big_k, wide_tab, codes=big_codes, want_recon=False, table_sqnorm=wide_norms)
-        torch.cuda.synchronize(device)
-        start.record()
-        for _ in range(reps):
-            ops.encode(big_k, wide_tab, codes=big_codes, want_recon=False, table_sqnorm=wide_norms)
-            ops.encode(big_k, wide_tab, codes=big_codes, want_recon=False, table_sqnorm=wide_norms)
-        end.record()
-        torch.cuda.synchronize(device)
-        layer_ms = start.elapsed_time(end) / reps
-        encode["full_width_layer"] = {
-            "value": round(16 * 16384 / (layer_ms * 1e-3), 1),
-            "unit": "tokens/s (K and V of one layer, fp16 [16,8,16384,128] each, 1 group x 2 stages x 128, codes only; synthetic N(0,1) rows stand in for both)",
-            "ms_per_layer": round(layer_ms, 4), "tflops_of_distances": round(2 * 2 * 16 * KV_HEADS * 16384 * 2 * 256 * DIM / (layer_ms * 1e-3) / 1e12, 1),
-        }
-        del k_rows, v_rows, kcodes, vcodes, wide_tab, wide_codes, big_k, big_codes
-        # the timed workload once more with the rotary step inside (codes of pre-rotary keys, theta 1e6)
-        rope = ops.rope_table(CONTEXT, DIM, 1.0e6, device)
-        for i in range(3):
-            kc, vc = code_sets[i % CODE_SETS]
-            ops.attn_decode(queries[i % CODE_SETS], kc, vc, ktab, vtab, workspace=workspace, out=out, rope=rope)
-        torch.cuda.synchronize(device)
-        rot_steps = 20
-        start.record()
-        for i in range(rot_steps):
-            kc, vc = code_sets[i % CODE_SETS]
-            ops.attn_decode(queries[i % CODE_SETS], kc, vc, ktab, vtab, workspace=workspace, out=out, rope=rope)
-        end.record()
-        torch.cuda.synchronize(device)
-        rot_ms = start.elapsed_time(end) / rot_steps
-        # the 4096-token case of the same configuration: a sliding window over the last 4096 of the 32768 stored tokens
-        w_start = torch.full((BATCH,), CONTEXT - 4096, dtype=torch.int32, device=device)
-        w_end = torch.full((BATCH,), CONTEXT, dtype=torch.int32, device=device)
-        for i in range(3):
-            kc, vc = code_sets[i % CODE_SETS]
-            ops.attn_decode(queries[i % CODE_SETS], kc, vc, ktab, vtab, w_start, w_end, workspace=workspace, out=out)
-        torch.cuda.synchronize(device)
-        start.record()
-        for i in range(rot_steps):
-            kc, vc = code_sets[i % CODE_SETS]
-            ops.attn_decode(queries[i % CODE_SETS], kc, vc, ktab, vtab, w_start, w_end, workspace=workspace, out=out)
-        end.record()
-        torch.cuda.synchronize(device)
-        win_ms = start.elapsed_time(end) / rot_steps
-        # reconstruction of the whole 32768-token window as fp16 rows (what the reference keeps per layer): output-bound
-        for i in range(3):
-            ops.decode(code_sets[i % CODE_SETS][0], ktab, torch.float16)
-        torch.cuda.synchronize(device)
-        start.record()
-        for i in range(rot_steps):
-            ops.decode(code_sets[i % CODE_SETS][0], ktab, torch.float16)
-        end.record()
-        torch.cuda.synchronize(device)
-        rec_ms = start.elapsed_time(end) / rot_steps
-        rec_bytes = BATCH * KV_HEADS * CONTEXT * (DIM * 2 + STAGES * GROUPS)
-        reconstruct = {"value": round(BATCH * KV_HEADS * CONTEXT / (rec_ms * 1e-3), 1), "unit": "rows/s (fp16 [8,8,32768,128] rebuilt from 2 x 16 code bytes per row)",
-                       "ms": round(rec_ms, 4), "achieved_gbs": round(rec_bytes / (rec_ms * 1e-3) / 1e9, 1), "frac_of_hbm_peak": round(rec_bytes / (rec_ms * 1e-3) / 1e9 / peak, 4)}
-        window = {"value": round(BATCH / (win_ms * 1e-3), 1), "unit": "decode tokens/s (per layer; batch 8, sliding window of 4096 over a 32768-token code cache)",
-                  "ms_per_step": round(win_ms, 4)}
-        rotary = {"value": round(BATCH / (rot_ms * 1e-3), 1), "unit": UNIT + "; keys stored pre-rotary, rotated inside the kernel",
-                  "ms_per_step": round(rot_ms, 4)}
-        del rope
+    if rank == 0:
+        extras = decode_extras(ops, device, ktab, vtab, code_sets, queries, workspace, out, peaks)
         if world == 1:
-            cpu = cpu_decode_baseline(sample_seconds=12.0)
-
+            cpu = cpu_decode_baseline(max_steps=8, budget_s=12.0)
     clocks.__exit__(None, None, None)
     result = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
-        "data": "synthetic",
-        "config": {
-            "workload": "packed-code decode attention, one layer per GPU: batch 8, 32 query / 8 KV heads, head_dim 128, 32768-token context, "
-                        "K and V as GSRQ 2-stage x 16-group uint8 codes, fp16 tables, fp16 query scaled 1/sqrt(128)",
-            "batch": BATCH, "context": CONTEXT, "q_heads": Q_HEADS, "kv_heads": KV_HEADS, "head_dim": DIM, "stages": STAGES, "groups": GROUPS,
-            "parallelism": f"layer-sharded x{world} (no data-path collective)",
-            "l2": f"{CODE_SETS} code sets rotated between steps ({CODE_SETS * 2 * BATCH * KV_HEADS * CONTEXT * 32 // 2**20} MiB > 126 MB L2)",
-        },
+        "data": "synthetic", "config": decode_config(world),
         "kv_tokens_scanned_per_s": round(BATCH * CONTEXT * world / (ms_per_step * 1e-3), 1),
-        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "encode": encode, "rotary": rotary, "window4096": window, "reconstruct": reconstruct,
-        "gpu_launches": 3 * args.steps, "clocks": clocks.summary(),
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, **extras,
+        "gpu_launches": 2 * args.steps, "clocks": clocks.summary(),
     }
     if world > 1:
         dist.destroy_process_group()
     return result if rank == 0 else {}
 
+
+def decode_extras(ops, device, ktab, vtab, code_sets, queries, workspace, out, peaks) -> dict:
+    """Sections beside the headline (rank 0): encode, rotary step, 4096 window, reconstruction, full-width decode."""
+    egen = torch.Generator().manual_seed(8601)
+    k_cpu = torch.randn(4, KV_HEADS, 8192, DIM, generator=egen)
+    for h in range(KV_HEADS):
+        k_cpu[:, h, :, torch.randperm(DIM, generator=egen)[:4]] *= 8.0
+    k_cpu = k_cpu.half()
+    v_cpu = torch.randn(4, KV_HEADS, 8192, DIM, generator=egen).half()
+    k_rows, v_rows = k_cpu.to(device), v_cpu.to(device)
+    kcodes = torch.empty(4, KV_HEADS, 8192, STAGES, GROUPS, dtype=torch.uint8, device=device)
+    vcodes = torch.empty_like(kcodes)
+
+    def enc(_i):
+        ops.encode(k_rows, ktab, codes=kcodes)
+        ops.encode(v_rows, vtab, codes=vcodes)
+
+    for i in range(3):
+        enc(i)
+    enc_ms = timed(enc, 5, device)
+    distances = 2 * 4 * KV_HEADS * 8192 * STAGES * GROUPS * 256
+    flops = distances * SUB * 2
+    # CPU baseline: the reference's hard_residual_vq_exits (groups folded into heads) restated in oracle/, whole layer
+    from oracle import jointkv_oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    ktab_c, vtab_c = ktab.cpu().float(), vtab.cpu().float()
+    t0 = time.perf_counter()
+    _, ref_codes = O.grouped_residual_encode(k_cpu[:1], ktab_c)
+    O.grouped_residual_encode(v_cpu[:1], vtab_c)
+    cpu_s = (time.perf_counter() - t0) * 4  # one of the four batch rows of K and of V, scaled by 4
+    same = bool(torch.equal(ref_codes, kcodes[:1].cpu()))
+    encode = {
+        "value": round(4 * 8192 / (enc_ms * 1e-3), 1), "unit": "tokens/s (K and V of one layer, fp16 [4,8,8192,128], 2 stages x 16 groups, with reconstruction)",
+        "ms_per_layer": round(enc_ms, 4), "distances_per_s": round(distances / (enc_ms * 1e-3), 1),
+        "roofline": {"bound": "compute (fp32 issue: tensor cores only filter, the exact fp32 re-evaluation decides)", "achieved": round(flops / (enc_ms * 1e-3) / 1e12, 2),
+                     "peak": round(FP32_FMA_TFLOPS, 1), "unit": "TFLOP/s", "frac": round(flops / (enc_ms * 1e-3) / 1e12 / FP32_FMA_TFLOPS, 4),
+                     "peak_source": "nominal fp32 FMA rate (148 SMs x 128 lanes x 1.965 GHz)", "flops_per_layer": flops},
+        "cpu_baseline": {"value": round(4 * 8192 / cpu_s, 1), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": "hard_residual_vq_exits on batch row 0 of K and of V ([1,8,8192,128] each, groups folded into heads), time x 4",
+                         "codes_equal_gpu": same},
+    }
+    # the same K rows through two full-width codebooks (1 group x 2 stages x 128): the tcgen05 kernel
+    wide_tab = (torch.randn(KV_HEADS, 2, 1, 256, DIM, generator=egen) * 0.1).half().to(device)
+    wide_codes = torch.empty(4, KV_HEADS, 8192, 2, 1, dtype=torch.uint8, device=device)
+    for _ in range(3):
+        ops.encode(k_rows, wide_tab, codes=wide_codes)
+    wide_ms = timed(lambda _i: ops.encode(k_rows, wide_tab, codes=wide_codes), 5, device)
+    encode["full_width"] = {
+        "value": round(4 * 8192 / (wide_ms * 1e-3), 1), "unit": "tokens/s (one tensor fp16 [4,8,8192,128], 1 group x 2 stages x 128, with reconstruction)",
+        "ms_per_tensor": round(wide_ms, 4),
+    }
+    # one layer of the all-layer configuration: K and V fp16 [16,8,16384,128] through two full-width codebooks, codes only
+    big_gen = torch.Generator(device=device).manual_seed(8601)
+    big_k = torch.randn(16, KV_HEADS, 16384, DIM, generator=big_gen, device=device).half()
+    big_codes = torch.empty(16, KV_HEADS, 16384, 2, 1, dtype=torch.uint8, device=device)
+    wide_norms = ops.table_sqnorm(wide_tab)
+
+    def big(_i):
+        ops.encode(big_k, wide_tab, codes=big_codes, want_recon=False, table_sqnorm=wide_norms)
+        ops.encode(big_k, wide_tab, codes=big_codes, want_recon=False, table_sqnorm=wide_norms)
+
+    for i in range(2):
+        big(i)
+    layer_ms = timed(big, 5, device)
+    wide_flops = 2 * 2 * 16 * KV_HEADS * 16384 * 2 * 256 * DIM
+    encode["full_width_layer"] = {
+        "value": round(16 * 16384 / (layer_ms * 1e-3), 1),
+        "unit": "tokens/s (K and V of one layer, fp16 [16,8,16384,128] each, 1 group x 2 stages x 128, codes only; synthetic N(0,1) rows stand in for both)",
+        "ms_per_layer": round(layer_ms, 4),
+        "roofline": {"bound": "tensor", "achieved": round(wide_flops / (layer_ms * 1e-3) / 1e12, 1), "peak": peaks["bf16"], "unit": "TFLOP/s",
+                     "frac": round(wide_flops / (layer_ms * 1e-3) / 1e12 / peaks["bf16"], 4), "peak_source": f"{peaks['kind']} bf16 GEMM (burst)",
+                     "flops_per_layer": wide_flops, "note": "flops of all row-word distances; the tcgen05 product is a filter, the exact fp32 chains dominate the time"},
+    }
+    del k_rows, v_rows, kcodes, vcodes, wide_codes, big_k, big_codes
+    # the timed workload once more with the rotary step inside (codes of pre-rotary keys, theta 1e6)
+    rope = ops.rope_table(CONTEXT, DIM, 1.0e6, device)
+
+    def rot(i):
+        kc, vc = code_sets[i % CODE_SETS]
+        ops.attn_decode(queries[i % CODE_SETS], kc, vc, ktab, vtab, workspace=workspace, out=out, rope=rope)
+
+    for i in range(3):
+        rot(i)
+    rot_ms = timed(rot, 20, device)
+    del rope
+    # the 4096-token case: a sliding window over the last 4096 of the 32768 stored tokens, replayed from a CUDA graph
+    # (at this size the host cannot enqueue as fast as the GPU runs)
+    w_start = torch.full((BATCH,), CONTEXT - 4096, dtype=torch.int32, device=device)
+    w_end = torch.full((BATCH,), CONTEXT, dtype=torch.int32, device=device)
+
+    def win(i):
+        kc, vc = code_sets[i % CODE_SETS]
+        ops.attn_decode(queries[i % CODE_SETS], kc, vc, ktab, vtab, w_start, w_end, workspace=workspace, out=out)
+
+    for i in range(3):
+        win(i)
+    win_ms = timed(win, 40, device)
+    graph_ms = None
+    try:
+        side = torch.cuda.Stream(device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            win(0)
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(CODE_SETS):
+                    win(i)
+        torch.cuda.synchronize(device)
+        graph.replay()
+        graph_ms = timed(lambda _i: graph.replay(), 20, device) / CODE_SETS
+    except Exception:  # graph capture unavailable: the stream-launched figure stands alone
+        graph_ms = None
+    win_bytes = algorithmic_bytes(BATCH, 4096)
+    best = min(win_ms, graph_ms) if graph_ms else win_ms
+    window = {"value": round(BATCH / (best * 1e-3), 1), "unit": "decode tokens/s (per layer; batch 8, sliding window of 4096 over a 32768-token code cache)",
+              "ms_per_step": round(best, 4), "ms_per_step_stream_launched": round(win_ms, 4),
+              "ms_per_step_graph_replay": None if graph_ms is None else round(graph_ms, 4),
+              "frac_of_hbm_peak": round(win_bytes / (best * 1e-3) / 1e9 / peaks["hbm"], 4)}
+    # reconstruction of the whole 32768-token window as fp16 rows (what the reference keeps per layer): output-bound
+    for i in range(3):
+        ops.decode(code_sets[i % CODE_SETS][0], ktab, torch.float16)
+    rec_ms = timed(lambda i: ops.decode(code_sets[i % CODE_SETS][0], ktab, torch.float16), 20, device)
+    rec_bytes = BATCH * KV_HEADS * CONTEXT * (DIM * 2 + STAGES * GROUPS)
+    reconstruct = {"value": round(BATCH * KV_HEADS * CONTEXT / (rec_ms * 1e-3), 1), "unit": "rows/s (fp16 [8,8,32768,128] rebuilt from 2 x 16 code bytes per row)",
+                   "ms": round(rec_ms, 4), "achieved_gbs": round(rec_bytes / (rec_ms * 1e-3) / 1e9, 1),
+                   "frac_of_hbm_peak": round(rec_bytes / (rec_ms * 1e-3) / 1e9 / peaks["hbm"], 4)}
+    rotary = {"value": round(BATCH / (rot_ms * 1e-3), 1), "unit": UNIT + "; keys stored pre-rotary, rotated inside the kernel", "ms_per_step": round(rot_ms, 4)}
+    return {"encode": encode, "rotary": rotary, "window4096": window, "reconstruct": reconstruct}
+
+
+# ------------------------------------------------------------------- all 32 layers, full-width codebooks
+
+
+CQ_LAYERS, CQ_BATCH, CQ_CONTEXT = 32, 16, 16384
+
+
+def run_cq32layers(args) -> dict:
+    """All 32 layers of the full-width configuration, layers sharded over the ranks (no collective).
+
+    Per layer: K and V fp16 [16,8,16384,128] (seed 8601 + layer, drawn on the device), two additive 256 x 128
+    codebooks N(0, 0.1) per side.  A step is one layer: encode K and V into the layer's code cache, then one
+    decode-attention step over it.  Inputs of at most four layers are resident and rotated (2 GiB per layer:
+    far beyond L2); every layer has its own tables and code cache.  Layers 0 and 31 are checked against the
+    C oracle inside the run (batch rows 0-1, the first 1024 tokens' codes and the attention result).
+    """
+    from tac_vq_kv_cache_b200 import _lib, ops
+    from tac_vq_kv_cache_b200.code_cache import VQCodeCache
+    from tac_vq_kv_cache_b200.dist import shard_range
+
+    _lib.load()
+    world, rank, local = dist_env()
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    lo, hi = shard_range(CQ_LAYERS, rank, world)
+    layers = list(range(lo, hi))
+    resident = layers[: min(4, len(layers))]
+    inputs = {}
+    for layer in resident:
+        g = torch.Generator(device=device).manual_seed(8601 + layer)
+        inputs[layer] = (torch.randn(CQ_BATCH, KV_HEADS, CQ_CONTEXT, DIM, generator=g, device=device).half(),
+                         torch.randn(CQ_BATCH, KV_HEADS, CQ_CONTEXT, DIM, generator=g, device=device).half())
+    tables, caches, norms, queries = {}, {}, {}, {}
+    for layer in layers:
+        g = torch.Generator().manual_seed(8601 + layer)
+        kt = (torch.randn(KV_HEADS, 2, 1, 256, DIM, generator=g) * 0.1).half().to(device)
+        vt = (torch.randn(KV_HEADS, 2, 1, 256, DIM, generator=g) * 0.1).half().to(device)
+        tables[layer] = (kt, vt)
+        norms[layer] = (ops.table_sqnorm(kt), ops.table_sqnorm(vt))
+        caches[layer] = VQCodeCache(kt, vt, batch=CQ_BATCH, max_tokens=CQ_CONTEXT, device=device)
+        queries[layer] = (torch.randn(CQ_BATCH, Q_HEADS, DIM, generator=g) / DIM**0.5).half().to(device)
+    out = torch.empty(CQ_BATCH, Q_HEADS, DIM, dtype=torch.float16, device=device)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+
+    def layer_step(i: int, record: bool):
+        layer = layers[i % len(layers)]
+        keys, values = inputs[resident[i % len(resident)]]
+        cache, (kt, vt), (kn, vn) = caches[layer], tables[layer], norms[layer]
+        cache.reset()
+        if record:
+            ev[0].record()
+        ops.encode(keys, kt, codes=cache.key, want_recon=False, table_sqnorm=kn)
+        ops.encode(values, vt, codes=cache.value, want_recon=False, table_sqnorm=vn)
+        cache.length = CQ_CONTEXT
+        if record:
+            ev[1].record()
+        result = cache.attend(queries[layer])
+        if record:
+            ev[2].record()
+        return result
+
+    for i in range(max(args.warmup, len(layers))):  # every layer's cache gets filled at least once
+        layer_step(i, False)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    clocks = ClockSampler(local)
+    clocks.__enter__()
+    enc_ms = dec_ms = 0.0
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        layer_step(i, True)
+        ev[2].synchronize()
+        enc_ms += ev[0].elapsed_time(ev[1])
+        dec_ms += ev[1].elapsed_time(ev[2])
+    end.record()
+    torch.cuda.synchronize(device)
+    clocks.__exit__(None, None, None)
+    t = torch.tensor([start.elapsed_time(end), enc_ms, dec_ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, enc_ms, dec_ms = (float(x) / args.steps for x in t.tolist())
+
+    parity = None
+    if rank == 0 or hi == CQ_LAYERS:
+        from oracle import c_oracle as C
+
+        layer = 0 if rank == 0 else CQ_LAYERS - 1
+        g = torch.Generator(device=device).manual_seed(8601 + layer)
+        keys = torch.randn(CQ_BATCH, KV_HEADS, CQ_CONTEXT, DIM, generator=g, device=device).half()
+        values = torch.randn(CQ_BATCH, KV_HEADS, CQ_CONTEXT, DIM, generator=g, device=device).half()
+        kt, vt = tables[layer]
+        cache = caches[layer]
+        cache.reset()
+        cache.append(keys, values)
+        got = cache.attend(queries[layer])[:2].cpu()
+        want_k, _ = C.encode(keys[:2, :, :1024].cpu().contiguous(), kt.cpu(), want_recon=False)
+        want_v, _ = C.encode(values[:2, :, :1024].cpu().contiguous(), vt.cpu(), want_recon=False)
+        codes_ok = bool(torch.equal(cache.key[:2, :, :1024].cpu(), want_k) and torch.equal(cache.value[:2, :, :1024].cpu(), want_v))
+        want, _ = C.attention(queries[layer][:2].cpu(), cache.key[:2].cpu().contiguous(), cache.value[:2].cpu().contiguous(), kt.cpu(), vt.cpu())
+        err = float((got.double() - want.double()).norm() / want.double().norm())
+        parity = {"layer": layer, "codes_bit_exact": codes_ok, "attention_rel_l2": round(err, 6), "ok": codes_ok and err <= 2e-3}
+        if world > 1 and rank != 0:
+            print(json.dumps({"workload": "cq32layers", "rank": rank, "parity": parity}), file=sys.stderr, flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return {}
+    peaks = measured_peaks()
+    dec_bytes = CQ_BATCH * KV_HEADS * CQ_CONTEXT * 4 + 2 * KV_HEADS * 2 * 256 * DIM * 2 + 2 * CQ_BATCH * Q_HEADS * DIM * 2
+    enc_flops = 2 * CQ_BATCH * KV_HEADS * CQ_CONTEXT * 2 * 256 * DIM * 2
+    return {
+        "metric": "vq_kv_decode_attention_tokens_per_s_full_width_all_layers", "value": round(CQ_BATCH * world / (dec_ms * 1e-3), 1),
+        "unit": "decode tokens/s per layer-step, summed over ranks (batch 16, 16384-token context, two additive 256x128 codebooks)",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total_ms, 4), "higher_is_better": True,
+        "scaling": "strong (32 layers over the ranks); the figures are per layer-step, so they read as weak scaling",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "encode K and V of a layer (fp16 [16,8,16384,128], two additive 256x128 codebooks), then one decode-attention step over its codes; "
+                               "32 layers sharded by layer", "layers_per_rank": len(layers), "batch": CQ_BATCH, "context": CQ_CONTEXT,
+                   "l2": "inputs of up to 4 layers (2 GiB each) rotated"},
+        "encode": {"ms_per_layer": round(enc_ms, 4), "tokens_per_s": round(CQ_BATCH * CQ_CONTEXT * world / (enc_ms * 1e-3), 1),
+                   "tflops_of_distances": round(enc_flops / (enc_ms * 1e-3) / 1e12, 1), "frac_of_bf16_peak": round(enc_flops / (enc_ms * 1e-3) / 1e12 / peaks["bf16"], 4)},
+        "decode": {"ms_per_layer_step": round(dec_ms, 4), "tokens_per_s": round(CQ_BATCH * world / (dec_ms * 1e-3), 1)},
+        "roofline": {"bound": "hbm", "achieved": round(dec_bytes / (dec_ms * 1e-3) / 1e9, 1), "peak": peaks["hbm"], "unit": "GB/s",
+                     "frac": round(dec_bytes / (dec_ms * 1e-3) / 1e9 / peaks["hbm"], 4), "peak_source": f"{peaks['kind']} copy bandwidth",
+                     "algorithmic_bytes_per_launch": dec_bytes, "kernel": "attn_fullwidth_kernel (decode side of a layer-step)", "traffic": None},
+        "parity": parity, "gpu_launches": 4 * args.steps, "clocks": clocks.summary(),
+    }
 
 
 # --------------------------------------------------------------------- sequence split (extra workload)
@@ -412,8 +544,8 @@ def run_sequence_split(args) -> dict:
     """One long sequence split across the ranks: batch 1, 32 query / 8 KV heads, 131072 stored tokens.
 
     Every rank scans its token range and produces partial softmax states; one NCCL all-gather of
-    [1,32,130] fp32 per rank and the merge kernel give every rank the result.  Scan and exchange+merge
-    are timed separately (the exchange is latency bound: 16,640 bytes per rank).
+    [1,32,130] fp32 per rank and the merge kernel give every rank the result.  Scan, exchange and merge are
+    timed separately (the exchange is latency bound: 16,640 bytes per rank); N = 1 is the anchor.
     """
     import torch.distributed as dist
 
@@ -421,7 +553,7 @@ def run_sequence_split(args) -> dict:
     from tac_vq_kv_cache_b200.dist import exchange_states, sequence_split
 
     _lib.load()
-    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    world, rank, local = dist_env()
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
@@ -432,23 +564,32 @@ def run_sequence_split(args) -> dict:
     ktab, vtab = (t.to(device) for t in make_tables(gen))
     dgen = torch.Generator(device=device).manual_seed(8601 + rank)
     own = hi - lo
-    sets = [tuple(torch.randint(0, 256, (1, KV_HEADS, own, STAGES, GROUPS), dtype=torch.uint8, device=device, generator=dgen) for _ in range(2)) for _ in range(8)]
+    n_sets = 16  # 16 x 2 x 8 x own x 32 bytes: beyond L2 even at 8 ranks
+    sets = [tuple(torch.randint(0, 256, (1, KV_HEADS, own, STAGES, GROUPS), dtype=torch.uint8, device=device, generator=dgen) for _ in range(2)) for _ in range(n_sets)]
     q = (torch.randn(1, Q_HEADS, DIM, device=device, generator=dgen) / DIM**0.5).half()
     workspace = torch.empty(ops.attn_workspace_bytes(1, Q_HEADS, KV_HEADS, DIM, GROUPS, STAGES), dtype=torch.uint8, device=device)
     state = torch.empty(1, Q_HEADS, DIM + 2, dtype=torch.float32, device=device)
+    gathered = torch.empty(world, 1, Q_HEADS, DIM + 2, dtype=torch.float32, device=device)
+    result = torch.empty(1, Q_HEADS, DIM, dtype=torch.float16, device=device)
 
     def scan(i):
-        ops.attn_decode(q, *sets[i % 8], ktab, vtab, workspace=workspace, want_out=False, want_state=True, state=state)
+        ops.attn_decode(q, *sets[i % n_sets], ktab, vtab, workspace=workspace, want_out=False, want_state=True, state=state)
+
+    def exchange():
+        if world > 1:
+            exchange_states(state, out=gathered)
+        else:
+            gathered[0].copy_(state)
 
     def merge():
-        gathered = exchange_states(state) if world > 1 else state[None]
-        return ops.attn_combine(gathered)[0]
+        ops.attn_combine(gathered, out=result)
 
     for i in range(args.warmup):
         scan(i)
+        exchange()
         merge()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    scan_ms = merge_ms = 0.0
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    acc = [0.0, 0.0, 0.0]
     for i in range(args.steps):  # per-step events: a decode step cannot pipeline across its own exchange
         if world > 1:
             dist.barrier()
@@ -456,126 +597,120 @@ def run_sequence_split(args) -> dict:
         ev[0].record()
         scan(i)
         ev[1].record()
-        merge()
+        exchange()
         ev[2].record()
+        merge()
+        ev[3].record()
         torch.cuda.synchronize(device)
-        scan_ms += ev[0].elapsed_time(ev[1])
-        merge_ms += ev[1].elapsed_time(ev[2])
-    t = torch.tensor([scan_ms / args.steps, merge_ms / args.steps], device=device)
+        for j in range(3):
+            acc[j] += ev[j].elapsed_time(ev[j + 1])
+    t = torch.tensor([a / args.steps for a in acc], device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.destroy_process_group()
-    scan_ms, merge_ms = (float(x) for x in t.tolist())
+    scan_ms, exchange_ms, merge_ms = (float(x) for x in t.tolist())
     if rank != 0:
         return {}
-    total = scan_ms + merge_ms
+    total = scan_ms + exchange_ms + merge_ms
     return {
         "metric": "vq_kv_sequence_split_decode_tokens_per_s_at_131k_ctx", "value": round(1e3 / total, 1), "unit": "decode tokens/s (one layer, batch 1, 131072-token context split by sequence)",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total, 5), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "sequence-split decode attention over GSRQ 2-stage codes, batch 1, 32 query / 8 KV heads, head_dim 128, 131072 tokens",
-                   "tokens_per_rank": own, "l2": "8 code sets rotated between steps"},
-        "scan_ms": round(scan_ms, 5), "exchange_and_merge_ms": round(merge_ms, 5),
-        "exchange_bytes_per_rank": Q_HEADS * (DIM + 2) * 4, "gpu_launches": 4 * args.steps,
+                   "tokens_per_rank": own, "l2": f"{n_sets} code sets rotated between steps"},
+        "scan_ms": round(scan_ms, 5), "exchange_ms": round(exchange_ms, 5), "merge_ms": round(merge_ms, 5),
+        "exchange_bytes_per_rank": Q_HEADS * (DIM + 2) * 4, "gpu_launches": (3 if world > 1 else 4) * args.steps,
+        "per_rank_scan_gbs": round((2 * KV_HEADS * own * 32 + 2_097_152) / (scan_ms * 1e-3) / 1e9, 1),
     }
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum of the scan kernel for one full-size launch, from the
-# ncu capture summarised under profiles/.
-TRAFFIC_BYTES_PER_LAUNCH = 143_500_000  # 139.5 MB read + 4.0 MB written (profiles/attn_gsrq_scan_32k.md)
 
 
 # ------------------------------------------------------------------------------------- CPU legs
 
 
-def _cpu_window(gen: torch.Generator, rows: int, heads: int, context: int):
-    """A (rows x heads) slice of the workload, decoded the way the reference keeps its window."""
-    from oracle import jointkv_oracle as O
+class CpuDecodeStep:
+    """The reference's decode branch on the CPU, rotary step left out, one whole step of the workload.
 
-    ktab, vtab = make_tables(gen)
-    kcodes = torch.randint(0, 256, (rows, heads, context, STAGES, GROUPS), generator=gen, dtype=torch.uint8)
-    vcodes = torch.randint(0, 256, (rows, heads, context, STAGES, GROUPS), generator=gen, dtype=torch.uint8)
-    t0 = time.perf_counter()
-    k = O.reconstruct(kcodes, ktab[:heads].float(), torch.float16)
-    v = O.reconstruct(vcodes, vtab[:heads].float(), torch.float16)
-    rebuild_s = time.perf_counter() - t0
-    return ktab[:heads], vtab[:heads], k, v, rebuild_s
+    Per batch row (the reference decodes batch one): encode the new token's K and V rows, then
+    ``repeat_kv`` of the dense fp16 window and ``scaled_dot_product_attention`` in fp16
+    (experiments_followup_mistral/evaluate_mistral_longbench.py:94-98, 119-122).  The fp16 window is what
+    the reference keeps per layer; it is rebuilt from the codes once, outside the timed region.
+    """
 
+    def __init__(self):
+        from oracle import jointkv_oracle as O
 
-def _cpu_decode_step(q, k_new, v_new, ktab, vtab, k_window, v_window):
-    """The reference's decode branch on the CPU, rotary step left out: encode the new token's K/V,
-    then repeat_kv + scaled_dot_product_attention over the dense fp16 window
-    (experiments_followup_mistral/evaluate_mistral_longbench.py:94-98, 119-122)."""
-    import torch.nn.functional as F
-
-    from oracle import jointkv_oracle as O
-
-    O.grouped_residual_encode(k_new, ktab.float())
-    O.grouped_residual_encode(v_new, vtab.float())
-    rep = q.shape[1] // k_window.shape[1]
-    kk = k_window.repeat_interleave(rep, dim=1).float()
-    vv = v_window.repeat_interleave(rep, dim=1).float()
-    return F.scaled_dot_product_attention(q.float(), kk, vv, scale=1.0)
-
-
-def cpu_decode_baseline(sample_seconds: float) -> dict:
-    """Oracle-port CPU baseline on a bounded sample: one batch row, all 8 KV heads, full context."""
-    torch.set_num_threads(os.cpu_count() or 1)
-    gen = torch.Generator().manual_seed(8601)
-    ktab, vtab, k, v, rebuild_s = _cpu_window(gen, 1, KV_HEADS, CONTEXT)
-    q = (torch.randn(1, Q_HEADS, 1, DIM, generator=gen) / DIM**0.5).half()
-    k_new = torch.randn(1, KV_HEADS, 1, DIM, generator=gen).half()
-    v_new = torch.randn(1, KV_HEADS, 1, DIM, generator=gen).half()
-    _cpu_decode_step(q, k_new, v_new, ktab, vtab, k, v)
-    times = []
-    t_end = time.perf_counter() + sample_seconds
-    while time.perf_counter() < t_end and len(times) < 50:
+        self.O = O
+        torch.set_num_threads(os.cpu_count() or 1)
+        gen = torch.Generator().manual_seed(8601)
+        self.ktab, self.vtab = make_tables(gen)
         t0 = time.perf_counter()
-        _cpu_decode_step(q, k_new, v_new, ktab, vtab, k, v)
+        self.k_window, self.v_window = [], []
+        for _ in range(BATCH):
+            kc = torch.randint(0, 256, (1, KV_HEADS, CONTEXT, STAGES, GROUPS), generator=gen, dtype=torch.uint8)
+            vc = torch.randint(0, 256, (1, KV_HEADS, CONTEXT, STAGES, GROUPS), generator=gen, dtype=torch.uint8)
+            self.k_window.append(O.reconstruct(kc, self.ktab.float(), torch.float16))
+            self.v_window.append(O.reconstruct(vc, self.vtab.float(), torch.float16))
+        self.rebuild_s = time.perf_counter() - t0
+        self.q = (torch.randn(BATCH, Q_HEADS, 1, DIM, generator=gen) / DIM**0.5).half()
+        self.k_new = torch.randn(BATCH, KV_HEADS, 1, DIM, generator=gen).half()
+        self.v_new = torch.randn(BATCH, KV_HEADS, 1, DIM, generator=gen).half()
+        self.cores = torch.get_num_threads()
+
+    def step(self):
+        import torch.nn.functional as F
+
+        rep = Q_HEADS // KV_HEADS
+        outs = []
+        for b in range(BATCH):
+            self.O.grouped_residual_encode(self.k_new[b : b + 1], self.ktab.float())
+            self.O.grouped_residual_encode(self.v_new[b : b + 1], self.vtab.float())
+            kk = self.k_window[b].repeat_interleave(rep, dim=1)
+            vv = self.v_window[b].repeat_interleave(rep, dim=1)
+            outs.append(F.scaled_dot_product_attention(self.q[b : b + 1], kk, vv, scale=1.0))
+        return outs
+
+
+def cpu_decode_baseline(max_steps: int, budget_s: float) -> dict:
+    """CPU baseline beside the GPU line: whole decode steps (8 batch rows x 8 KV heads x 32768 tokens)."""
+    leg = CpuDecodeStep()
+    leg.step()
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < max_steps and (not times or time.perf_counter() < t_end):
+        t0 = time.perf_counter()
+        leg.step()
         times.append(time.perf_counter() - t0)
-    per_row = statistics.median(times)
+    sec = statistics.median(times)
     return {
-        "value": round(1.0 / per_row, 3), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-        "sample": f"1 of {BATCH} batch rows (all 8 KV heads, 32768 tokens), {len(times)} timed steps, median; dense fp16 window prebuilt "
-                  f"({rebuild_s:.1f} s, untimed) as the reference keeps it; value = 1 row / median seconds",
-        "seconds_per_row_step": round(per_row, 4),
+        "value": round(BATCH / sec, 3), "unit": UNIT, "cores": leg.cores, "kind": "port",
+        "sample": f"{len(times)} whole steps (8 batch rows x 8 KV heads x 32768 tokens) after 1 warm-up, median; dense fp16 window rebuilt once "
+                  f"({leg.rebuild_s:.1f} s, untimed) as the reference keeps it",
+        "seconds_per_step": round(sec, 4),
     }
 
 
 def run_reference(args) -> dict:
-    """Reference arm: the reference's CPU decode path (oracle port) on the host cores, rank 0 only."""
-    if int(os.environ.get("RANK", "0")) != 0:
+    """Reference arm: the reference's CPU decode path (oracle port) on the host cores, rank 0 only, whole steps."""
+    world, rank, _ = dist_env()
+    if rank != 0:
         return {}
-    torch.set_num_threads(os.cpu_count() or 1)
-    gen = torch.Generator().manual_seed(8601)
-    heads = 2  # sample: one batch row, 2 of 8 KV heads (8 of 32 query heads), full 32768-token context
-    ktab, vtab, k, v, rebuild_s = _cpu_window(gen, 1, heads, CONTEXT)
-    q = (torch.randn(1, heads * 4, 1, DIM, generator=gen) / DIM**0.5).half()
-    k_new = torch.randn(1, heads, 1, DIM, generator=gen).half()
-    v_new = torch.randn(1, heads, 1, DIM, generator=gen).half()
-    budget = time.perf_counter() + 240.0
-    for _ in range(min(args.warmup, 3)):
-        _cpu_decode_step(q, k_new, v_new, ktab, vtab, k, v)
-    times = []
+    if args.workload != "decode32k":
+        return {"impl": "reference", "unavailable": "the reference arm covers the headline workload (decode32k) only"}
+    leg = CpuDecodeStep()
+    for _ in range(args.warmup):
+        leg.step()
+    t0 = time.perf_counter()
     for _ in range(args.steps):
-        t0 = time.perf_counter()
-        _cpu_decode_step(q, k_new, v_new, ktab, vtab, k, v)
-        times.append(time.perf_counter() - t0)
-        if time.perf_counter() > budget:
-            break
-    sec = sum(times) / len(times)
-    fraction = heads / (BATCH * KV_HEADS)  # share of one full step the sample covers
-    value = BATCH * fraction / sec
-    cores = torch.get_num_threads()
-    sample = (f"1 batch row x {heads} of 8 KV heads x 32768 tokens = {fraction:.4f} of a step; {len(times)} steps timed; "
-              f"dense fp16 window prebuilt ({rebuild_s:.1f} s, untimed); scaled to the full step by that share")
+        leg.step()
+    sec = (time.perf_counter() - t0) / args.steps
+    value = BATCH / sec
+    sample = (f"{args.steps} whole steps (8 batch rows x 8 KV heads x 32768 tokens) after {args.warmup} warm-up steps; per row: encode of the new token, "
+              f"repeat_kv of the dense fp16 window, fp16 SDPA; window rebuilt once ({leg.rebuild_s:.1f} s, untimed)")
     return {
-        "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
-        "steps": len(times), "warmup": min(args.warmup, 3), "ms_per_step": round(sec / fraction * 1e3, 3), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "packed-code decode attention (CPU reference path: dense fp16 window + SDPA), batch 8, 32 query / 8 KV heads, "
-                               "head_dim 128, 32768-token context", "batch": BATCH, "context": CONTEXT},
-        "cpu_baseline": {"value": round(value, 4), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": decode_config(world),
+        "cpu_baseline": {"value": round(value, 4), "unit": UNIT, "cores": leg.cores, "kind": "port", "sample": sample},
         "e2e": {"value": round(value, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -587,19 +722,23 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=("decode32k", "seqsplit131k"), default="decode32k",
-                        help="decode32k: the headline configuration; seqsplit131k: one sequence split across the ranks (extra)")
-    parser.add_argument("--encode-only", action="store_true", help="run only the layer encode (used for profiler captures)")
-    parser.add_argument("--decode-only", action="store_true", help="run only the reconstruction of rows from codes (profiler captures)")
-    parser.add_argument("--encode-wide-only", action="store_true", help="run only a full-width (d = 128) encode (profiler captures)")
-    parser.add_argument("--rotary-only", action="store_true", help="run only rotary attention at 8192 tokens (profiler captures)")
-    parser.add_argument("--kernel-only", action="store_true", help="time the decode-attention launches only (used for profiler captures)")
+    parser.add_argument("--workload", choices=("decode32k", "cq32layers", "seqsplit131k"), default="decode32k",
+                        help="decode32k: the headline configuration; cq32layers: all 32 layers with full-width codebooks, encode + decode; "
+                             "seqsplit131k: one sequence split across the ranks")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.workload == "seqsplit131k" and args.impl == "ours":
+    if args.impl == "reference":
+        if args.steps == 200 and args.warmup == 20:  # defaults: a CPU step takes ~0.5 s
+            args.steps, args.warmup = 20, 3
+        result = run_reference(args)
+    elif args.workload == "seqsplit131k":
         result = run_sequence_split(args)
+    elif args.workload == "cq32layers":
+        if args.steps == 200 and args.warmup == 20:
+            args.steps, args.warmup = 32, 3
+        result = run_cq32layers(args)
     else:
-        result = run_reference(args) if args.impl == "reference" else run_ours(args)
+        result = run_decode32k(args)
     if result:
         print(json.dumps(result), flush=True)
 

@@ -45,23 +45,36 @@ def sequence_split(length: int, rank: int, world: int, *, window: int | None = N
     return start + min(lo * align, visible), start + min(hi * align, visible)
 
 
-def exchange_states(state: torch.Tensor, group: dist.ProcessGroup | None = None) -> torch.Tensor:
-    """All-gather per-rank partial states ``[B,Hq,2+D]`` fp32 -> ``[world,B,Hq,2+D]`` on every rank."""
+def exchange_states(state: torch.Tensor, group: dist.ProcessGroup | None = None, *, out: torch.Tensor | None = None) -> torch.Tensor:
+    """All-gather per-rank partial states ``[B,Hq,2+D]`` fp32 -> ``[world,B,Hq,2+D]`` on every rank.
+
+    ``out``: a caller-kept ``[world,B,Hq,2+D]`` buffer, so that a decode loop allocates nothing per step.
+    One collective (``all_gather_into_tensor``); backends without it fall back to the list form.
+    """
     if state.dtype != torch.float32 or state.ndim != 3:
         raise ValueError("state must be fp32 [B,Hq,2+D]")
     world = dist.get_world_size(group)
-    gathered = torch.empty((world, *state.shape), dtype=state.dtype, device=state.device)
-    # views of one contiguous buffer: NCCL runs this as a single all-gather, gloo accepts the list form
-    dist.all_gather(list(gathered.unbind(0)), state.contiguous(), group=group)
-    return gathered
+    shape = (world, *state.shape)
+    if out is None:
+        out = torch.empty(shape, dtype=state.dtype, device=state.device)
+    elif tuple(out.shape) != shape or out.dtype != state.dtype or out.device != state.device or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [world,B,Hq,2+D] buffer on the state's device")
+    state = state.contiguous()
+    try:
+        dist.all_gather_into_tensor(out, state, group=group)
+    except (RuntimeError, NotImplementedError):
+        dist.all_gather(list(out.unbind(0)), state, group=group)  # views of the one buffer
+    return out
 
 
-def merge_split_sequence(state: torch.Tensor, group: dist.ProcessGroup | None = None, *, want_state: bool = False):
+def merge_split_sequence(state: torch.Tensor, group: dist.ProcessGroup | None = None, *, want_state: bool = False,
+                         gathered: torch.Tensor | None = None, out: torch.Tensor | None = None):
     """Exchange the partial states of a sequence-split decode step and merge them on this GPU.
 
-    Returns fp16 ``[B,Hq,D]`` (and the merged fp32 state when ``want_state``).
+    Returns fp16 ``[B,Hq,D]`` (and the merged fp32 state when ``want_state``).  ``gathered`` and ``out`` are
+    optional caller-kept buffers (see :func:`exchange_states`, :func:`ops.attn_combine`).
     """
     from . import ops
 
-    out, merged = ops.attn_combine(exchange_states(state, group), want_out=True, want_state=want_state)
-    return (out, merged) if want_state else out
+    result, merged = ops.attn_combine(exchange_states(state, group, out=gathered), want_out=True, want_state=want_state, out=out)
+    return (result, merged) if want_state else result

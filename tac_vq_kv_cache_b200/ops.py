@@ -307,15 +307,25 @@ def set_ranges(seq_start: torch.Tensor, seq_end: torch.Tensor, start: int, end: 
     _lib.check("tacvq_set_ranges", status)
 
 
-def attn_combine(states: torch.Tensor, *, want_out: bool = True, want_state: bool = False):
-    """Merge ``states fp32 [n_parts,B,Hq,2+D]`` -> ``(out fp16 [B,Hq,D] | None, merged [B,Hq,2+D] | None)``."""
-    device = _require_cuda(states)
+def attn_combine(states: torch.Tensor, *, want_out: bool = True, want_state: bool = False, out: torch.Tensor | None = None,
+                 merged: torch.Tensor | None = None):
+    """Merge ``states fp32 [n_parts,B,Hq,2+D]`` -> ``(out fp16 [B,Hq,D] | None, merged [B,Hq,2+D] | None)``.
+
+    ``out`` / ``merged`` may be caller-kept buffers of those shapes (nothing is allocated then).
+    """
+    device = _require_cuda(states, out, merged)
     if states.dtype != torch.float32 or states.ndim != 4:
         raise ValueError("states must be fp32 [n_parts,B,Hq,2+D]")
     states = states.contiguous()
     n, b, hq, w = map(int, states.shape)
-    out = torch.empty(b, hq, w - 2, dtype=torch.float16, device=device) if want_out else None
-    merged = torch.empty(b, hq, w, dtype=torch.float32, device=device) if want_state else None
+    if out is None and want_out:
+        out = torch.empty(b, hq, w - 2, dtype=torch.float16, device=device)
+    if merged is None and want_state:
+        merged = torch.empty(b, hq, w, dtype=torch.float32, device=device)
+    if out is not None and (out.dtype != torch.float16 or tuple(out.shape) != (b, hq, w - 2) or not out.is_contiguous()):
+        raise ValueError("out must be contiguous fp16 [B,Hq,D]")
+    if merged is not None and (merged.dtype != torch.float32 or tuple(merged.shape) != (b, hq, w) or not merged.is_contiguous()):
+        raise ValueError("merged must be contiguous fp32 [B,Hq,2+D]")
     with _on(device):
         status = _lib.load().tacvq_attn_combine(_ptr(states), n, _ptr(out), _ptr(merged), b, hq, w - 2, _stream(device))
     _lib.check("tacvq_attn_combine", status)
