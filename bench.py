@@ -430,7 +430,8 @@ def run_cq32layers(args) -> dict:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=device)
-    lo, hi = shard_range(CQ_LAYERS, rank, world)
+    n_layers = max(world, min(CQ_LAYERS, args.layers))
+    lo, hi = shard_range(n_layers, rank, world)
     layers = list(range(lo, hi))
     resident = layers[: min(4, len(layers))]
     inputs = {}
@@ -491,10 +492,10 @@ def run_cq32layers(args) -> dict:
     total_ms, enc_ms, dec_ms = (float(x) / args.steps for x in t.tolist())
 
     parity = None
-    if rank == 0 or hi == CQ_LAYERS:
+    if rank == 0 or hi == n_layers:
         from oracle import c_oracle as C
 
-        layer = 0 if rank == 0 else CQ_LAYERS - 1
+        layer = 0 if rank == 0 else n_layers - 1
         g = torch.Generator(device=device).manual_seed(8601 + layer)
         keys = torch.randn(CQ_BATCH, KV_HEADS, CQ_CONTEXT, DIM, generator=g, device=device).half()
         values = torch.randn(CQ_BATCH, KV_HEADS, CQ_CONTEXT, DIM, generator=g, device=device).half()
@@ -525,7 +526,7 @@ def run_cq32layers(args) -> dict:
         "scaling": "strong (32 layers over the ranks); the figures are per layer-step, so they read as weak scaling",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "encode K and V of a layer (fp16 [16,8,16384,128], two additive 256x128 codebooks), then one decode-attention step over its codes; "
-                               "32 layers sharded by layer", "layers_per_rank": len(layers), "batch": CQ_BATCH, "context": CQ_CONTEXT,
+                               "32 layers sharded by layer", "layers": n_layers, "layers_per_rank": len(layers), "batch": CQ_BATCH, "context": CQ_CONTEXT,
                    "l2": "inputs of up to 4 layers (2 GiB each) rotated"},
         "encode": {"ms_per_layer": round(enc_ms, 4), "tokens_per_s": round(CQ_BATCH * CQ_CONTEXT * world / (enc_ms * 1e-3), 1),
                    "tflops_of_distances": round(enc_flops / (enc_ms * 1e-3) / 1e12, 1), "frac_of_bf16_peak": round(enc_flops / (enc_ms * 1e-3) / 1e12 / peaks["bf16"], 4)},
@@ -604,11 +605,41 @@ def run_sequence_split(args) -> dict:
         torch.cuda.synchronize(device)
         for j in range(3):
             acc[j] += ev[j].elapsed_time(ev[j + 1])
-    t = torch.tensor([a / args.steps for a in acc], device=device)
+    # the whole step once more as one CUDA graph per code set (scan, all-gather, merge): what a decode loop would
+    # replay; it removes the host's launch latency between the four launches of a step
+    graph_ms = float("nan")
+    try:
+        side = torch.cuda.Stream(device)
+        graphs = []
+        with torch.cuda.stream(side):
+            scan(0); exchange(); merge()
+            side.synchronize()
+            for i in range(4):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    scan(i); exchange(); merge()
+                graphs.append(g)
+        torch.cuda.synchronize(device)
+        for g in graphs:
+            g.replay()
+        total = 0.0
+        for i in range(args.steps):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(device)
+            ev[0].record()
+            graphs[i % 4].replay()
+            ev[1].record()
+            torch.cuda.synchronize(device)
+            total += ev[0].elapsed_time(ev[1])
+        graph_ms = total / args.steps
+    except Exception as exc:  # capture of the collective unavailable: the stream-launched figures stand alone
+        print(f"graph replay skipped: {exc}", file=sys.stderr, flush=True)
+    t = torch.tensor([a / args.steps for a in acc] + [graph_ms], device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.destroy_process_group()
-    scan_ms, exchange_ms, merge_ms = (float(x) for x in t.tolist())
+    scan_ms, exchange_ms, merge_ms, graph_ms = (float(x) for x in t.tolist())
     if rank != 0:
         return {}
     total = scan_ms + exchange_ms + merge_ms
@@ -619,6 +650,7 @@ def run_sequence_split(args) -> dict:
         "config": {"workload": "sequence-split decode attention over GSRQ 2-stage codes, batch 1, 32 query / 8 KV heads, head_dim 128, 131072 tokens",
                    "tokens_per_rank": own, "l2": f"{n_sets} code sets rotated between steps"},
         "scan_ms": round(scan_ms, 5), "exchange_ms": round(exchange_ms, 5), "merge_ms": round(merge_ms, 5),
+        "ms_per_step_graph_replay": None if graph_ms != graph_ms else round(graph_ms, 5),
         "exchange_bytes_per_rank": Q_HEADS * (DIM + 2) * 4, "gpu_launches": (3 if world > 1 else 4) * args.steps,
         "per_rank_scan_gbs": round((2 * KV_HEADS * own * 32 + 2_097_152) / (scan_ms * 1e-3) / 1e9, 1),
     }
@@ -725,6 +757,7 @@ def main() -> None:
     parser.add_argument("--workload", choices=("decode32k", "cq32layers", "seqsplit131k"), default="decode32k",
                         help="decode32k: the headline configuration; cq32layers: all 32 layers with full-width codebooks, encode + decode; "
                              "seqsplit131k: one sequence split across the ranks")
+    parser.add_argument("--layers", type=int, default=CQ_LAYERS, help="cq32layers: number of layers (default 32; fewer for a small run)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
