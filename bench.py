@@ -230,26 +230,36 @@ def run_decode32k(args) -> dict:
     host_rows = [torch.cat([(torch.randn(nq, generator=hgen) / DIM**0.5).half(), torch.randn(nk, generator=hgen).half(),
                             torch.randn(nk, generator=hgen).half()]).pin_memory() for _ in range(4)]
     host_out = torch.empty(BATCH, Q_HEADS, DIM, dtype=torch.float16).pin_memory()
-    for i in range(8):
-        cache.decode_step_host(host_rows[i % 4], host_out, Q_HEADS)  # waits for the result: the next token depends on it
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        cache.decode_step_host(host_rows[i % 4], host_out, Q_HEADS)
-    barrier()
-    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
-    # host share: the same calls without waiting (enqueue cost only), then one wait
-    t0 = time.perf_counter()
-    for i in range(50):
-        cache.decode_step_host(host_rows[i % 4], host_out, Q_HEADS, synchronize=False)
-    enqueue_ms = (time.perf_counter() - t0) * 1e3 / 50
-    torch.cuda.synchronize(device)
+    def time_host_steps(direct: bool) -> tuple[float, float]:
+        for i in range(8):
+            cache.decode_step_host(host_rows[i % 4], host_out, Q_HEADS, direct=direct)  # waits: the next token depends on it
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            cache.decode_step_host(host_rows[i % 4], host_out, Q_HEADS, direct=direct)
+        barrier()
+        whole = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
+        # host share: the same calls without waiting (enqueue cost only), then one wait
+        t0 = time.perf_counter()
+        for i in range(50):
+            cache.decode_step_host(host_rows[i % 4], host_out, Q_HEADS, synchronize=False, direct=direct)
+        enqueue = (time.perf_counter() - t0) * 1e3 / 50
+        torch.cuda.synchronize(device)
+        return whole, enqueue
+
+    copy_ms, copy_enqueue_ms = time_host_steps(direct=False)
+    cache.length = CONTEXT
+    e2e_ms, enqueue_ms = time_host_steps(direct=True)
     e2e = {
         "value": round(BATCH * world / (e2e_ms * 1e-3), 1), "unit": UNIT, "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps,
         "h2d_bytes_per_step": host_rows[0].numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2,
         "host_enqueue_ms_per_step": round(enqueue_ms, 4),
-        "api": "tacvq_decode_step_host through VQCodeCache.decode_step_host: copy the token's rows from pinned host memory, "
-               "encode + append K and V, attend, copy the result back, wait; code cache resident in HBM",
+        "api": "tacvq_decode_step_host through VQCodeCache.decode_step_host(direct=True): one cudaMemcpyAsync brings the token's "
+               "rows from pinned host memory, K and V are encoded and appended inside the table-preparation kernel, attention "
+               "runs and stores its result straight into the pinned host buffer, the host waits; code cache resident in HBM",
+        "with_copy_back": {"ms_per_step": round(copy_ms, 4), "value": round(BATCH * world / (copy_ms * 1e-3), 1),
+                                 "host_enqueue_ms_per_step": round(copy_enqueue_ms, 4),
+                                 "api": "the same call with direct=False: the result comes back by a second cudaMemcpyAsync"},
     }
     del cache
 

@@ -210,8 +210,12 @@ TACVQ_API int tacvq_decode_step(const uint16_t *q_f16, const void *k_rows, const
  *
  *   host_rows     host buffer (pinned for an asynchronous copy): q [B,Hq,D] fp16, then the new K rows
  *                 [B,Hkv,T_new,D], then the new V rows, K and V in rows_dtype, packed back to back
- *   dev_rows      device buffer of the same size, 16-byte aligned: the landing place of host_rows
- *   dev_out       device [B,Hq,D] fp16;  host_out  host buffer of the same size receiving it
+ *   dev_rows      device buffer of the same size, 16-byte aligned: the landing place of host_rows;
+ *                 NULL: no copy is enqueued and the kernels read host_rows in place over the host link, which
+ *                 needs host_rows to be page-locked (cudaHostAlloc / cudaHostRegister) and 16-byte aligned;
+ *                 pageable memory is refused with TACVQ_ERR_NULL before anything is launched
+ *   dev_out       device [B,Hq,D] fp16;  host_out  host buffer of the same size receiving it;
+ *                 dev_out NULL: the attention kernel stores the result straight into host_out (page-locked)
  *   synchronize   non-zero: return after the stream has finished (host_out is valid on return)
  * Other arguments and status codes as tacvq_decode_step.
  */

@@ -24,6 +24,14 @@ import torch
 from . import ops
 
 
+
+def _raw_stream(index: int) -> int:
+    """Handle of torch's current stream on device ``index`` (the quick accessor when this torch has it)."""
+    try:
+        return torch._C._cuda_getCurrentRawStream(index)
+    except AttributeError:  # older or newer torch without the accessor
+        return torch.cuda.current_stream(index).cuda_stream
+
 class VQCodeCache:
     """K and V codes of one layer for a batch of sequences that advance in lockstep."""
 
@@ -173,7 +181,7 @@ class VQCodeCache:
         return out
 
     def decode_step_host(self, host_rows: torch.Tensor, host_out: torch.Tensor, q_heads: int, *, tokens: int = 1,
-                         synchronize: bool = True) -> torch.Tensor:
+                         synchronize: bool = True, direct: bool = False) -> torch.Tensor:
         """One decode step driven from HOST buffers in a single library call (``tacvq_decode_step_host``).
 
         ``host_rows``: pinned CPU fp16 tensor holding, back to back, the scaled query ``[B,Hq,D]``, the new K
@@ -181,41 +189,57 @@ class VQCodeCache:
         result.  The call enqueues the copy to the device, the encode + append + attention of
         :meth:`decode_step` and the copy back, and by default waits for them.  A decoding loop passes the same
         buffers every step: checks and argument marshalling happen once per pair of buffers.
+        ``direct=True`` enqueues no copy back: the attention kernel stores the result straight into the pinned
+        ``host_out`` (the rows still arrive by an enqueued copy, which is faster than reading them in place).
         """
+        key = (host_rows.data_ptr(), host_out.data_ptr(), host_rows.numel(), host_out.numel(), q_heads, tokens, direct)
+        if key != self._host_key:
+            self._prepare_host_call(host_rows, host_out, int(q_heads), int(tokens), bool(direct))
+            self._host_key = key
+        args, call, index = self._host_call
+        if self.length + tokens > self.max_tokens:
+            raise ValueError("code cache is full")
+        args[9] = self.length
+        args[24] = 1 if synchronize else 0
+        args[25] = _raw_stream(index)
+        if index == torch.cuda.current_device():
+            status = call(*args)
+        else:
+            with torch.cuda.device(self.device):
+                status = call(*args)
+        if status:
+            from . import _lib
+
+            _lib.check("tacvq_decode_step_host", status)
+        self.length += tokens
+        self._range_is = self.visible()
+        return host_out
+
+    def _prepare_host_call(self, host_rows: torch.Tensor, host_out: torch.Tensor, q_heads: int, tokens: int, direct: bool) -> None:
+        """Checks and argument marshalling of :meth:`decode_step_host`, done once per pair of host buffers."""
         from . import _lib
 
         if self.rope is not None:
             raise ValueError("the single-call host path has no rotary step; use append() + attend()")
-        key = (host_rows.data_ptr(), host_out.data_ptr(), int(q_heads), int(tokens), host_rows.numel(), host_out.numel())
-        if key != self._host_key:
-            nq, nkv = self.batch * int(q_heads) * self.dim, self.batch * self.heads * int(tokens) * self.dim
-            if host_rows.device.type != "cpu" or host_out.device.type != "cpu" or not (host_rows.is_pinned() and host_out.is_pinned()):
-                raise ValueError("host_rows and host_out must be pinned CPU tensors")
-            if host_rows.dtype != torch.float16 or host_out.dtype != torch.float16:
-                raise ValueError("host buffers must be fp16")
-            if host_rows.numel() != nq + 2 * nkv or host_out.numel() != nq or not (host_rows.is_contiguous() and host_out.is_contiguous()):
-                raise ValueError("host_rows must hold q, K rows and V rows back to back; host_out must be [B,Hq,D]")
-            if self._workspace is None:
-                need = ops.attn_workspace_bytes(self.batch, int(q_heads), self.heads, self.dim, self.groups, self.stages)
-                if need == 0:
-                    raise ValueError("attention geometry not supported")
-                self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
-            dev_rows = torch.empty(nq + 2 * nkv, dtype=torch.float16, device=self.device)
-            dev_out = torch.empty(nq, dtype=torch.float16, device=self.device)
-            head = (host_rows.data_ptr(), dev_rows.data_ptr(), ops._DTYPE_TAG[torch.float16], self.key_tables.data_ptr(),
-                    self.value_tables.data_ptr(), self.key.data_ptr(), self.value.data_ptr(), self._range[0].data_ptr(),
-                    self._range[1].data_ptr())
-            mid = (self._workspace.data_ptr(), self._workspace.numel(), dev_out.data_ptr(), host_out.data_ptr(), self.batch,
-                   int(q_heads), self.heads, self.dim, self.groups, self.stages, int(self.key_tables.shape[-2]), int(tokens),
-                   self.max_tokens)
-            self._host_key, self._host_call = key, (head, mid, dev_rows, dev_out, _lib.load().tacvq_decode_step_host)
-        head, mid, _dev_rows, _dev_out, call = self._host_call
-        if self.length + tokens > self.max_tokens:
-            raise ValueError("code cache is full")
-        with ops._on(self.device):
-            status = call(*head, self.length, 0 if self.window is None else self.window, *mid, 1 if synchronize else 0,
-                          ops._stream(self.device))
-        _lib.check("tacvq_decode_step_host", status)
-        self.length += tokens
-        self._range_is = self.visible()
-        return host_out
+        nq, nkv = self.batch * q_heads * self.dim, self.batch * self.heads * tokens * self.dim
+        if host_rows.device.type != "cpu" or host_out.device.type != "cpu" or not (host_rows.is_pinned() and host_out.is_pinned()):
+            raise ValueError("host_rows and host_out must be pinned CPU tensors")
+        if host_rows.dtype != torch.float16 or host_out.dtype != torch.float16:
+            raise ValueError("host buffers must be fp16")
+        if host_rows.numel() != nq + 2 * nkv or host_out.numel() != nq or not (host_rows.is_contiguous() and host_out.is_contiguous()):
+            raise ValueError("host_rows must hold q, K rows and V rows back to back; host_out must be [B,Hq,D]")
+        if self._workspace is None:
+            need = ops.attn_workspace_bytes(self.batch, q_heads, self.heads, self.dim, self.groups, self.stages)
+            if need == 0:
+                raise ValueError("attention geometry not supported")
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        dev_rows = torch.empty(nq + 2 * nkv, dtype=torch.float16, device=self.device)
+        dev_out = None if direct else torch.empty(nq, dtype=torch.float16, device=self.device)
+        args = [host_rows.data_ptr(), dev_rows.data_ptr(), ops._DTYPE_TAG[torch.float16], self.key_tables.data_ptr(),
+                self.value_tables.data_ptr(), self.key.data_ptr(), self.value.data_ptr(), self._range[0].data_ptr(),
+                self._range[1].data_ptr(), 0, 0 if self.window is None else self.window, self._workspace.data_ptr(),
+                self._workspace.numel(), ops._ptr(dev_out), host_out.data_ptr(), self.batch, q_heads, self.heads, self.dim,
+                self.groups, self.stages, int(self.key_tables.shape[-2]), tokens, self.max_tokens, 1, 0]
+        index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self._host_buffers = (dev_rows, dev_out)  # keep the landing buffers alive
+        self._host_call = (args, _lib.load().tacvq_decode_step_host, index)

@@ -34,7 +34,7 @@ size_t attn_gsrq_workspace_bytes(int B, int Hq, int Hkv, int D, int sms);
 int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
                        const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, void *workspace,
                        __half *out, float *state_out, int B, int Hq, int Hkv, int64_t T_cap, int sms,
-                       cudaStream_t stream, bool after_prologue = false);
+                       cudaStream_t stream, const GsrqNewToken *fresh = nullptr);
 int decode_prologue_dispatch(const void *k_rows, const void *v_rows, int rows_dtype, int64_t sxb, int64_t sxh, int64_t sxt,
                              const __half *ktab, const __half *vtab, uint8_t *kcodes, uint8_t *vcodes, int32_t *seq_start,
                              int32_t *seq_end, int start, int end, int B, int H, int T, int D, int G, int S, int K, int64_t t0,
@@ -349,14 +349,25 @@ int tacvq_decode_step(const uint16_t *q_f16, const void *k_rows, const void *v_r
                            (((uintptr_t)kcodes | (uintptr_t)vcodes) & 15) == 0;
         if (plain) {
             cudaStream_t s = (cudaStream_t)stream;
+            const bool gsrq = attn_gsrq_supported(Hq, Hkv, D, G, S, K) && gsrq_batch_ok(B, Hkv) && gsrq_aligned(q_f16, ktab_f16, vtab_f16);
+            if (gsrq && T_new == 1 && ((((uintptr_t)k_rows | (uintptr_t)v_rows) & 15) == 0)) {
+                // benchmark geometry, one new token: the table preparation encodes the token and sets the ranges
+                // itself, so the whole step is two launches
+                const GsrqNewToken token = {k_rows, v_rows, rows_dtype == TACVQ_F32 ? 1 : 0, kcodes, vcodes, seq_start, seq_end,
+                                            (int)new_start, (int)new_end, (long long)length, (long long)T_cap};
+                const int fast = attn_gsrq_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
+                                                    (const __half *)vtab_f16, seq_start, seq_end, workspace, (__half *)out_f16,
+                                                    state_out, B, Hq, Hkv, T_cap, sm_count(), s, &token);
+                if (fast != TACVQ_ERR_UNSUPPORTED) return fast;
+            }
             const int pro = decode_prologue_dispatch(k_rows, v_rows, rows_dtype, (int64_t)Hkv * row, row, D, (const __half *)ktab_f16,
                                                      (const __half *)vtab_f16, kcodes, vcodes, seq_start, seq_end, (int)new_start,
                                                      (int)new_end, B, Hkv, T_new, D, G, S, K, length, T_cap, s);
             if (pro == TACVQ_OK) {
-                if (attn_gsrq_supported(Hq, Hkv, D, G, S, K) && gsrq_batch_ok(B, Hkv) && gsrq_aligned(q_f16, ktab_f16, vtab_f16)) {
+                if (gsrq) {
                     const int fast = attn_gsrq_dispatch((const __half *)q_f16, kcodes, vcodes, (const __half *)ktab_f16,
                                                         (const __half *)vtab_f16, seq_start, seq_end, workspace,
-                                                        (__half *)out_f16, state_out, B, Hq, Hkv, T_cap, sm_count(), s, true);
+                                                        (__half *)out_f16, state_out, B, Hq, Hkv, T_cap, sm_count(), s);
                     if (fast != TACVQ_ERR_UNSUPPORTED) return fast;
                 }
                 return tacvq_attn_decode(q_f16, kcodes, vcodes, ktab_f16, vtab_f16, seq_start, seq_end, workspace,
@@ -379,27 +390,55 @@ int tacvq_decode_step(const uint16_t *q_f16, const void *k_rows, const void *v_r
                              out_f16, state_out, B, Hq, Hkv, D, G, S, K, T_cap, stream);
 }
 
+// The device address of a host buffer that kernels may dereference in place (pinned or registered memory), or
+// nullptr when the buffer is ordinary pageable memory or lives on the device.
+static void *device_view_of_host(const void *host) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, host) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    if (attr.type != cudaMemoryTypeHost) return nullptr;
+    return attr.devicePointer;
+}
+
 int tacvq_decode_step_host(const void *host_rows, void *dev_rows, int rows_dtype, const uint16_t *ktab_f16,
                            const uint16_t *vtab_f16, uint8_t *kcodes, uint8_t *vcodes, int32_t *seq_start, int32_t *seq_end,
                            int64_t length, int64_t window, void *workspace, size_t workspace_bytes, uint16_t *dev_out,
                            void *host_out, int B, int Hq, int Hkv, int D, int G, int S, int K, int T_new, int64_t T_cap,
                            int synchronize, tacvq_stream_t stream) {
-    if (!host_rows || !dev_rows || !dev_out || !host_out) return TACVQ_ERR_NULL;
+    if (!host_rows || !host_out) return TACVQ_ERR_NULL;
     if (!dtype_ok(rows_dtype)) return TACVQ_ERR_DTYPE;
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || T_new <= 0) return TACVQ_ERR_GEOMETRY;
     const size_t q_bytes = (size_t)B * Hq * D * sizeof(uint16_t);
     const size_t kv_bytes = (size_t)B * Hkv * T_new * D * (rows_dtype == TACVQ_F16 ? 2 : 4);
-    if ((((uintptr_t)dev_rows) & 15) != 0 || (q_bytes & 15) != 0 || (kv_bytes & 15) != 0) return TACVQ_ERR_ALIGN;
+    if ((q_bytes & 15) != 0 || (kv_bytes & 15) != 0) return TACVQ_ERR_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
-    cudaError_t e = cudaMemcpyAsync(dev_rows, host_rows, q_bytes + 2 * kv_bytes, cudaMemcpyHostToDevice, s);
-    if (e != cudaSuccess) return (int)e;
-    unsigned char *base = (unsigned char *)dev_rows;
-    const int st = tacvq_decode_step((const uint16_t *)base, base + q_bytes, base + q_bytes + kv_bytes, rows_dtype, ktab_f16,
+    cudaError_t e;
+    // Without a landing buffer the kernels read the rows where they lie (the prologue and the table preparation
+    // each read them once, over the host link), and without dev_out the merging blocks store to host_out.
+    const unsigned char *rows = (const unsigned char *)dev_rows;
+    if (!rows) {
+        rows = (const unsigned char *)device_view_of_host(host_rows);
+        if (!rows) return TACVQ_ERR_NULL;
+    } else {
+        e = cudaMemcpyAsync(dev_rows, host_rows, q_bytes + 2 * kv_bytes, cudaMemcpyHostToDevice, s);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (((uintptr_t)rows & 15) != 0) return TACVQ_ERR_ALIGN;
+    uint16_t *out = dev_out;
+    if (!out) {
+        out = (uint16_t *)device_view_of_host(host_out);
+        if (!out) return TACVQ_ERR_NULL;
+    }
+    const int st = tacvq_decode_step((const uint16_t *)rows, rows + q_bytes, rows + q_bytes + kv_bytes, rows_dtype, ktab_f16,
                                      vtab_f16, kcodes, vcodes, seq_start, seq_end, length, window, workspace, workspace_bytes,
-                                     dev_out, nullptr, B, Hq, Hkv, D, G, S, K, T_new, T_cap, stream);
+                                     out, nullptr, B, Hq, Hkv, D, G, S, K, T_new, T_cap, stream);
     if (st != TACVQ_OK) return st;
-    e = cudaMemcpyAsync(host_out, dev_out, q_bytes, cudaMemcpyDeviceToHost, s);
-    if (e != cudaSuccess) return (int)e;
+    if (dev_out) {
+        e = cudaMemcpyAsync(host_out, dev_out, q_bytes, cudaMemcpyDeviceToHost, s);
+        if (e != cudaSuccess) return (int)e;
+    }
     if (synchronize) {
         e = cudaStreamSynchronize(s);
         if (e != cudaSuccess) return (int)e;

@@ -36,14 +36,15 @@
 // once; the successor waits for it before touching its results):
 //   prepare  one block per (batch row, KV head, stage): the score table of the pair (q . codeword for
 //            4096 codewords x 4 heads straight from the fp16 K tables, quantised to 13 bits), written to
-//            scratch in the order the scan's shared memory wants.  A build costs about 5 us of a 512-thread
+//            scratch in the order the scan's shared memory wants; its share of the V codewords in that
+//            order; and, in a decode step, the codes of the pair's new K or V row and the visible ranges.  A build costs about 5 us of a 512-thread
 //            block per stage (64 values per thread, quarter-rate conversions); building inside the scan
 //            was measured twice and repeats that for every block that enters a pair (3.3 per pair).
 //   scan     a persistent grid (one block per SM) walks the flattened (KV head, batch row, 32-token
 //            tile) space; every block gets an equal share of work units.  When it enters a new (batch
 //            row, KV head) pair it copies that pair's score table (64 KB, flat) and, when the head
-//            changed, gathers the head's V codewords from the fp16 V tables into their bank-striped
-//            order (for its first pair before it waits for the prepare grid).  It writes one partial
+//            changed, the head's V codewords, which the prepare grid wrote in their bank-striped
+//            order (128 KB, flat).  It writes one partial
 //            softmax state per pair it touches, then marks it; the block that finds every partial of a
 //            pair marked merges them (log-sum-exp) and writes fp16 output and/or fp32 state.  A pair
 //            that lies inside one block's share is written directly.
@@ -57,6 +58,7 @@
 #include <atomic>
 
 #include "common.cuh"
+#include "encode_rows.cuh"
 
 namespace tacvq {
 
@@ -81,6 +83,9 @@ constexpr int kMaxBatch = 512;
 #endif
 #ifndef TACVQ_GSRQ_EARLY_K
 #define TACVQ_GSRQ_EARLY_K 0  // 1: the next tile's K codes are requested before the score phase (8 more registers live)
+#endif
+#ifndef TACVQ_GSRQ_VPERM
+#define TACVQ_GSRQ_VPERM 1  // 1: the prepare grid writes the V codewords in shared-memory order, the scan copies them flat
 #endif
 #ifndef TACVQ_GSRQ_LAZY_MAX
 #define TACVQ_GSRQ_LAZY_MAX 1  // 0: every tile reduces its maximum over the warp (20 shuffles)
@@ -190,6 +195,8 @@ __device__ __forceinline__ int value_pos(int s, int g) { return (g >> 2) * 8 + s
 
 __device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+using NewToken = GsrqNewToken;
+
 // ------------------------------------------------------------------------------------------------
 // prepare kernel: block (pair p = h*B + b, stage) builds one stage of the pair's score table
 // ------------------------------------------------------------------------------------------------
@@ -205,7 +212,7 @@ constexpr int kPrepCodes = kWords / (2 * kPrepWarps);  // codes per thread
 
 __global__ void __launch_bounds__(kPrepThreads)
 attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict__ ktab, const __half *__restrict__ vtab,
-                         uint2 *__restrict__ lut_g, float *__restrict__ scale_g, uint4 *__restrict__ vperm_g, int B, int Hkv) {
+                         uint2 *__restrict__ lut_g, float *__restrict__ scale_g, uint4 *__restrict__ vperm_g, int B, int Hkv, const NewToken fresh) {
     __shared__ float red[kPrepWarps * 8 * 32];  // [warp][min x4, max x4][lane]
     __shared__ float red2[8 * 32];
     launch_dependents();  // the scan may be scheduled as soon as SMs free up; it waits for this grid itself
@@ -214,31 +221,51 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
     const int h = pair / B, b = pair % B;
     const int Hq = Hkv * kRep;
     const int g = lane & 15, half = lane >> 4;
-    // inputs of this kernel (q, K and V tables) are not produced by the kernels of this chain: read at once
-    // this block's share of the V codewords in the scan's bank-striped order: entry (head, code, pos) <- 16 bytes
-    constexpr int kPermPerThread = 8;
-    const int perm_total = Hkv * kWords * kSlots;
-    const int perm_per_block = (perm_total + (int)gridDim.x - 1) / (int)gridDim.x;
-    uint4 perm[kPermPerThread];
+    // A decode step's new token: this block (pair, side = stage) encodes the 16 groups of the pair's new K
+    // (side 0) or V (side 1) row, a warp per group, with the arithmetic of the row-at-a-time encode kernel.
+    // The words of both stages are requested at once (one memory latency instead of two); the codes are kept
+    // in registers and stored after the wait below.  None of these inputs is produced by this chain.
+    int fresh_code[kStages] = {0, 0};
+    if (fresh.k_rows != nullptr) {
+        static_assert(kPrepWarps == kGroups && kStages == 2 && kWords == 256, "a warp per group, 8 words per lane and stage");
+        const __half *side_tab = stage ? vtab : ktab;
+        const uint4 *words0 = reinterpret_cast<const uint4 *>(side_tab + (((size_t)h * kStages + 0) * kGroups + warp) * kWords * kSub);
+        const uint4 *words1 = words0 + (size_t)kGroups * kWords;
+        uint4 w0[8], w1[8];
 #pragma unroll
-    for (int i = 0; i < kPermPerThread; ++i) {
-        const int local = tid + i * kPrepThreads;
-        const int e = blockIdx.x * perm_per_block + local;
-        perm[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (local < perm_per_block && e < perm_total) {
-            const int hh = e >> 13, code = (e >> 5) & 255, pos = e & 31;
-            const int s = (pos >> 2) & 1, gg = ((pos >> 3) << 2) | (pos & 3);
-            perm[i] = __ldg(reinterpret_cast<const uint4 *>(vtab + ((((size_t)hh * kStages + s) * kGroups + gg) * kWords + code) * kSub));
+        for (int i = 0; i < 8; ++i) w0[i] = __ldg(words0 + lane + 32 * i);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w1[i] = __ldg(words1 + lane + 32 * i);
+        const size_t at = ((size_t)b * Hkv + h) * kDim + warp * kSub;
+        float res[kSub];
+        if (fresh.rows_f32) {
+            const float4 *src = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(stage ? fresh.v_rows : fresh.k_rows) + at);
+            const float4 lo = src[0], hi = src[1];
+            res[0] = lo.x, res[1] = lo.y, res[2] = lo.z, res[3] = lo.w, res[4] = hi.x, res[5] = hi.y, res[6] = hi.z, res[7] = hi.w;
+        } else {
+            unpack8(*reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(stage ? fresh.v_rows : fresh.k_rows) + at), res);
         }
+        fresh_code[0] = nearest_of_fetched_words(res, w0, lane);
+        {
+            float c[kSub];
+            unpack8(__ldg(words0 + fresh_code[0]), c);
+#pragma unroll
+            for (int i = 0; i < kSub; ++i) res[i] = __fsub_rn(res[i], c[i]);
+        }
+        fresh_code[1] = nearest_of_fetched_words(res, w1, lane);
     }
+    // inputs of the table build (q and the K tables) are not produced by the kernels of this chain either
     const uint4 *tab = reinterpret_cast<const uint4 *>(ktab + (((size_t)h * kStages + stage) * kGroups + g) * kWords * kSub);
     uint4 raw[kPrepCodes];
 #pragma unroll
     for (int c = 0; c < kPrepCodes; ++c) raw[c] = __ldg(tab + warp * 2 + half + 2 * kPrepWarps * c);
+    uint4 qraw[kRep];
+#pragma unroll
+    for (int r = 0; r < kRep; ++r) qraw[r] = __ldg(reinterpret_cast<const uint4 *>(q + ((size_t)b * Hq + h * kRep + r) * kDim + g * kSub));
     float qv[kRep][kSub];
 #pragma unroll
     for (int r = 0; r < kRep; ++r) {
-        const uint4 qr = __ldg(reinterpret_cast<const uint4 *>(q + ((size_t)b * Hq + h * kRep + r) * kDim + g * kSub));
+        const uint4 qr = qraw[r];
         const __half2 *hp = reinterpret_cast<const __half2 *>(&qr);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -327,6 +354,20 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
     // The scratch written below is read by the scan of the call before this one, which may still be
     // running when this grid starts: wait for everything before this grid, then write.
     wait_for_previous_kernel();
+    if (fresh.k_rows != nullptr) {
+        // the scan before this grid read the ranges and the code buffers up to its own end; both may change now
+        if (lane == 0) {
+            uint8_t *dst = (stage ? fresh.vcodes : fresh.kcodes) + (((size_t)b * Hkv + h) * (size_t)fresh.T_cap + (size_t)fresh.position) * kSlots;
+#pragma unroll
+            for (int s = 0; s < kStages; ++s) dst[s * kGroups + warp] = (uint8_t)fresh_code[s];
+        }
+        if (blockIdx.x == 0) {
+            for (int i = tid; i < B; i += kPrepThreads) {
+                fresh.seq_start[i] = fresh.start;
+                fresh.seq_end[i] = fresh.end;
+            }
+        }
+    }
 #pragma unroll
     for (int c = 0; c < kPrepCodes; ++c) {
         const int code = warp * 2 + half + 2 * kPrepWarps * c;
@@ -339,20 +380,20 @@ attn_gsrq_prepare_kernel(const __half *__restrict__ q, const __half *__restrict_
             scale_g[((size_t)pair * kStages + stage) * 8 + 4 + r] = scale_offs[r];
         }
     }
-#pragma unroll
-    for (int i = 0; i < kPermPerThread; ++i) {
-        const int local = tid + i * kPrepThreads;
-        const int e = blockIdx.x * perm_per_block + local;
-        if (local < perm_per_block && e < perm_total) vperm_g[e] = perm[i];
-    }
-    for (int local = tid + kPermPerThread * kPrepThreads; local < perm_per_block; local += kPrepThreads) {  // tiny batches only
-        const int e = blockIdx.x * perm_per_block + local;
-        if (e < perm_total) {
-            const int hh = e >> 13, code = (e >> 5) & 255, pos = e & 31;
-            const int s = (pos >> 2) & 1, gg = ((pos >> 3) << 2) | (pos & 3);
-            vperm_g[e] = __ldg(reinterpret_cast<const uint4 *>(vtab + ((((size_t)hh * kStages + s) * kGroups + gg) * kWords + code) * kSub));
+#if TACVQ_GSRQ_VPERM
+    {
+        const int perm_total = Hkv * kWords * kSlots;
+        const int perm_per_block = (perm_total + (int)gridDim.x - 1) / (int)gridDim.x;
+        for (int local = tid; local < perm_per_block; local += kPrepThreads) {
+            const int e = blockIdx.x * perm_per_block + local;
+            if (e < perm_total) {
+                const int hh = e >> 13, code = (e >> 5) & 255, pos = e & 31;
+                const int s = (pos >> 2) & 1, gg = ((pos >> 3) << 2) | (pos & 3);
+                vperm_g[e] = __ldg(reinterpret_cast<const uint4 *>(vtab + ((((size_t)hh * kStages + s) * kGroups + gg) * kWords + code) * kSub));
+            }
         }
     }
+#endif
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -425,7 +466,7 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
 __global__ void __launch_bounds__(kThreads, 1)
 attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes, const uint8_t *__restrict__ vcodes,
                       const uint2 *__restrict__ lut_g, const float *__restrict__ scale_g,
-                      const uint4 *__restrict__ vperm_g, const int32_t *__restrict__ seq_start,
+                      const __half *__restrict__ vtab, const uint4 *__restrict__ vperm_g, const int32_t *__restrict__ seq_start,
                       const int32_t *__restrict__ seq_end, float *__restrict__ part, unsigned long long *__restrict__ marks,
                       __half *__restrict__ out, float *__restrict__ state_out, int B, int Hkv, int T_cap,
                       unsigned long long epoch) {
@@ -461,16 +502,35 @@ attn_gsrq_scan_kernel(const uint8_t *__restrict__ kcodes, const uint8_t *__restr
         }
         __syncthreads();
     };
-    // value codewords of a head, which the prepare grid wrote in the bank-striped order: a flat 128 KB copy
+    // value codewords of a head in the bank-striped rows [word][position].  Default: a flat 128 KB copy of what the
+    // prepare grid wrote in that order.  Without TACVQ_GSRQ_VPERM the block gathers them from the fp16 V tables
+    // [stage][group][word][8] itself (per trip a warp copies 4 neighbouring words of 8 positions with different
+    // banks: whole 32-byte sectors in, no conflicts out) and starts with the head it will most likely begin in
+    // before it waits for the prepare grid; measured 6 us per step slower than the flat copy.
     auto copy_value_table = [&](int h) {
-        const uint4 *src = vperm_g + (size_t)h * (kWords * kSlots);
-        for (int e = tid; e < kWords * kSlots; e += kThreads) cp_async16(smem_u32(vtab_s) + e * 16, src + e);
+#if TACVQ_GSRQ_VPERM
+        const uint4 *flat = vperm_g + (size_t)h * (kWords * kSlots);
+        for (int e = tid; e < kWords * kSlots; e += kThreads) cp_async16(smem_u32(vtab_s) + e * 16, flat + e);
+#else
+        const __half *src = vtab + (size_t)h * (kStages * kGroups * kWords * kSub);
+        const uint32_t dst = smem_u32(vtab_s);
+        for (int idx = tid; idx < kWords * kSlots; idx += kThreads) {
+            const int pos = ((idx >> 5) & 3) * 8 + (idx & 7);
+            const int word = ((idx >> 7) << 2) | ((idx >> 3) & 3);
+            const int s = (pos >> 2) & 1, g = ((pos >> 3) << 2) | (pos & 3);
+            cp_async16(dst + word * (kSlots * 16) + pos * 16, src + ((size_t)(s * kGroups + g) * kWords + word) * kSub);
+        }
+#endif
     };
 
-    // The score and value tables come from the prepare grid, and the visible ranges and newest code rows may
-    // still be being written two kernels back (a decode step's prologue lets its successors start early): of
-    // the kernels of this chain, nothing is read before this wait.
+    // The score and value tables come from the prepare grid, and the visible ranges and newest code rows may be
+    // written by it too (a decode step's new token): of the kernels of this chain, nothing is read before the wait.
+#if TACVQ_GSRQ_VPERM
     int loaded_head = -1;
+#else
+    int loaded_head = min((int)(((long long)blockIdx.x * Hkv) / (long long)gridDim.x), Hkv - 1);
+    copy_value_table(loaded_head);
+#endif
     wait_for_previous_kernel();
     launch_dependents();  // the next kernel on the stream may take SMs as they free up; it waits for this grid itself
     work_prefix();
@@ -907,7 +967,7 @@ struct GsrqWorkspace {  // offsets into the caller's scratch; slot index = pair 
         marks = align256(slots * gsrq::kRep * gsrq::kStateWidth * sizeof(float));
         lut = align256(marks + slots * sizeof(unsigned long long));
         vperm = lut + pairs * gsrq::kLutBytes;
-        scale = vperm + (size_t)Hkv * gsrq::kVtabBytes;
+        scale = vperm + (TACVQ_GSRQ_VPERM ? (size_t)Hkv * gsrq::kVtabBytes : 0);
         total = align256(scale + pairs * gsrq::kStages * 8 * sizeof(float));
     }
 };
@@ -925,9 +985,8 @@ static std::atomic<unsigned long long> g_epoch{0x9e3779b97f4a7c15ull};
 int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
                        const __half *vtab, const int32_t *seq_start, const int32_t *seq_end, void *workspace,
                        __half *out, float *state_out, int B, int Hq, int Hkv, int64_t T_cap, int sms,
-                       cudaStream_t stream, bool after_prologue) {
+                       cudaStream_t stream, const GsrqNewToken *fresh) {
     (void)Hq;
-    (void)after_prologue;  // every kernel of the chain waits for its predecessor by itself
     if (B > gsrq::kMaxBatch || sms > gsrq::kMaxScanBlocks) return TACVQ_ERR_UNSUPPORTED;
     if (T_cap > ((int64_t)1 << 26)) return TACVQ_ERR_UNSUPPORTED;  // byte offsets inside a row's codes are 32-bit
     if (((T_cap + gsrq::kTile - 1) / gsrq::kTile + gsrq::kItemCost) * B * Hkv > 0x7fffffffLL) return TACVQ_ERR_UNSUPPORTED;
@@ -957,14 +1016,15 @@ int attn_gsrq_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vc
     unsigned long long *marks = (unsigned long long *)(base + ws.marks);
     uint2 *lut = (uint2 *)(base + ws.lut);
     float *scale = (float *)(base + ws.scale);
-    uint4 *vperm = (uint4 *)(base + ws.vperm);
     const unsigned long long epoch = g_epoch.fetch_add(2, std::memory_order_relaxed);  // odd, so never 0 (= cleared)
+    GsrqNewToken token = {};
+    if (fresh) token = *fresh;
     cudaError_t e = launch_dependent(gsrq::attn_gsrq_prepare_kernel, dim3(2 * B * Hkv), dim3(gsrq::kPrepThreads), 0, stream, q,
-                                     ktab, vtab, lut, scale, vperm, B, Hkv);
+                                     ktab, vtab, lut, scale, (uint4 *)(base + ws.vperm), B, Hkv, token);
     int st = e == cudaSuccess ? launch_status() : (int)e;
     if (st != TACVQ_OK) return st;
     e = launch_dependent(gsrq::attn_gsrq_scan_kernel, dim3(sms), dim3(gsrq::kThreads), gsrq::kSmemBytes, stream, kcodes, vcodes,
-                         (const uint2 *)lut, (const float *)scale, (const uint4 *)vperm, seq_start, seq_end, part, marks, out,
+                         (const uint2 *)lut, (const float *)scale, vtab, (const uint4 *)(base + ws.vperm), seq_start, seq_end, part, marks, out,
                          state_out, B, Hkv, (int)T_cap, epoch);
     return e == cudaSuccess ? launch_status() : (int)e;
 }

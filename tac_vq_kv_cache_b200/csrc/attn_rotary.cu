@@ -657,10 +657,20 @@ static int launch_rotary_staged(const __half *q, const uint8_t *kcodes, const ui
     return launch_status();
 }
 
+// attn_rotary_mma.cu: the same block decomposition with both contractions on the tensor cores
+bool attn_rotary_mma_supported(int Hq, int Hkv, int D, int G, int S, int K);
+int attn_rotary_mma_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab, const __half *vtab,
+                             const __half *rope, const int32_t *seq_start, const int32_t *seq_end, float *part, int B, int Hq,
+                             int Hkv, int64_t T_cap, int splits, cudaStream_t stream);
+
 int attn_rotary_staged_dispatch(const __half *q, const uint8_t *kcodes, const uint8_t *vcodes, const __half *ktab,
                                 const __half *vtab, const __half *rope, const int32_t *seq_start, const int32_t *seq_end,
                                 float *part, int B, int Hq, int Hkv, int G, int S, int64_t T_cap, int splits,
                                 cudaStream_t stream) {
+#ifndef TACVQ_ROTARY_SCALAR
+    if (rope != nullptr && attn_rotary_mma_supported(Hq, Hkv, 128, G, S, 256) && (((uintptr_t)kcodes | (uintptr_t)vcodes | (uintptr_t)q) & 15) == 0)
+        return attn_rotary_mma_dispatch(q, kcodes, vcodes, ktab, vtab, rope, seq_start, seq_end, part, B, Hq, Hkv, T_cap, splits, stream);
+#endif
     switch (Hq / Hkv) {
         case 1: return launch_rotary_staged<1>(q, kcodes, vcodes, ktab, vtab, rope, seq_start, seq_end, part, B, Hq, Hkv, G, S, T_cap, splits, stream);
         case 2: return launch_rotary_staged<2>(q, kcodes, vcodes, ktab, vtab, rope, seq_start, seq_end, part, B, Hq, Hkv, G, S, T_cap, splits, stream);

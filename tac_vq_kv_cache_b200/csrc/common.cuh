@@ -130,6 +130,18 @@ struct EncodeArgs {
     cudaStream_t stream;
 };
 
+// The new token of a decode step, handed to the benchmark-geometry attention when its table preparation
+// also does the step's bookkeeping: rows [B][Hkv][128] of K and V to encode into the code buffers at
+// `position`, and the visible range [start, end) that every sequence gets.
+struct GsrqNewToken {
+    const void *k_rows, *v_rows;
+    int rows_f32;
+    uint8_t *kcodes, *vcodes;
+    int32_t *seq_start, *seq_end;
+    int start, end;
+    long long position, T_cap;
+};
+
 inline int launch_status() {
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TACVQ_OK : static_cast<int>(e);

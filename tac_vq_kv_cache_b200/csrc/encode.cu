@@ -13,6 +13,7 @@
 // src/jointkv/cq_tac.py:86-105 (grouped one-stage form).
 
 #include "common.cuh"
+#include "encode_rows.cuh"
 
 #ifndef TACVQ_ENCODE_TC
 #define TACVQ_ENCODE_TC 1  // 8-wide groups go to the tensor-core filtered kernel (encode_tc.cu)
@@ -179,33 +180,7 @@ __device__ __forceinline__ void encode_row_unit(const XT *__restrict__ x, int64_
     }
     for (int s = 0; s < S; ++s) {
         const int64_t base = (((int64_t)h * S + s) * G + g) * K;
-        const float xx = sqnorm_ordered<DSUB>([&](int i) { return res[i]; });
-        float best = __int_as_float(0x7f800000);
-        int arg = 0x7fffffff;
-        for (int k = lane; k < K; k += 32) {
-            float c[DSUB];
-#pragma unroll
-            for (int i = 0; i < DSUB; ++i) c[i] = __half2float(tables[(base + k) * DSUB + i]);
-            const float cc = sqnorm_in ? sqnorm_in[base + k] : sqnorm_ordered<DSUB>([&](int i) { return c[i]; });
-            float dot = 0.0f;
-#pragma unroll
-            for (int i = 0; i < DSUB; ++i) dot = __fmaf_rn(res[i], c[i], dot);
-            const float dist = distance_expr(xx, cc, dot);
-            if (dist < best) {
-                best = dist;
-                arg = k;
-            }
-        }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, off);
-            const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
-            if (ob < best || (ob == best && oa < arg)) {
-                best = ob;
-                arg = oa;
-            }
-        }
-        if (arg >= K) arg = 0;  // every distance was +inf or NaN
+        const int arg = nearest_word_in_warp<DSUB>(res, tables + base * DSUB, sqnorm_in ? sqnorm_in + base : nullptr, K, lane);
 #pragma unroll
         for (int i = 0; i < DSUB; ++i) {
             const float w = __half2float(tables[(base + arg) * DSUB + i]);

@@ -50,9 +50,11 @@ def test_prefill_then_decode_steps_match_the_oracle(device, window):
     assert cache.length == 0 and cache.payload_bytes() == 0
 
 
-def test_single_call_host_step_equals_the_device_step(device):
+@pytest.mark.parametrize("direct", [False, True], ids=["copies", "in-place"])
+def test_single_call_host_step_equals_the_device_step(device, direct):
     """tacvq_decode_step_host (rows from pinned host memory, result back to host, one call) gives the same
-    codes and the same attention result as decode_step on device tensors."""
+    codes and the same attention result as decode_step on device tensors, both with enqueued copies and with the
+    kernels reading and writing the pinned buffers in place."""
     from tac_vq_kv_cache_b200.code_cache import VQCodeCache
 
     gen = torch.Generator().manual_seed(8603)
@@ -72,9 +74,9 @@ def test_single_call_host_step_equals_the_device_step(device):
         host_rows[:nq].copy_(query.reshape(-1))
         host_rows[nq : nq + nkv].copy_(k_new.reshape(-1))
         host_rows[nq + nkv :].copy_(v_new.reshape(-1))
-        got = a.decode_step_host(host_rows, host_out, q_heads)
+        got = a.decode_step_host(host_rows, host_out, q_heads, direct=direct)
         want = b.decode_step(query.to(device), k_new.to(device), v_new.to(device))
         assert torch.equal(got, want.cpu()), step
     assert a.length == b.length == 90 and torch.equal(a.key, b.key) and torch.equal(a.value, b.value)
     with pytest.raises(ValueError):
-        a.decode_step_host(host_rows[:-1], host_out, q_heads)
+        a.decode_step_host(host_rows[:-1], host_out, q_heads, direct=direct)

@@ -68,6 +68,8 @@ def test_rotary_attention_matches_the_reference_golden(golden, device, case):
         (1, 4, 2, 900, 8, 3, 8, 10000.0),        # head_dim 64
         (2, 8, 2, 5000, 32, 1, 4, 1000000.0),    # 32 groups of 4 in the two-pass kernel
         (2, 8, 4, 4500, 16, 1, 8, 10000.0),      # one-stage grouped CQ in the two-pass kernel
+        (1, 8, 4, 9001, 16, 2, 8, 10000.0),      # benchmark layout, 2 query heads per KV head, several splits, ragged tail
+        (2, 4, 4, 333, 16, 2, 8, 1000000.0),     # benchmark layout without head sharing, less than one block of tokens
     ],
 )
 def test_rotary_attention_matches_the_oracle(device, b, hq, hkv, t, groups, stages, sub, theta):
