@@ -615,10 +615,12 @@ def run_sequence_split(args) -> dict:
         torch.cuda.synchronize(device)
         for j in range(3):
             acc[j] += ev[j].elapsed_time(ev[j + 1])
-    # the whole step once more as one CUDA graph per code set (scan, all-gather, merge): what a decode loop would
-    # replay; it removes the host's launch latency between the four launches of a step
+    # on one GPU the whole step once more as one CUDA graph per code set (scan, merge): what a decode loop would
+    # replay; it removes the host's launch latency between the launches of a step
     graph_ms = float("nan")
     try:
+        if world > 1:  # a captured collective would need every rank to capture and replay in lockstep: not timed
+            raise RuntimeError("measured on one GPU only")
         side = torch.cuda.Stream(device)
         graphs = []
         with torch.cuda.stream(side):
@@ -634,8 +636,6 @@ def run_sequence_split(args) -> dict:
             g.replay()
         total = 0.0
         for i in range(args.steps):
-            if world > 1:
-                dist.barrier()
             torch.cuda.synchronize(device)
             ev[0].record()
             graphs[i % 4].replay()
@@ -643,7 +643,7 @@ def run_sequence_split(args) -> dict:
             torch.cuda.synchronize(device)
             total += ev[0].elapsed_time(ev[1])
         graph_ms = total / args.steps
-    except Exception as exc:  # capture of the collective unavailable: the stream-launched figures stand alone
+    except Exception as exc:  # the stream-launched figures stand alone
         print(f"graph replay skipped: {exc}", file=sys.stderr, flush=True)
     t = torch.tensor([a / args.steps for a in acc] + [graph_ms], device=device)
     if world > 1:
