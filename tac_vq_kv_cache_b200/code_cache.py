@@ -181,7 +181,7 @@ class VQCodeCache:
         return out
 
     def decode_step_host(self, host_rows: torch.Tensor, host_out: torch.Tensor, q_heads: int, *, tokens: int = 1,
-                         synchronize: bool = True, direct: bool = False) -> torch.Tensor:
+                         synchronize: bool = True, direct: bool | str = False) -> torch.Tensor:
         """One decode step driven from HOST buffers in a single library call (``tacvq_decode_step_host``).
 
         ``host_rows``: pinned CPU fp16 tensor holding, back to back, the scaled query ``[B,Hq,D]``, the new K
@@ -190,11 +190,14 @@ class VQCodeCache:
         :meth:`decode_step` and the copy back, and by default waits for them.  A decoding loop passes the same
         buffers every step: checks and argument marshalling happen once per pair of buffers.
         ``direct=True`` enqueues no copy back: the attention kernel stores the result straight into the pinned
-        ``host_out`` (the rows still arrive by an enqueued copy, which is faster than reading them in place).
+        ``host_out`` (the rows still arrive by an enqueued copy, which was measured faster than reading them in
+        place).  ``direct="rows"`` enqueues no copy at all: the kernels also read the pinned rows in place.
         """
         key = (host_rows.data_ptr(), host_out.data_ptr(), host_rows.numel(), host_out.numel(), q_heads, tokens, direct)
         if key != self._host_key:
-            self._prepare_host_call(host_rows, host_out, int(q_heads), int(tokens), bool(direct))
+            if direct not in (False, True, "rows"):
+                raise ValueError('direct must be False, True or "rows"')
+            self._prepare_host_call(host_rows, host_out, int(q_heads), int(tokens), direct)
             self._host_key = key
         args, call, index = self._host_call
         if self.length + tokens > self.max_tokens:
@@ -215,7 +218,7 @@ class VQCodeCache:
         self._range_is = self.visible()
         return host_out
 
-    def _prepare_host_call(self, host_rows: torch.Tensor, host_out: torch.Tensor, q_heads: int, tokens: int, direct: bool) -> None:
+    def _prepare_host_call(self, host_rows: torch.Tensor, host_out: torch.Tensor, q_heads: int, tokens: int, direct: bool | str) -> None:
         """Checks and argument marshalling of :meth:`decode_step_host`, done once per pair of host buffers."""
         from . import _lib
 
@@ -233,9 +236,9 @@ class VQCodeCache:
             if need == 0:
                 raise ValueError("attention geometry not supported")
             self._workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
-        dev_rows = torch.empty(nq + 2 * nkv, dtype=torch.float16, device=self.device)
+        dev_rows = None if direct == "rows" else torch.empty(nq + 2 * nkv, dtype=torch.float16, device=self.device)
         dev_out = None if direct else torch.empty(nq, dtype=torch.float16, device=self.device)
-        args = [host_rows.data_ptr(), dev_rows.data_ptr(), ops._DTYPE_TAG[torch.float16], self.key_tables.data_ptr(),
+        args = [host_rows.data_ptr(), ops._ptr(dev_rows), ops._DTYPE_TAG[torch.float16], self.key_tables.data_ptr(),
                 self.value_tables.data_ptr(), self.key.data_ptr(), self.value.data_ptr(), self._range[0].data_ptr(),
                 self._range[1].data_ptr(), 0, 0 if self.window is None else self.window, self._workspace.data_ptr(),
                 self._workspace.numel(), ops._ptr(dev_out), host_out.data_ptr(), self.batch, q_heads, self.heads, self.dim,

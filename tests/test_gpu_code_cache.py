@@ -50,7 +50,7 @@ def test_prefill_then_decode_steps_match_the_oracle(device, window):
     assert cache.length == 0 and cache.payload_bytes() == 0
 
 
-@pytest.mark.parametrize("direct", [False, True], ids=["copies", "in-place"])
+@pytest.mark.parametrize("direct", [False, True, "rows"], ids=["copies", "result-in-place", "rows-and-result-in-place"])
 def test_single_call_host_step_equals_the_device_step(device, direct):
     """tacvq_decode_step_host (rows from pinned host memory, result back to host, one call) gives the same
     codes and the same attention result as decode_step on device tensors, both with enqueued copies and with the
