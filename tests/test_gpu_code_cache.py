@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("window", [96, None])
 def test_prefill_then_decode_steps_match_the_oracle(device, window):
     """The visible range changes at every step - a sliding window of 96, or all stored tokens with the length
-    crossing a 32-token tile edge at 128 - and the fused single call alternates with the two-call route."""
+    crossing a 32-token tile edge at 128 - and the fused single call (fp16 and fp32 rows) alternates with the two-call route."""
     from tac_vq_kv_cache_b200.code_cache import VQCodeCache
 
     gen = torch.Generator().manual_seed(8601)
@@ -36,6 +36,8 @@ def test_prefill_then_decode_steps_match_the_oracle(device, window):
         if step % 2:  # both routes: two calls, or the fused single call
             cache.append(k_new, v_new)
             out = cache.attend(query.to(device))
+        elif step % 4:  # fp32 rows (the same values) take the same route and give the same codes
+            out = cache.decode_step(query.to(device), k_new.float(), v_new.float())
         else:
             out = cache.decode_step(query.to(device), k_new, v_new)
         start, end = cache.visible()
