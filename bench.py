@@ -89,10 +89,12 @@ class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index: int, enabled: bool = True):
+        self.index, self.rows, self.proc, self.enabled = index, [], None, enabled
 
     def __enter__(self):
+        if not self.enabled:  # only the rank that prints the line samples: one polling process per box
+            return self
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
@@ -109,6 +111,9 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         if self.proc is not None:
+            deadline = time.perf_counter() + 1.0
+            while not self.rows and time.perf_counter() < deadline:  # a short region: keep the first sample at least
+                time.sleep(0.02)
             time.sleep(0.15)
             self.proc.terminate()
             try:
@@ -197,7 +202,7 @@ def run_decode32k(args) -> dict:
         step(i)
     barrier()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    clocks = ClockSampler(local)
+    clocks = ClockSampler(local, enabled=rank == 0)
     clocks.__enter__()  # samples through the timed region and the sections after it
     barrier()
     start.record()
@@ -478,13 +483,13 @@ def run_cq32layers(args) -> dict:
             ev[2].record()
         return result
 
+    clocks = ClockSampler(local, enabled=rank == 0)
+    clocks.__enter__()  # from the warm-up on (the same kernels): the timed region alone can be shorter than a sampling period
     for i in range(max(args.warmup, len(layers))):  # every layer's cache gets filled at least once
         layer_step(i, False)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(device)
-    clocks = ClockSampler(local)
-    clocks.__enter__()
     enc_ms = dec_ms = 0.0
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
