@@ -35,7 +35,13 @@ import threading
 import time
 from pathlib import Path
 
-import torch
+# The CPU arm uses every host thread.  A launcher that starts one process per GPU exports OMP_NUM_THREADS=1,
+# which the math libraries read when they load: give them the host's thread count before torch is imported.
+if any(a == "reference" or a == "--impl=reference" for a in sys.argv[1:]) and os.environ.get("RANK", "0") == "0":
+    for _var in ("OMP_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_var] = str(os.cpu_count() or 1)
+
+import torch  # noqa: E402
 
 ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
